@@ -1,0 +1,101 @@
+"""ctypes binding of the C ABI in ``include/gptoss_b200.h`` (the CUDA shared library).
+
+There is no CPU fallback: if the library has not been built, ``load()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB_PATH = CSRC / "libgptoss_b200.so"
+SOURCES = ["routing.cu", "grouped_gemm.cu", "convert.cu", "capi.cu"]
+HEADERS = ["common.cuh", "kernels.cuh", "../../include/gptoss_b200.h"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-shared", "--threads", "4"]
+
+OK, ERR_BAD_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_STATE = range(6)
+WIRE_F32, WIRE_BF16 = 0, 1
+(TAP_SCORES, TAP_TOPK_W, TAP_TOPK_I, TAP_OFFSETS, TAP_SORTED, TAP_X_PACKED, TAP_GATE_UP,
+ TAP_Y_PAIRS) = range(8)
+
+# every symbol include/gptoss_b200.h declares
+EXPORTS = [
+    "gptoss_ctx_create", "gptoss_ctx_destroy", "gptoss_last_error", "gptoss_ctx_status",
+    "gptoss_upload_layer", "gptoss_fill_layer_synthetic", "gptoss_set_router_bias",
+    "gptoss_download_layer", "gptoss_moe_forward", "gptoss_moe_forward_host",
+    "gptoss_moe_forward_partial", "gptoss_moe_route", "gptoss_moe_mlp1_swiglu", "gptoss_moe_mlp2",
+    "gptoss_moe_combine", "gptoss_topk_softmax", "gptoss_moe_build_offsets", "gptoss_read_tap",
+    "gptoss_synth_normal_bf16", "gptoss_version",
+]
+
+
+class MoEDims(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("intermediate", C.c_int), ("n_experts", C.c_int),
+                ("top_k", C.c_int), ("n_layers", C.c_int), ("swiglu_limit", C.c_float)]
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    t = LIB_PATH.stat().st_mtime
+    return any((CSRC / f).stat().st_mtime > t for f in SOURCES + HEADERS)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles the library for sm_100a with nvcc (works without a GPU)."""
+    if not force and not needs_build():
+        return LIB_PATH
+    cmd = ["nvcc", *NVCC_FLAGS, "-o", str(LIB_PATH), *SOURCES]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    r = subprocess.run(cmd, cwd=CSRC, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{r.stdout}")
+    if verbose:
+        print(r.stdout)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as e; "
+                           "e.build()'` first (there is no CPU fallback)")
+    lib = C.CDLL(str(LIB_PATH))
+    vp, i32, u64, f32 = C.c_void_p, C.c_int, C.c_uint64, C.c_float
+    ctxp = vp
+    sig = {
+        "gptoss_ctx_create": ([C.POINTER(MoEDims), i32, i32, i32, i32, i32, C.POINTER(vp)], i32),
+        "gptoss_ctx_destroy": ([ctxp], i32),
+        "gptoss_last_error": ([ctxp], C.c_char_p),
+        "gptoss_ctx_status": ([ctxp], i32),
+        "gptoss_upload_layer": ([ctxp, i32, vp, vp, vp, vp, vp, vp], i32),
+        "gptoss_fill_layer_synthetic": ([ctxp, i32, u64, f32], i32),
+        "gptoss_set_router_bias": ([ctxp, i32, vp], i32),
+        "gptoss_download_layer": ([ctxp, i32, vp, vp, vp, vp, vp, vp], i32),
+        "gptoss_moe_forward": ([ctxp, i32, i32, vp, vp, vp], i32),
+        "gptoss_moe_forward_host": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_moe_forward_partial": ([ctxp, i32, i32, vp, vp, vp], i32),
+        "gptoss_moe_route": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_moe_mlp1_swiglu": ([ctxp, i32, vp], i32),
+        "gptoss_moe_mlp2": ([ctxp, i32, vp], i32),
+        "gptoss_moe_combine": ([ctxp, i32, vp, i32, vp], i32),
+        "gptoss_topk_softmax": ([ctxp, i32, vp, vp, vp, vp], i32),
+        "gptoss_moe_build_offsets": ([ctxp, i32, vp, vp, vp, vp], i32),
+        "gptoss_read_tap": ([ctxp, i32, vp, u64], i32),
+        "gptoss_synth_normal_bf16": ([vp, u64, u64, u64, u64, f32, vp], i32),
+        "gptoss_version": ([], C.c_char_p),
+    }
+    for name, (args, res) in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = args, res
+    _lib = lib
+    return lib

@@ -1,0 +1,520 @@
+// extern "C" entry points of gptoss_b200 (declared in include/gptoss_b200.h): context, weights, the
+// per-layer MoE operator and its stages, taps.  No call aborts or throws; every failure is a status
+// code plus a message retrievable with gptoss_last_error().
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+
+using namespace gptoss;
+
+namespace {
+
+// tensor-stream ids of the synthetic generator (kind + 16 * layer), shared with the Python module `synth`
+enum { kTidRouterW = 2, kTidRouterB = 3, kTidMlp1W = 4, kTidMlp1B = 5, kTidMlp2W = 6, kTidMlp2B = 7 };
+
+struct LayerWeights {
+  __nv_bfloat16 *router_w = nullptr;  // [E,H]
+  float *router_b = nullptr;          // [E]
+  __nv_bfloat16 *w1 = nullptr;        // [E_local][2][I][H]   gate rows, then up rows
+  float *b1g = nullptr, *b1u = nullptr;  // [E_local][I]
+  __nv_bfloat16 *w2 = nullptr;        // [E_local][H][I]
+  float *b2 = nullptr;                // [E_local][H]
+  CUtensorMap map_w1, map_w2;
+  bool ready = false;
+};
+
+}  // namespace
+
+struct gptoss_ctx {
+  gptoss_moe_dims dims;
+  Dims d;
+  int device = 0, rank = 0, world = 1, max_tokens = 0, wire = 0;
+  int n_local = 0, sm_count = kSmCountFallback;
+  int cur_T = 0;
+  RouteBuffers rb{};
+  __nv_bfloat16 *x_packed = nullptr;  // [P,H]
+  __nv_bfloat16 *gate_up = nullptr;   // [P,I]
+  float *y_pairs = nullptr;           // [P,H]
+  int *status = nullptr;              // [kStatusWords]
+  __nv_bfloat16 *t_stage = nullptr;   // [max_tokens,H]  device copies for the host-buffer entry point
+  float *x_stage = nullptr;           // [max_tokens,H]
+  float *staging = nullptr;           // fp32 scratch for weight conversion
+  size_t staging_elems = 0;
+  CUtensorMap map_x, map_h;
+  std::vector<LayerWeights> layers;
+  std::string err;
+
+  int fail(int code, const char *what, cudaError_t e = cudaSuccess) {
+    char buf[512];
+    if (e != cudaSuccess)
+      snprintf(buf, sizeof buf, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    else
+      snprintf(buf, sizeof buf, "%s", what);
+    err = buf;
+    return code;
+  }
+};
+
+#define CK(call)                                                          \
+  do {                                                                    \
+    cudaError_t e_ = (call);                                              \
+    if (e_ != cudaSuccess) return ctx->fail(GPTOSS_ERR_CUDA, #call, e_); \
+  } while (0)
+
+namespace {
+
+template <typename T>
+cudaError_t dev_alloc(T **p, size_t n) {
+  return cudaMalloc(reinterpret_cast<void **>(p), (n ? n : 1) * sizeof(T));
+}
+
+int ensure_staging(gptoss_ctx *ctx, size_t elems) {
+  if (ctx->staging_elems >= elems) return GPTOSS_OK;
+  if (ctx->staging) cudaFree(ctx->staging);
+  ctx->staging = nullptr;
+  ctx->staging_elems = 0;
+  CK(dev_alloc(&ctx->staging, elems));
+  ctx->staging_elems = elems;
+  return GPTOSS_OK;
+}
+
+int check_layer(gptoss_ctx *ctx, int layer, bool need_ready) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (layer < 0 || layer >= ctx->dims.n_layers) return ctx->fail(GPTOSS_ERR_BAD_ARG, "layer index out of range");
+  if (need_ready && !ctx->layers[layer].ready) return ctx->fail(GPTOSS_ERR_STATE, "layer has no weights yet");
+  return GPTOSS_OK;
+}
+
+int alloc_layer(gptoss_ctx *ctx, LayerWeights &w) {
+  if (w.router_w) return GPTOSS_OK;
+  const size_t H = ctx->d.H, I = ctx->d.I, E = ctx->d.E, EL = ctx->n_local;
+  CK(dev_alloc(&w.router_w, E * H));
+  CK(dev_alloc(&w.router_b, E));
+  CK(dev_alloc(&w.w1, EL * 2 * I * H));
+  CK(dev_alloc(&w.b1g, EL * I));
+  CK(dev_alloc(&w.b1u, EL * I));
+  CK(dev_alloc(&w.w2, EL * H * I));
+  CK(dev_alloc(&w.b2, EL * H));
+  CK(encode_weight_map(&w.map_w1, w.w1, H, I, EL * 2));
+  CK(encode_weight_map(&w.map_w2, w.w2, I, H, EL));
+  return GPTOSS_OK;
+}
+
+void free_layer(LayerWeights &w) {
+  cudaFree(w.router_w);
+  cudaFree(w.router_b);
+  cudaFree(w.w1);
+  cudaFree(w.b1g);
+  cudaFree(w.b1u);
+  cudaFree(w.w2);
+  cudaFree(w.b2);
+  w = LayerWeights();
+}
+
+int check_T(gptoss_ctx *ctx, int T) {
+  if (T < 0 || T > ctx->max_tokens) return ctx->fail(GPTOSS_ERR_BAD_ARG, "T outside [0, max_tokens]");
+  return GPTOSS_OK;
+}
+
+GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.map_w = mlp1 ? w.map_w1 : w.map_w2;
+  a.map_act = mlp1 ? ctx->map_x : ctx->map_h;
+  a.offsets = ctx->rb.offsets;
+  a.tb_prefix = ctx->rb.tb_prefix;
+  a.e_begin = ctx->d.e_begin;
+  a.n_local = ctx->n_local;
+  a.n_feat = mlp1 ? ctx->d.I : ctx->d.H;
+  a.n_feat_tiles = (a.n_feat + kTileF - 1) / kTileF;
+  a.k_blocks = ((mlp1 ? ctx->d.H : ctx->d.I) + kBlockK - 1) / kBlockK;
+  a.limit = ctx->d.limit;
+  a.bias_a = mlp1 ? w.b1g : w.b2;
+  a.bias_b = mlp1 ? w.b1u : nullptr;
+  a.gate_up = ctx->gate_up;
+  a.y_pairs = ctx->y_pairs;
+  a.sorted = ctx->rb.sorted;
+  a.topk_w = ctx->rb.topk_w;
+  a.status = ctx->status;
+  return a;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *gptoss_version(void) { return "gptoss_b200 0.1 sm_100a"; }
+
+int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int world, int max_tokens,
+                      int wire_dtype, gptoss_ctx **out) {
+  if (!dims || !out) return GPTOSS_ERR_BAD_ARG;
+  *out = nullptr;
+  if (dims->hidden <= 0 || dims->hidden % 8 || dims->intermediate <= 0 || dims->intermediate % 8 ||
+      dims->n_experts <= 0 || dims->n_experts > kMaxExperts || dims->top_k <= 0 || dims->top_k > kMaxTopK ||
+      dims->top_k > dims->n_experts || dims->n_layers <= 0 || world <= 0 || rank < 0 || rank >= world ||
+      dims->n_experts % world || max_tokens <= 0 || (wire_dtype != GPTOSS_WIRE_F32 && wire_dtype != GPTOSS_WIRE_BF16))
+    return GPTOSS_ERR_BAD_ARG;
+  if ((long long)max_tokens * dims->top_k > (1ll << 30)) return GPTOSS_ERR_BAD_ARG;
+  int n_dev = 0;
+  if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) return GPTOSS_ERR_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return GPTOSS_ERR_CUDA;
+  if (prop.major != 10) return GPTOSS_ERR_UNSUPPORTED;
+  if (cudaSetDevice(device) != cudaSuccess) return GPTOSS_ERR_CUDA;
+
+  gptoss_ctx *ctx = new (std::nothrow) gptoss_ctx();
+  if (!ctx) return GPTOSS_ERR_CUDA;
+  ctx->dims = *dims;
+  ctx->device = device;
+  ctx->rank = rank;
+  ctx->world = world;
+  ctx->max_tokens = max_tokens;
+  ctx->wire = wire_dtype;
+  ctx->n_local = dims->n_experts / world;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->d = Dims{dims->hidden, dims->intermediate, dims->n_experts, dims->top_k, rank * ctx->n_local,
+                (rank + 1) * ctx->n_local, dims->swiglu_limit};
+  ctx->layers.resize(dims->n_layers);
+
+  const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
+  const size_t P = T * k, nblk = (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock;
+  cudaError_t e = cudaSuccess;
+  auto A = [&](cudaError_t r) {
+    if (e == cudaSuccess) e = r;
+  };
+  A(dev_alloc(&ctx->rb.scores, T * E));
+  A(dev_alloc(&ctx->rb.topk_w, P));
+  A(dev_alloc(&ctx->rb.topk_i, P));
+  A(dev_alloc(&ctx->rb.blk_hist, nblk * E));
+  A(dev_alloc(&ctx->rb.blk_base, nblk * E));
+  A(dev_alloc(&ctx->rb.offsets, E + 1));
+  A(dev_alloc(&ctx->rb.sorted, P));
+  A(dev_alloc(&ctx->rb.tb_prefix, E + 1));
+  A(dev_alloc(&ctx->x_packed, P * H));
+  A(dev_alloc(&ctx->gate_up, P * I));
+  A(dev_alloc(&ctx->y_pairs, P * H));
+  A(dev_alloc(&ctx->status, kStatusWords));
+  A(dev_alloc(&ctx->t_stage, T * H));
+  A(dev_alloc(&ctx->x_stage, T * H));
+  if (e == cudaSuccess) A(cudaMemset(ctx->status, 0, kStatusWords * sizeof(int)));
+  // rows never written by the gather are still read by TMA (their columns are discarded): keep them finite
+  if (e == cudaSuccess) A(cudaMemset(ctx->x_packed, 0, P * H * sizeof(__nv_bfloat16)));
+  if (e == cudaSuccess) A(cudaMemset(ctx->gate_up, 0, P * I * sizeof(__nv_bfloat16)));
+  if (e == cudaSuccess) A(encode_act_map(&ctx->map_x, ctx->x_packed, H, P));
+  if (e == cudaSuccess) A(encode_act_map(&ctx->map_h, ctx->gate_up, I, P));
+  if (e != cudaSuccess) {
+    gptoss_ctx_destroy(ctx);
+    return GPTOSS_ERR_CUDA;
+  }
+  *out = ctx;
+  return GPTOSS_OK;
+}
+
+int gptoss_ctx_destroy(gptoss_ctx *ctx) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  for (auto &w : ctx->layers) free_layer(w);
+  cudaFree(ctx->rb.scores);
+  cudaFree(ctx->rb.topk_w);
+  cudaFree(ctx->rb.topk_i);
+  cudaFree(ctx->rb.blk_hist);
+  cudaFree(ctx->rb.blk_base);
+  cudaFree(ctx->rb.offsets);
+  cudaFree(ctx->rb.sorted);
+  cudaFree(ctx->rb.tb_prefix);
+  cudaFree(ctx->x_packed);
+  cudaFree(ctx->gate_up);
+  cudaFree(ctx->y_pairs);
+  cudaFree(ctx->status);
+  cudaFree(ctx->t_stage);
+  cudaFree(ctx->x_stage);
+  cudaFree(ctx->staging);
+  delete ctx;
+  return GPTOSS_OK;
+}
+
+const char *gptoss_last_error(const gptoss_ctx *ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+int gptoss_ctx_status(gptoss_ctx *ctx) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  CK(cudaSetDevice(ctx->device));
+  CK(cudaDeviceSynchronize());
+  int st[kStatusWords];
+  CK(cudaMemcpy(st, ctx->status, sizeof st, cudaMemcpyDeviceToHost));
+  if (st[0] != 0) {
+    CK(cudaMemset(ctx->status, 0, sizeof st));
+    char buf[160];
+    snprintf(buf, sizeof buf, "device-side bounded wait gave up: code %d site 0x%x block %d", st[0], st[1], st[2]);
+    return ctx->fail(st[0] == kDevErrTimeout ? GPTOSS_ERR_TIMEOUT : GPTOSS_ERR_CUDA, buf);
+  }
+  return GPTOSS_OK;
+}
+
+// ---- weights ------------------------------------------------------------------------------------------
+int gptoss_upload_layer(gptoss_ctx *ctx, int layer, const float *router_w, const float *router_b,
+                        const float *mlp1_w, const float *mlp1_b, const float *mlp2_w, const float *mlp2_b) {
+  int rc = check_layer(ctx, layer, false);
+  if (rc) return rc;
+  if (!router_w || !router_b || !mlp1_w || !mlp1_b || !mlp2_w || !mlp2_b)
+    return ctx->fail(GPTOSS_ERR_BAD_ARG, "null weight pointer");
+  CK(cudaSetDevice(ctx->device));
+  LayerWeights &w = ctx->layers[layer];
+  if ((rc = alloc_layer(ctx, w))) return rc;
+  const size_t H = ctx->d.H, I = ctx->d.I, E = ctx->d.E, EL = ctx->n_local, e0 = ctx->d.e_begin;
+  size_t need = 2 * I * H;
+  if (E * H > need) need = E * H;
+  if (EL * 2 * I > need) need = EL * 2 * I;
+  if ((rc = ensure_staging(ctx, need))) return rc;
+  float *st = ctx->staging;
+
+  CK(cudaMemcpy(st, router_w, E * H * sizeof(float), cudaMemcpyHostToDevice));
+  CK(launch_f32_to_bf16(st, w.router_w, E * H, 0));
+  CK(cudaMemcpy(st, router_b, E * sizeof(float), cudaMemcpyHostToDevice));
+  CK(launch_round_bf16_f32(st, w.router_b, E, 0));
+  for (size_t el = 0; el < EL; ++el) {
+    CK(cudaMemcpy(st, mlp1_w + (e0 + el) * 2 * I * H, 2 * I * H * sizeof(float), cudaMemcpyHostToDevice));
+    CK(launch_mlp1_deinterleave(st, w.w1 + el * 2 * I * H, (int)I, (int)H, 0));
+  }
+  for (size_t el = 0; el < EL; ++el) {
+    CK(cudaMemcpy(st, mlp2_w + (e0 + el) * H * I, H * I * sizeof(float), cudaMemcpyHostToDevice));
+    CK(launch_f32_to_bf16(st, w.w2 + el * H * I, H * I, 0));
+  }
+  CK(cudaMemcpy(st, mlp1_b + e0 * 2 * I, EL * 2 * I * sizeof(float), cudaMemcpyHostToDevice));
+  CK(launch_bias_split(st, w.b1g, w.b1u, EL * I, 0));
+  CK(cudaMemcpy(st, mlp2_b + e0 * H, EL * H * sizeof(float), cudaMemcpyHostToDevice));
+  CK(launch_round_bf16_f32(st, w.b2, EL * H, 0));
+  CK(cudaDeviceSynchronize());
+  w.ready = true;
+  return GPTOSS_OK;
+}
+
+int gptoss_fill_layer_synthetic(gptoss_ctx *ctx, int layer, uint64_t seed, float sigma) {
+  int rc = check_layer(ctx, layer, false);
+  if (rc) return rc;
+  CK(cudaSetDevice(ctx->device));
+  LayerWeights &w = ctx->layers[layer];
+  if ((rc = alloc_layer(ctx, w))) return rc;
+  const size_t H = ctx->d.H, I = ctx->d.I, E = ctx->d.E, EL = ctx->n_local, e0 = ctx->d.e_begin;
+  if ((rc = ensure_staging(ctx, EL * 2 * I))) return rc;
+  const uint64_t lo = 16ull * (uint64_t)layer;
+  CK(launch_synth_normal(w.router_w, E * H, seed, kTidRouterW + lo, 0, sigma, 0));
+  CK(launch_synth_normal_f32(w.router_b, E, seed, kTidRouterB + lo, 0, sigma, 0));
+  for (size_t el = 0; el < EL; ++el)
+    CK(launch_synth_mlp1(w.w1 + el * 2 * I * H, (int)I, (int)H, seed, kTidMlp1W + lo, (e0 + el) * 2 * I * H, sigma, 0));
+  CK(launch_synth_normal(w.w2, EL * H * I, seed, kTidMlp2W + lo, e0 * H * I, sigma, 0));
+  CK(launch_synth_normal_f32(ctx->staging, EL * 2 * I, seed, kTidMlp1B + lo, e0 * 2 * I, sigma, 0));
+  CK(launch_bias_split(ctx->staging, w.b1g, w.b1u, EL * I, 0));
+  CK(launch_synth_normal_f32(w.b2, EL * H, seed, kTidMlp2B + lo, e0 * H, sigma, 0));
+  CK(cudaDeviceSynchronize());
+  w.ready = true;
+  return GPTOSS_OK;
+}
+
+int gptoss_set_router_bias(gptoss_ctx *ctx, int layer, const float *router_b) {
+  int rc = check_layer(ctx, layer, true);
+  if (rc) return rc;
+  if (!router_b) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null router bias");
+  CK(cudaSetDevice(ctx->device));
+  if ((rc = ensure_staging(ctx, ctx->d.E))) return rc;
+  CK(cudaMemcpy(ctx->staging, router_b, ctx->d.E * sizeof(float), cudaMemcpyHostToDevice));
+  CK(launch_round_bf16_f32(ctx->staging, ctx->layers[layer].router_b, ctx->d.E, 0));
+  CK(cudaDeviceSynchronize());
+  return GPTOSS_OK;
+}
+
+int gptoss_download_layer(gptoss_ctx *ctx, int layer, float *router_w, float *router_b, float *mlp1_w,
+                          float *mlp1_b, float *mlp2_w, float *mlp2_b) {
+  int rc = check_layer(ctx, layer, true);
+  if (rc) return rc;
+  CK(cudaSetDevice(ctx->device));
+  const LayerWeights &w = ctx->layers[layer];
+  const size_t H = ctx->d.H, I = ctx->d.I, E = ctx->d.E, EL = ctx->n_local;
+  size_t need = 2 * I * H;
+  if (E * H > need) need = E * H;
+  if (EL * 2 * I > need) need = EL * 2 * I;
+  if ((rc = ensure_staging(ctx, need))) return rc;
+  float *st = ctx->staging;
+  if (router_w) {
+    CK(launch_bf16_to_f32(w.router_w, st, E * H, 0));
+    CK(cudaMemcpy(router_w, st, E * H * sizeof(float), cudaMemcpyDeviceToHost));
+  }
+  if (router_b) CK(cudaMemcpy(router_b, w.router_b, E * sizeof(float), cudaMemcpyDeviceToHost));
+  if (mlp1_w)
+    for (size_t el = 0; el < EL; ++el) {
+      CK(launch_mlp1_interleave(w.w1 + el * 2 * I * H, st, (int)I, (int)H, 0));
+      CK(cudaMemcpy(mlp1_w + el * 2 * I * H, st, 2 * I * H * sizeof(float), cudaMemcpyDeviceToHost));
+    }
+  if (mlp1_b) {
+    CK(launch_bias_merge(w.b1g, w.b1u, st, EL * I, 0));
+    CK(cudaMemcpy(mlp1_b, st, EL * 2 * I * sizeof(float), cudaMemcpyDeviceToHost));
+  }
+  if (mlp2_w)
+    for (size_t el = 0; el < EL; ++el) {
+      CK(launch_bf16_to_f32(w.w2 + el * H * I, st, H * I, 0));
+      CK(cudaMemcpy(mlp2_w + el * H * I, st, H * I * sizeof(float), cudaMemcpyDeviceToHost));
+    }
+  if (mlp2_b) CK(cudaMemcpy(mlp2_b, w.b2, EL * H * sizeof(float), cudaMemcpyDeviceToHost));
+  return GPTOSS_OK;
+}
+
+// ---- stages ---------------------------------------------------------------------------------------------
+int gptoss_moe_route(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream) {
+  int rc = check_layer(ctx, layer, true);
+  if (rc) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (!t_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null activation pointer");
+  CK(cudaSetDevice(ctx->device));
+  ctx->cur_T = T;
+  if (T == 0) return GPTOSS_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const LayerWeights &w = ctx->layers[layer];
+  const __nv_bfloat16 *t = static_cast<const __nv_bfloat16 *>(t_dev_bf16);
+  CK(launch_router_topk(t, w.router_w, w.router_b, T, ctx->d, ctx->rb, s));
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, s));
+  CK(launch_scatter_gather(t, ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base, ctx->rb.sorted, ctx->x_packed, s));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_mlp1_swiglu(gptoss_ctx *ctx, int layer, void *stream) {
+  int rc = check_layer(ctx, layer, true);
+  if (rc) return rc;
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  CK(launch_grouped_mlp1(gemm_args(ctx, ctx->layers[layer], true), ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_mlp2(gptoss_ctx *ctx, int layer, void *stream) {
+  int rc = check_layer(ctx, layer, true);
+  if (rc) return rc;
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  CK(launch_grouped_mlp2(gemm_args(ctx, ctx->layers[layer], false), ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_combine(gptoss_ctx *ctx, int T, float *x_dev, int residual, void *stream) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  int rc = check_T(ctx, T);
+  if (rc) return rc;
+  if (!x_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null output pointer");
+  if (T != ctx->cur_T) return ctx->fail(GPTOSS_ERR_STATE, "combine: T differs from the routed batch");
+  CK(cudaSetDevice(ctx->device));
+  if (T == 0) return GPTOSS_OK;
+  CK(launch_combine(ctx->y_pairs, ctx->rb.topk_i, T, ctx->d, x_dev, residual, ctx->sm_count,
+                    static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+// ---- the per-layer operator --------------------------------------------------------------------------------
+static int forward_common(gptoss_ctx *ctx, int layer, int T, const void *t, float *out, int residual, void *stream) {
+  int rc;
+  if ((rc = gptoss_moe_route(ctx, layer, T, t, stream))) return rc;
+  if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
+  if ((rc = gptoss_moe_mlp2(ctx, layer, stream))) return rc;
+  return gptoss_moe_combine(ctx, T, out, residual, stream);
+}
+
+int gptoss_moe_forward(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, float *x_dev, void *stream) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (!x_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null residual pointer");
+  if (ctx->world > 1)
+    return ctx->fail(GPTOSS_ERR_STATE, "world > 1 without attached peers: use gptoss_moe_forward_partial");
+  return forward_common(ctx, layer, T, t_dev_bf16, x_dev, 1, stream);
+}
+
+int gptoss_moe_forward_partial(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, float *partial_dev,
+                               void *stream) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (!partial_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null output pointer");
+  return forward_common(ctx, layer, T, t_dev_bf16, partial_dev, 0, stream);
+}
+
+int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host) {
+  int rc = check_layer(ctx, layer, true);
+  if (rc) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (!t_host || !x_host) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
+  if (T == 0) return GPTOSS_OK;
+  CK(cudaSetDevice(ctx->device));
+  const size_t n = (size_t)T * ctx->d.H;
+  CK(cudaMemcpyAsync(ctx->t_stage, t_host, n * sizeof(uint16_t), cudaMemcpyHostToDevice, 0));
+  CK(cudaMemcpyAsync(ctx->x_stage, x_host, n * sizeof(float), cudaMemcpyHostToDevice, 0));
+  if ((rc = gptoss_moe_forward(ctx, layer, T, ctx->t_stage, ctx->x_stage, nullptr))) return rc;
+  CK(cudaMemcpyAsync(x_host, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, 0));
+  return gptoss_ctx_status(ctx);
+}
+
+// ---- stand-alone routing operators ---------------------------------------------------------------------------
+int gptoss_topk_softmax(gptoss_ctx *ctx, int T, const float *scores_dev, float *topk_w_dev, int *topk_i_dev,
+                        void *stream) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (T < 0) return ctx->fail(GPTOSS_ERR_BAD_ARG, "negative T");
+  if (!scores_dev || !topk_w_dev || !topk_i_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null pointer");
+  if (T == 0) return GPTOSS_OK;
+  CK(cudaSetDevice(ctx->device));
+  CK(launch_topk_softmax(scores_dev, T, ctx->d.E, ctx->d.k, topk_w_dev, topk_i_dev, static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int *offsets_dev, int *sorted_pair_ids_dev,
+                             void *stream) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  int rc = check_T(ctx, T);
+  if (rc) return rc;
+  if (!topk_i_dev || !offsets_dev || !sorted_pair_ids_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null pointer");
+  CK(cudaSetDevice(ctx->device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    CK(cudaMemsetAsync(offsets_dev, 0, (ctx->d.E + 1) * sizeof(int), s));
+    return GPTOSS_OK;
+  }
+  RouteBuffers rb = ctx->rb;  // block histograms/bases live in the context scratch; results go to the caller
+  rb.offsets = offsets_dev;
+  rb.sorted = sorted_pair_ids_dev;
+  CK(launch_pair_hist(topk_i_dev, T, ctx->d, rb.blk_hist, s));
+  CK(launch_expert_scan(rb, T, ctx->d, s));
+  CK(launch_scatter_gather(nullptr, topk_i_dev, T, ctx->d, rb.blk_base, rb.sorted, nullptr, s));
+  return GPTOSS_OK;
+}
+
+// ---- taps --------------------------------------------------------------------------------------------------------
+int gptoss_read_tap(gptoss_ctx *ctx, int tap, void *host_dst, uint64_t bytes) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (!host_dst) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null destination");
+  const size_t T = ctx->max_tokens, H = ctx->d.H, I = ctx->d.I, E = ctx->d.E, k = ctx->d.k, P = T * k;
+  const void *src = nullptr;
+  size_t cap = 0;
+  switch (tap) {
+    case GPTOSS_TAP_SCORES: src = ctx->rb.scores; cap = T * E * 4; break;
+    case GPTOSS_TAP_TOPK_W: src = ctx->rb.topk_w; cap = P * 4; break;
+    case GPTOSS_TAP_TOPK_I: src = ctx->rb.topk_i; cap = P * 4; break;
+    case GPTOSS_TAP_OFFSETS: src = ctx->rb.offsets; cap = (E + 1) * 4; break;
+    case GPTOSS_TAP_SORTED: src = ctx->rb.sorted; cap = P * 4; break;
+    case GPTOSS_TAP_X_PACKED: src = ctx->x_packed; cap = P * H * 2; break;
+    case GPTOSS_TAP_GATE_UP: src = ctx->gate_up; cap = P * I * 2; break;
+    case GPTOSS_TAP_Y_PAIRS: src = ctx->y_pairs; cap = P * H * 4; break;
+    default: return ctx->fail(GPTOSS_ERR_BAD_ARG, "unknown tap");
+  }
+  if (bytes > cap) return ctx->fail(GPTOSS_ERR_BAD_ARG, "tap read larger than the buffer");
+  CK(cudaSetDevice(ctx->device));
+  CK(cudaDeviceSynchronize());
+  CK(cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost));
+  return GPTOSS_OK;
+}
+
+int gptoss_synth_normal_bf16(void *dst_dev_bf16, uint64_t n, uint64_t seed, uint64_t tensor_id, uint64_t start,
+                             float sigma, void *stream) {
+  if (!dst_dev_bf16) return GPTOSS_ERR_BAD_ARG;
+  if (n == 0) return GPTOSS_OK;
+  cudaError_t e = launch_synth_normal(static_cast<__nv_bfloat16 *>(dst_dev_bf16), n, seed, tensor_id, start, sigma,
+                                      static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? GPTOSS_OK : GPTOSS_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,46 @@
+// Shared definitions of the gptoss_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gptoss_b200.h"
+
+namespace gptoss {
+
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 8;
+constexpr int kTokensPerRouteBlock = 8;  // one warp per token, 8 warps per block
+constexpr int kSmCountFallback = 148;
+
+// GEMM tiling (shared by host launch code and kernels)
+constexpr int kBlockK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
+constexpr int kTileF = 128;        // output features per accumulator tile (UMMA M)
+constexpr int kTokChunk = 64;      // token rows per TMA box of the activation operand
+constexpr int kMaxTileTokens = 256;  // token rows per tile (UMMA N max)
+
+// device status word layout (int[8] in global memory)
+//   [0] sticky error code (0 = ok)   [1] where (kernel id << 16 | site)   [2..3] detail
+constexpr int kStatusWords = 8;
+constexpr int kDevErrTimeout = 3;
+
+// Device scratch shared by the routing kernels and read by the GEMM kernels.
+struct RouteBuffers {
+  float *scores;        // [T,E]
+  float *topk_w;        // [T,k]
+  int *topk_i;          // [T,k]
+  int *blk_hist;        // [n_route_blocks, E]
+  int *blk_base;        // [n_route_blocks, E]   global start row of each block's pairs per expert
+  int *offsets;         // [E+1]
+  int *sorted;          // [T*k]
+  int *tb_prefix;       // [E_local+1]   cumulative count of token blocks (kMaxTileTokens rows) of local experts
+};
+
+struct Dims {
+  int H, I, E, k;
+  int e_begin, e_end;  // local experts
+  float limit;
+};
+
+}  // namespace gptoss

@@ -1,0 +1,67 @@
+// Host-callable launchers of the gptoss_b200 kernels (internal to the library).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace gptoss {
+
+// routing.cu
+cudaError_t launch_router_topk(const __nv_bfloat16 *t, const __nv_bfloat16 *wr, const float *br, int T,
+                               const Dims &d, const RouteBuffers &rb, cudaStream_t s);
+cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
+                                cudaStream_t s);
+cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s);
+cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, cudaStream_t s);
+cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int T, const Dims &d,
+                                  const int *blk_base, int *sorted, __nv_bfloat16 *x_packed,
+                                  cudaStream_t s);
+cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
+                           int residual, int sm_count, cudaStream_t s);
+
+// grouped_gemm.cu
+struct GemmArgs {
+  CUtensorMap map_w;    // weights: 3-D (k, feature, expert-slab), bf16, 128-byte swizzle, box {64,128,1}
+  CUtensorMap map_act;  // activations: 2-D (k, row), bf16, 128-byte swizzle, box {64,64}
+  const int *offsets;    // [E+1] global expert offsets
+  const int *tb_prefix;  // [E_local+1]
+  int e_begin, n_local;  // local expert range
+  int n_feat;            // output features per expert (I for mlp1, H for mlp2)
+  int n_feat_tiles;      // ceil(n_feat / 128)
+  int k_blocks;          // ceil(K / 64)
+  float limit;           // swiglu clamp (mlp1)
+  const float *bias_a;   // mlp1: gate bias [E_local, I];  mlp2: bias [E_local, H]
+  const float *bias_b;   // mlp1: up bias   [E_local, I];  mlp2: unused
+  __nv_bfloat16 *gate_up;  // mlp1 out [P, I]
+  float *y_pairs;          // mlp2 out [P, H] by pair id
+  const int *sorted;       // mlp2: [P]
+  const float *topk_w;     // mlp2: [P] by pair id
+  int *status;             // device status words
+};
+cudaError_t launch_grouped_mlp1(const GemmArgs &a, int sm_count, cudaStream_t s);
+cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s);
+// Encodes the two tensor maps (driver entry point resolved at run time; no link-time libcuda).
+// weights: base of [slabs][rows][K] bf16;  activations: base of [rows][K] bf16.
+cudaError_t encode_weight_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs);
+cudaError_t encode_act_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows);
+
+// convert.cu
+cudaError_t launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t s);
+cudaError_t launch_bf16_to_f32(const __nv_bfloat16 *src, float *dst, size_t n, cudaStream_t s);
+// mlp1 rows: checkpoint order (gate row 2c, up row 2c+1) <-> device order [2][I][K] per expert
+cudaError_t launch_mlp1_deinterleave(const float *src, __nv_bfloat16 *dst, int I, int K, cudaStream_t s);
+cudaError_t launch_mlp1_interleave(const __nv_bfloat16 *src, float *dst, int I, int K, cudaStream_t s);
+cudaError_t launch_bias_split(const float *src, float *g, float *u, size_t n_pairs, cudaStream_t s);
+cudaError_t launch_bias_merge(const float *g, const float *u, float *dst, size_t n_pairs, cudaStream_t s);
+cudaError_t launch_round_bf16_f32(const float *src, float *dst, size_t n, cudaStream_t s);
+cudaError_t launch_synth_normal(__nv_bfloat16 *dst, uint64_t n, uint64_t seed, uint64_t tensor_id,
+                                uint64_t start, float sigma, cudaStream_t s);
+// synthetic mlp1 slab for one expert directly in device order; `start` = checkpoint-order index of the
+// expert's first element
+cudaError_t launch_synth_mlp1(__nv_bfloat16 *dst, int I, int K, uint64_t seed, uint64_t tensor_id,
+                              uint64_t start, float sigma, cudaStream_t s);
+cudaError_t launch_synth_normal_f32(float *dst, uint64_t n, uint64_t seed, uint64_t tensor_id,
+                                    uint64_t start, float sigma, cudaStream_t s);
+
+}  // namespace gptoss

@@ -1,0 +1,452 @@
+// Routing side of the MoE block: router GEMM + top-k + softmax, expert histogram / prefix / stable
+// scatter (counting sort of pair ids), row gather, and the slot-ordered combine.
+//
+// Everything here is bandwidth/latency-bound integer and fp32 work: one warp per token, 16-byte
+// loads, warp shuffles, no global atomics, deterministic results (all ranks of an expert-parallel
+// group must derive bit-identical routing from the replicated activations).
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace gptoss {
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// vals[32] per lane  ->  lane l returns the sum over all lanes of vals[l]; fixed summation tree.
+__device__ __forceinline__ float warp_reduce_transpose32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (i < n / 2) {
+        const float send = upper ? v[i] : v[i + n / 2];
+        const float keep = upper ? v[i + n / 2] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+  }
+  return v[0];
+}
+
+// Top-k of E scores spread over the warp (position p = s*32 + lane holds val[s]) in the exact order
+// the reference kernel produces (layer_hip_batch.cpp:1119-1140): k rounds of "first maximum of
+// positions [i,E) under strict '>', swapped into position i" — the swap moves the displaced element
+// to the winner's old position, which decides later ties.  Then softmax over the selected raw
+// scores (layer_hip_batch.cpp:1143-1153).  Lanes j < k return (weight_j, id_j).
+template <int SLOTS>
+__device__ __forceinline__ void warp_topk_softmax(float (&val)[SLOTS], int E, int k, int lane,
+                                                  float &out_w, int &out_i) {
+  int idx[SLOTS];
+#pragma unroll
+  for (int s = 0; s < SLOTS; ++s) idx[s] = s * 32 + lane;
+
+  float sel_v[kMaxTopK];
+  int sel_i[kMaxTopK];
+#pragma unroll
+  for (int i = 0; i < kMaxTopK; ++i) {
+    sel_v[i] = 0.f;
+    sel_i[i] = -1;
+    if (i < k) {
+      // position i's current content (the initial max_idx of the round)
+      float vi = 0.f;
+      int ii = 0;
+#pragma unroll
+      for (int s = 0; s < SLOTS; ++s)
+        if (s == i / 32) {
+          vi = val[s];
+          ii = idx[s];
+        }
+      vi = __shfl_sync(0xffffffffu, vi, i & 31);
+      ii = __shfl_sync(0xffffffffu, ii, i & 31);
+
+      // best strictly-greater candidate among positions (i, E): lowest position among the maxima
+      float bv = vi;
+      int bp = i;
+#pragma unroll
+      for (int s = 0; s < SLOTS; ++s) {
+        const int p = s * 32 + lane;
+        if (p > i && p < E && (val[s] > bv)) {
+          bv = val[s];
+          bp = p;
+        }
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int op = __shfl_xor_sync(0xffffffffu, bp, off);
+        if (ov > bv || (ov == bv && op < bp)) {
+          bv = ov;
+          bp = op;
+        }
+      }
+      // id stored at the winning position
+      int bi = 0;
+#pragma unroll
+      for (int s = 0; s < SLOTS; ++s)
+        if (s == bp / 32) bi = idx[s];
+      bi = __shfl_sync(0xffffffffu, bi, bp & 31);
+
+      if (bp != i) {  // swap positions i and bp
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+          const int p = s * 32 + lane;
+          if (p == bp) {
+            val[s] = vi;
+            idx[s] = ii;
+          } else if (p == i) {
+            val[s] = bv;
+            idx[s] = bi;
+          }
+        }
+      }
+      sel_v[i] = bv;
+      sel_i[i] = bi;
+    }
+  }
+
+  const float mx = sel_v[0];
+  double denom = 0.0;
+#pragma unroll
+  for (int i = 0; i < kMaxTopK; ++i)
+    if (i < k) denom += (double)expf(sel_v[i] - mx);
+  out_w = 0.f;
+  out_i = -1;
+#pragma unroll
+  for (int i = 0; i < kMaxTopK; ++i)
+    if (i < k && lane == i) {
+      out_w = expf(sel_v[i] - mx) / (float)denom;
+      out_i = sel_i[i];
+    }
+}
+
+}  // namespace
+
+// ---- router GEMM + top-k + softmax + per-block expert histogram ------------------------------------
+// One warp per token.  scores[b,e] = sum_h t[b,h] * Wr[e,h] + br[e]  (fp32 accumulation).
+template <int GROUPS>
+__global__ void __launch_bounds__(256) router_topk_kernel(const __nv_bfloat16 *__restrict__ t,
+                                                          const __nv_bfloat16 *__restrict__ wr,
+                                                          const float *__restrict__ br, int T, Dims d,
+                                                          RouteBuffers rb) {
+  extern __shared__ uint4 smem_rows[];
+  __shared__ int hist[kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x * kTokensPerRouteBlock + warp;
+  const int nchunk = d.H >> 3;
+  for (int e = threadIdx.x; e < d.E; e += blockDim.x) hist[e] = 0;
+  uint4 *trow = smem_rows + (size_t)warp * nchunk;
+  if (b < T) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)b * d.H);
+    for (int c = lane; c < nchunk; c += 32) trow[c] = __ldg(src + c);
+  }
+  __syncthreads();
+
+  if (b < T) {
+    float score[GROUPS];
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      float acc[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+      for (int c = lane; c < nchunk; c += 32) {
+        float tf[8];
+        unpack8(trow[c], tf);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int eg = g * 32 + e;
+          if (eg < d.E) {
+            float wf[8];
+            unpack8(__ldg(reinterpret_cast<const uint4 *>(wr + (size_t)eg * d.H) + c), wf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e] = fmaf(tf[i], wf[i], acc[e]);
+          }
+        }
+      }
+      const float s = warp_reduce_transpose32(acc, lane);
+      const int eg = g * 32 + lane;
+      score[g] = (eg < d.E) ? s + br[eg] : -INFINITY;
+      if (eg < d.E) rb.scores[(size_t)b * d.E + eg] = score[g];
+    }
+    float w;
+    int id;
+    warp_topk_softmax<GROUPS>(score, d.E, d.k, lane, w, id);
+    if (lane < d.k) {
+      rb.topk_w[(size_t)b * d.k + lane] = w;
+      rb.topk_i[(size_t)b * d.k + lane] = id;
+      atomicAdd(&hist[id], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < d.E; e += blockDim.x) rb.blk_hist[(size_t)blockIdx.x * d.E + e] = hist[e];
+}
+
+// ---- stand-alone top-k + softmax on a score matrix ---------------------------------------------------
+template <int GROUPS>
+__global__ void __launch_bounds__(256) topk_softmax_kernel(const float *__restrict__ scores, int T, int E,
+                                                           int k, float *__restrict__ topk_w,
+                                                           int *__restrict__ topk_i) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x * kTokensPerRouteBlock + warp;
+  if (b >= T) return;
+  float score[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int eg = g * 32 + lane;
+    score[g] = (eg < E) ? scores[(size_t)b * E + eg] : -INFINITY;
+  }
+  float w;
+  int id;
+  warp_topk_softmax<GROUPS>(score, E, k, lane, w, id);
+  if (lane < k) {
+    topk_w[(size_t)b * k + lane] = w;
+    topk_i[(size_t)b * k + lane] = id;
+  }
+}
+
+// ---- per-block expert histogram of caller-supplied ids (stand-alone build_offsets) --------------------
+__global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ topk_i, int T, int k, int E,
+                                                        int *__restrict__ blk_hist) {
+  __shared__ int hist[kMaxExperts];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int first = blockIdx.x * kTokensPerRouteBlock * k;
+  const int n = min(kTokensPerRouteBlock, T - blockIdx.x * kTokensPerRouteBlock) * k;
+  for (int q = threadIdx.x; q < n; q += blockDim.x) {
+    const int e = topk_i[first + q];
+    if (0 <= e && e < E) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
+// ---- prefix sums: expert offsets, per-block bases, token-block prefix for the GEMM tile scheduler -----
+__global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d) {
+  __shared__ int seg_sum[1024];
+  __shared__ int off_s[kMaxExperts + 1];
+  const int E = d.E;
+  const int nseg = 1024 / E;
+  const int tid = threadIdx.x;
+  const int seg = tid / E, e = tid % E;
+  const bool active = seg < nseg;
+  const int per = (n_blocks + nseg - 1) / nseg;
+  const int b0 = min(n_blocks, seg * per), b1 = min(n_blocks, b0 + per);
+  if (active) {
+    int sum = 0;
+    for (int b = b0; b < b1; ++b) sum += rb.blk_hist[(size_t)b * E + e];
+    seg_sum[seg * E + e] = sum;
+  }
+  __syncthreads();
+  if (tid < E) {
+    int run = 0;
+    for (int s = 0; s < nseg; ++s) {
+      const int v = seg_sum[s * E + tid];
+      seg_sum[s * E + tid] = run;
+      run += v;
+    }
+    off_s[tid + 1] = run;  // count of expert tid
+  }
+  __syncthreads();
+  if (tid == 0) {
+    off_s[0] = 0;
+    for (int x = 0; x < E; ++x) off_s[x + 1] += off_s[x];
+    int tb = 0;
+    rb.tb_prefix[0] = 0;
+    for (int x = d.e_begin; x < d.e_end; ++x) {
+      tb += (off_s[x + 1] - off_s[x] + kMaxTileTokens - 1) / kMaxTileTokens;
+      rb.tb_prefix[x - d.e_begin + 1] = tb;
+    }
+  }
+  __syncthreads();
+  if (tid <= E) rb.offsets[tid] = off_s[tid];
+  if (active) {
+    int run = off_s[e] + seg_sum[seg * E + e];
+    for (int b = b0; b < b1; ++b) {
+      rb.blk_base[(size_t)b * E + e] = run;
+      run += rb.blk_hist[(size_t)b * E + e];
+    }
+  }
+}
+
+// ---- stable scatter of pair ids (+ optional gather of the token rows of local experts) ---------------
+__global__ void __launch_bounds__(256) scatter_gather_kernel(const __nv_bfloat16 *__restrict__ t,
+                                                             const int *__restrict__ topk_i, int T, Dims d,
+                                                             const int *__restrict__ blk_base,
+                                                             int *__restrict__ sorted,
+                                                             __nv_bfloat16 *__restrict__ x_packed) {
+  __shared__ int ids[kTokensPerRouteBlock * kMaxTopK];
+  __shared__ int pos_s[kTokensPerRouteBlock * kMaxTopK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k = d.k;
+  const int first = blockIdx.x * kTokensPerRouteBlock * k;
+  const int n = min(kTokensPerRouteBlock, T - blockIdx.x * kTokensPerRouteBlock) * k;
+  for (int q = threadIdx.x; q < kTokensPerRouteBlock * k; q += blockDim.x)
+    ids[q] = (q < n) ? topk_i[first + q] : -1;
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    const int q = threadIdx.x, e = ids[q];
+    int pos = -1;
+    if (0 <= e && e < d.E) {
+      int rank = 0;
+      for (int r = 0; r < q; ++r) rank += (ids[r] == e);
+      pos = blk_base[(size_t)blockIdx.x * d.E + e] + rank;
+      sorted[pos] = first + q;
+    }
+    pos_s[q] = pos;
+  }
+  __syncthreads();
+  const int b = blockIdx.x * kTokensPerRouteBlock + warp;
+  if (t != nullptr && b < T) {
+    const int nchunk = d.H >> 3;
+    const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)b * d.H);
+    uint4 *dst = reinterpret_cast<uint4 *>(x_packed);
+    int pos[kMaxTopK];
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      pos[j] = -1;
+      if (j < k) {
+        const int e = ids[warp * k + j];
+        if (e >= d.e_begin && e < d.e_end) pos[j] = pos_s[warp * k + j];
+      }
+    }
+    for (int c = lane; c < nchunk; c += 32) {
+      const uint4 v = __ldg(src + c);
+#pragma unroll
+      for (int j = 0; j < kMaxTopK; ++j)
+        if (pos[j] >= 0) dst[(size_t)pos[j] * nchunk + c] = v;
+    }
+  }
+}
+
+// ---- combine: x[b,:] (+)= sum over this rank's slots j = 0..k-1 (ascending) of y_pairs[b*k+j,:] --------
+__global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ y_pairs,
+                                                      const int *__restrict__ topk_i, int T, Dims d,
+                                                      float *__restrict__ x, int residual) {
+  const int h4 = d.H >> 2;
+  const size_t total = (size_t)T * h4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int b = (int)(i / h4), c = (int)(i % h4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool first = true;
+    for (int j = 0; j < d.k; ++j) {
+      const int e = topk_i[(size_t)b * d.k + j];
+      if (e >= d.e_begin && e < d.e_end) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(y_pairs) + ((size_t)b * d.k + j) * h4 + c);
+        if (first) {
+          acc = v;
+          first = false;
+        } else {
+          acc.x += v.x;
+          acc.y += v.y;
+          acc.z += v.z;
+          acc.w += v.w;
+        }
+      }
+    }
+    float4 *xp = reinterpret_cast<float4 *>(x) + i;
+    if (residual) {
+      float4 o = *xp;
+      o.x += acc.x;
+      o.y += acc.y;
+      o.z += acc.z;
+      o.w += acc.w;
+      *xp = o;
+    } else {
+      *xp = acc;
+    }
+  }
+}
+
+// ---- launchers -------------------------------------------------------------------------------------------
+static inline int route_blocks(int T) { return (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock; }
+
+cudaError_t launch_router_topk(const __nv_bfloat16 *t, const __nv_bfloat16 *wr, const float *br, int T,
+                               const Dims &d, const RouteBuffers &rb, cudaStream_t s) {
+  const int groups = (d.E + 31) / 32;
+  const size_t smem = (size_t)kTokensPerRouteBlock * d.H * sizeof(__nv_bfloat16);
+  const dim3 grid(route_blocks(T)), block(256);
+#define GPTOSS_ROUTER_CASE(G)                                                                          \
+  case G: {                                                                                            \
+    cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                   \
+    if (e != cudaSuccess) return e;                                                                    \
+    router_topk_kernel<G><<<grid, block, smem, s>>>(t, wr, br, T, d, rb);                              \
+    break;                                                                                             \
+  }
+  switch (groups) {
+    GPTOSS_ROUTER_CASE(1)
+    GPTOSS_ROUTER_CASE(2)
+    GPTOSS_ROUTER_CASE(3)
+    GPTOSS_ROUTER_CASE(4)
+    GPTOSS_ROUTER_CASE(5)
+    GPTOSS_ROUTER_CASE(6)
+    GPTOSS_ROUTER_CASE(7)
+    GPTOSS_ROUTER_CASE(8)
+    default:
+      return cudaErrorInvalidValue;
+  }
+#undef GPTOSS_ROUTER_CASE
+  return cudaGetLastError();
+}
+
+cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
+                                cudaStream_t s) {
+  const int groups = (E + 31) / 32;
+  const dim3 grid(route_blocks(T)), block(256);
+#define GPTOSS_TOPK_CASE(G)                                                   \
+  case G:                                                                     \
+    topk_softmax_kernel<G><<<grid, block, 0, s>>>(scores, T, E, k, topk_w, topk_i); \
+    break;
+  switch (groups) {
+    GPTOSS_TOPK_CASE(1)
+    GPTOSS_TOPK_CASE(2)
+    GPTOSS_TOPK_CASE(3)
+    GPTOSS_TOPK_CASE(4)
+    GPTOSS_TOPK_CASE(5)
+    GPTOSS_TOPK_CASE(6)
+    GPTOSS_TOPK_CASE(7)
+    GPTOSS_TOPK_CASE(8)
+    default:
+      return cudaErrorInvalidValue;
+  }
+#undef GPTOSS_TOPK_CASE
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s) {
+  pair_hist_kernel<<<route_blocks(T), 256, 0, s>>>(topk_i, T, d.k, d.E, blk_hist);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, cudaStream_t s) {
+  expert_scan_kernel<<<1, 1024, 0, s>>>(rb, route_blocks(T), d);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int T, const Dims &d,
+                                  const int *blk_base, int *sorted, __nv_bfloat16 *x_packed,
+                                  cudaStream_t s) {
+  scatter_gather_kernel<<<route_blocks(T), 256, 0, s>>>(t, topk_i, T, d, blk_base, sorted, x_packed);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
+                           int residual, int sm_count, cudaStream_t s) {
+  const size_t total = (size_t)T * (d.H >> 2);
+  int blocks = (int)((total + 255) / 256);
+  const int cap = sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  combine_kernel<<<blocks, 256, 0, s>>>(y_pairs, topk_i, T, d, x, residual);
+  return cudaGetLastError();
+}
+
+}  // namespace gptoss

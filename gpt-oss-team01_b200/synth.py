@@ -11,7 +11,7 @@ Element ``i`` of tensor ``tensor_id``:
     key = splitmix64(seed * 0x100000001B3 + tensor_id)
     a, b = splitmix64(key + 2 i), splitmix64(key + 2 i + 1)
     S   = sum of the eight 16-bit fields of a and b            (Irwin-Hall, n = 8)
-    z   = fp32(S - 262140) * fp32(sigma / 53510.1067...)       (approximately N(0, sigma))
+    z   = fp32(S - 262140) * fp32(fp32(sigma) / 53509.9199...) (approximately N(0, sigma))
     val = bf16_round_nearest_even(z)
 
 The tails stop at +-4.9 sigma; for the N(0, 0.02) weights and N(0, 1) activations used by the
@@ -58,8 +58,9 @@ def stream_key(seed: int, tid: int) -> np.uint64:
 
 
 def scale_f32(sigma: float) -> np.float32:
-    """The fp32 constant both implementations multiply by."""
-    return np.float32(sigma / IH_STD)
+    """The fp32 constant both implementations multiply by (sigma is first rounded to fp32, because
+    it crosses the C ABI as a float)."""
+    return np.float32(float(np.float32(sigma)) / IH_STD)
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

@@ -1,0 +1,156 @@
+/*
+ * gptoss_b200 — C ABI of the B200-native GPT-OSS MoE FFN block.
+ *
+ * This is the boundary a C++ host (the replacement for the reference's getp-csrc/getp_run.cpp and
+ * src/model.cpp) binds to.  Plain pointers and sizes only; every call returns an int status
+ * (GPTOSS_OK == 0), nothing aborts and no exception crosses the boundary — unlike the reference's
+ * launchers, which return void and abort through CHECK_HIP (getp-csrc/include/tensor.hpp:20-27).
+ *
+ * One context per GPU (one host thread or one process per GPU, the reference's threading model,
+ * getp-csrc/submit/getp_run_submit.cpp:106-178).  The context owns all scratch, pre-allocated for
+ * `max_tokens` like the reference's run state (getp-csrc/submit/alloc_submit.cpp:882-1014); the caller
+ * owns the activations `t` and the residual stream `x`.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to the reference
+ * project root).
+ */
+#ifndef GPTOSS_B200_H
+#define GPTOSS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---------------------------------------------------------------------------- */
+#define GPTOSS_OK 0
+#define GPTOSS_ERR_BAD_ARG 1     /* null pointer, size out of range, unsupported dimension          */
+#define GPTOSS_ERR_CUDA 2        /* a CUDA runtime/driver call failed; see gptoss_last_error()       */
+#define GPTOSS_ERR_TIMEOUT 3     /* a bounded device-side wait (mbarrier / peer flag) gave up        */
+#define GPTOSS_ERR_UNSUPPORTED 4 /* device is not compute capability 10.x                            */
+#define GPTOSS_ERR_STATE 5       /* call out of order (e.g. forward before the layer has weights)    */
+
+/* wire format of the cross-GPU combine payload */
+#define GPTOSS_WIRE_F32 0
+#define GPTOSS_WIRE_BF16 1
+
+/* Dimensions of the MoE block; the subset of the checkpoint header (run.cpp:25-45) the block uses. */
+typedef struct {
+  int hidden;         /* hidden_dim        H                      */
+  int intermediate;   /* intermediate_dim  I                      */
+  int n_experts;      /* n_experts         E   (<= 256)           */
+  int top_k;          /* experts_per_token k   (<= 8)             */
+  int n_layers;       /* number of layer slots to hold weights for */
+  float swiglu_limit; /* swiglu_limit (7.0)                       */
+} gptoss_moe_dims;
+
+typedef struct gptoss_ctx gptoss_ctx;
+
+/* ---- life cycle --------------------------------------------------------------------------------
+ * Replaces the MoE part of our_init / our_free (getp-csrc/src/alloc.cpp:1035,1192) and of
+ * our_init_run_state_* (getp-csrc/submit/alloc_submit.cpp:882-1014).
+ * rank/world: this GPU owns experts [rank*E/world, (rank+1)*E/world), the reference's contiguous
+ * expert partition (getp-csrc/src/parallelism.cpp:1852-1855).  world == 1: no sharding. */
+int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int world, int max_tokens,
+                      int wire_dtype, gptoss_ctx **out);
+int gptoss_ctx_destroy(gptoss_ctx *ctx);
+/* Message of the last failing call on this context (never NULL; "" if none). */
+const char *gptoss_last_error(const gptoss_ctx *ctx);
+/* Synchronises the context's device and reports a sticky device-side error word:
+ * GPTOSS_OK, or GPTOSS_ERR_TIMEOUT if any kernel gave up on a bounded wait since the last call. */
+int gptoss_ctx_status(gptoss_ctx *ctx);
+
+/* ---- weights -----------------------------------------------------------------------------------
+ * Takes one layer's tensors in the flat checkpoint layouts AS THEY ARE (host fp32; run.cpp:66-76,
+ * 194-233): router_w [E,H], router_b [E], mlp1_w [E,2I,H] (gate rows even, up rows odd),
+ * mlp1_b [E,2I], mlp2_w [E,H,I], mlp2_b [E,H]; converts to bf16 and keeps this rank's experts.
+ * Replaces the host transposes + copies of getp-csrc/src/alloc.cpp:77-181 and the expert slicing of
+ * getp-csrc/submit/alloc_submit.cpp:555-598,744-832. */
+int gptoss_upload_layer(gptoss_ctx *ctx, int layer, const float *router_w, const float *router_b,
+                        const float *mlp1_w, const float *mlp1_b, const float *mlp2_w,
+                        const float *mlp2_b);
+/* Fills one layer with the seeded synthetic tensors (N(0,sigma) rounded to bf16) directly on the
+ * device; bit-identical to uploading the host generator's tensors.  No reference counterpart
+ * (real checkpoints are loaded through gptoss_upload_layer). */
+int gptoss_fill_layer_synthetic(gptoss_ctx *ctx, int layer, uint64_t seed, float sigma);
+/* Replaces the router bias of a layer (host fp32 [E]); used for the skewed-routing workload. */
+int gptoss_set_router_bias(gptoss_ctx *ctx, int layer, const float *router_b);
+/* Reads this rank's experts of one layer back in the checkpoint layouts (host fp32; any pointer may
+ * be NULL): router_w [E,H], router_b [E], mlp1_w [E_local,2I,H], mlp1_b [E_local,2I],
+ * mlp2_w [E_local,H,I], mlp2_b [E_local,H].  Test/debug aid (the reference has Tensor::from_device,
+ * getp-csrc/src/tensor.cpp:207-210). */
+int gptoss_download_layer(gptoss_ctx *ctx, int layer, float *router_w, float *router_b, float *mlp1_w,
+                          float *mlp1_b, float *mlp2_w, float *mlp2_b);
+
+/* ---- the per-layer operator ----------------------------------------------------------------------
+ * x[T,H] (fp32, device, in/out) += MoE(t[T,H]) (bf16, device).  Replaces the sequence
+ * getp-csrc/src/model.cpp:300-445 (120B) / :73-132 (20B): router_gemm_v2, topk_softmax_batched,
+ * moe_init_buffers_hip, moe_build_offsets_hip, moe_pack_inputs_hip, moe_build_local_ep_data,
+ * moe_get_max_rows_per_expert_hip, moe_mlp1_swiglu_fused_hip, moe_mlp2_forward_hip,
+ * moe_scatter_aggregate_ep_hip, tensor_quantize_fp8 + ring_reduce_agg_quantize_fp8 +
+ * tensor_dequantize_fp8, add_vector_batched.  Asynchronous on `stream` (a cudaStream_t, may be
+ * NULL for the default stream); no host round trip inside.  With world > 1 and peers attached the
+ * cross-GPU combine runs inside; with world > 1 and no peers use gptoss_moe_forward_partial. */
+int gptoss_moe_forward(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, float *x_dev,
+                       void *stream);
+/* Same with HOST buffers (t: bf16 bits [T,H]; x: fp32 [T,H] in/out): copies in, runs, copies out,
+ * synchronises, and returns the device status.  Pinned host memory makes the copies asynchronous. */
+int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host);
+/* Expert-parallel partial: partial[T,H] (fp32, device, overwritten) = sum over THIS rank's experts
+ * of gate_weight * expert(t) — the tensor the reference all-reduces (rs_now->e_agg,
+ * getp-csrc/src/model.cpp:411-423).  The caller reduces it across ranks and adds it to x. */
+int gptoss_moe_forward_partial(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16,
+                               float *partial_dev, void *stream);
+
+/* ---- stages of the operator (same order as inside gptoss_moe_forward) ------------------------------
+ * They work on the context's scratch so that a test can stop after any stage and read the taps. */
+/* router_gemm_v2 + topk_softmax_batched + moe_build_offsets_hip + moe_pack_inputs_hip
+ * (getp-csrc/src/layer_hip_batch.cpp:1046,1157; getp-csrc/src/kernel.cpp:851,867) */
+int gptoss_moe_route(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream);
+/* moe_mlp1_swiglu_fused_hip (getp-csrc/src/kernel.cpp:1033; kernel matrix_core.cpp:1448) */
+int gptoss_moe_mlp1_swiglu(gptoss_ctx *ctx, int layer, void *stream);
+/* moe_mlp2_forward_hip (getp-csrc/src/kernel.cpp:1061,1094) with the gate weight applied in the
+ * epilogue (moe_agg_kernel_120b's multiply, getp-csrc/src/kernel.cpp:764-767) */
+int gptoss_moe_mlp2(gptoss_ctx *ctx, int layer, void *stream);
+/* moe_scatter_aggregate_ep_hip + add_vector_batched (getp-csrc/src/layer_hip_batch.cpp:1344,856):
+ * residual != 0: x += sum of slots;  residual == 0: x = sum of this rank's slots. */
+int gptoss_moe_combine(gptoss_ctx *ctx, int T, float *x_dev, int residual, void *stream);
+
+/* ---- stand-alone routing operators on caller-supplied device buffers ------------------------------ */
+/* topk_softmax_batched (getp-csrc/src/layer_hip_batch.cpp:1157, kernel :1087): scores [T,E] fp32 ->
+ * topk_w [T,k] fp32 (softmax over the selected raw scores), topk_i [T,k] int32, descending, with
+ * the reference kernel's tie rule (selection sort with swap, strict '>'). */
+int gptoss_topk_softmax(gptoss_ctx *ctx, int T, const float *scores_dev, float *topk_w_dev,
+                        int *topk_i_dev, void *stream);
+/* moe_build_offsets (getp-csrc/src/kernel.cpp:851, kernel :504): topk_i [T*k] -> offsets [E+1],
+ * sorted_pair_ids [T*k] (pair id = token*k + slot), stable within an expert; ids outside [0,E) are
+ * skipped and the tail of sorted_pair_ids beyond offsets[E] is left untouched. */
+int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int *offsets_dev,
+                             int *sorted_pair_ids_dev, void *stream);
+
+/* ---- taps (debug/parity; the reference's DEBUG printDebug, getp-csrc/src/model.cpp:205-450) -------- */
+#define GPTOSS_TAP_SCORES 0    /* fp32 [T,E]   router scores incl. bias                            */
+#define GPTOSS_TAP_TOPK_W 1    /* fp32 [T,k]   gate weights                                        */
+#define GPTOSS_TAP_TOPK_I 2    /* int32 [T,k]  expert ids                                          */
+#define GPTOSS_TAP_OFFSETS 3   /* int32 [E+1]  expert_offsets                                      */
+#define GPTOSS_TAP_SORTED 4    /* int32 [T*k]  sorted_pair_ids                                     */
+#define GPTOSS_TAP_X_PACKED 5  /* bf16 [T*k,H] gathered inputs (rows of this rank's experts only)  */
+#define GPTOSS_TAP_GATE_UP 6   /* bf16 [T*k,I] SwiGLU output, rows in sorted order                 */
+#define GPTOSS_TAP_Y_PAIRS 7   /* fp32 [T*k,H] gate_weight * expert output, rows by PAIR id        */
+/* Copies `bytes` from the start of the tap to host memory after synchronising the device. */
+int gptoss_read_tap(gptoss_ctx *ctx, int tap, void *host_dst, uint64_t bytes);
+
+/* ---- synthetic data ------------------------------------------------------------------------------
+ * dst_dev_bf16[i] = bf16(N(0,sigma)) for stream (seed, tensor_id), elements [start, start+n);
+ * the generator is specified in the Python module `synth` and reproduced bit for bit. */
+int gptoss_synth_normal_bf16(void *dst_dev_bf16, uint64_t n, uint64_t seed, uint64_t tensor_id,
+                             uint64_t start, float sigma, void *stream);
+
+/* Library build info: "gptoss_b200 <version> sm_100a". */
+const char *gptoss_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
