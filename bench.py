@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE FFN block (one gpt-oss-20b layer call per step).
+
+    python bench.py --gpus N --steps K --warmup W                  our arm (CUDA, through the C ABI)
+    python bench.py --impl reference --gpus N --steps K --warmup W the reference's CPU path on the host
+
+A step is one pass of the block over one batch of synthetic tokens.  N = 1: hidden 2880, 32 experts,
+top-4, T = 1024 tokens (the single-GPU configuration the headline metric is quoted on).  N > 1 (one
+process per GPU under torchrun): the same layer with its experts sharded E/N per GPU and T = 1024*N
+replicated tokens, partial outputs summed with an NCCL all-reduce — per-GPU work is fixed, so the
+scaling is weak.  Weights rotate over several distinct layers (each 1.6 GB >> the 126 MB L2), so
+every step streams its weights from HBM.
+
+Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` goes through the
+host-buffer entry point with pinned host memory (H2D + block + D2H inside the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+entry.load_package()
+from gptoss_b200 import synth  # noqa: E402
+
+H = I = 2880
+E, K_TOP = 32, 4
+TOKENS_PER_GPU = 1024
+SEED = 2024
+SIGMA = 0.02
+N_WEIGHT_SETS = 4  # distinct layers the steps rotate over
+FLOP_PER_TOKEN = 2 * H * E + 2 * K_TOP * H * (2 * I) + 2 * K_TOP * I * H  # 199,249,920
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM kernel at this workload,
+# from the ncu capture summarised in profiles/ (None until captured).
+NCU_TRAFFIC_MLP1_BYTES = None
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], d.get("bf16_tflops_sustained", d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows if len(r) >= 6)]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def to_bf16_bits(x):
+    return synth.f32_to_bf16_bits(x).reshape(x.shape)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# reference / CPU arm
+# ----------------------------------------------------------------------------------------------------------
+def host_weights():
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle_lib
+    return oracle_lib, oracle_lib.oracle().layer_weights(H, I, E, SEED, layer=0, sigma=SIGMA)
+
+
+def cpu_arm(T, target_seconds, repeats, warmup):
+    """Times the reference's CPU implementation of the block (its own matmul/topk/softmax from run.cpp,
+    compiled into oracle/_ref) on a bounded sample of the workload's token rows; falls back to the C
+    port when the reference object is absent.  Returns (tok/s, info, per-repeat seconds)."""
+    oracle_lib, w = host_weights()
+    t = synth.activations(SEED, T, H)
+    ref = oracle_lib.reference()
+    if ref is not None:
+        kind, cores = "reference", ref.num_threads()
+        run = lambda n: ref.moe_rows(t, w, K_TOP, rows=(0, n))  # noqa: E731
+    else:
+        ora = oracle_lib.oracle()
+        kind, cores = "port", ora.num_threads()
+
+        def run(n):
+            sc = ora.router_scores(t[:n], w.router_w, w.router_b)
+            tw, ti, _, _ = ora.topk_softmax(sc, K_TOP, oracle_lib.RULE_QSORT)
+            ora.moe_block(np.ascontiguousarray(t[:n]), tw, ti, w, mode=oracle_lib.MODE_CPU)
+    run(8)  # first touch of the weights (page faults) is not representative
+    t0 = time.perf_counter()
+    run(8)
+    per_row = (time.perf_counter() - t0) / 8
+    rows = int(max(8, min(T, target_seconds / max(per_row, 1e-9))))
+    for _ in range(warmup):
+        run(min(rows, 16))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        run(rows)
+        times.append(time.perf_counter() - t0)
+    tok_s = rows * len(times) / sum(times)
+    info = {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": kind,
+            "sample": f"first {rows} of {T} token rows of the same seeded layer-0 workload, "
+                      f"{len(times)} timed pass(es)"}
+    return tok_s, info, times
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T = TOKENS_PER_GPU * args.gpus
+    tok_s, info, times = cpu_arm(T, target_seconds=6.0, repeats=max(1, args.steps), warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": "batched decode tok/s, gpt-oss-20b MoE FFN block (one layer call per step)",
+        "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (double accumulate)", "data": "synthetic",
+        "config": workload_config(args.gpus, T), "cpu_baseline": info,
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus, T):
+    return {"workload": f"gpt-oss-20b MoE layer: T={T} tokens N(0,1) bf16, hidden {H}, {E} experts "
+                        f"(gate_up {2 * I}x{H}, down {H}x{I}) N(0,0.02) bf16, top-{K_TOP} softmax, SwiGLU alpha 1.702 "
+                        f"clamp 7.0; experts sharded {E // n_gpus} per GPU" if n_gpus > 1 else
+                        f"gpt-oss-20b MoE layer: T={T} tokens N(0,1) bf16, hidden {H}, {E} experts "
+                        f"(gate_up {2 * I}x{H}, down {H}x{I}) N(0,0.02) bf16, top-{K_TOP} softmax, SwiGLU alpha 1.702 "
+                        f"clamp 7.0",
+            "tokens_per_step": T, "parallelism": f"ep{n_gpus}" if n_gpus > 1 else "single",
+            "l2": f"weights rotate over {N_WEIGHT_SETS} layers of 1.59 GB each (inputs larger than the 126 MB L2)",
+            "seed": SEED}
+
+
+# ----------------------------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from gptoss_b200 import moe
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    T = TOKENS_PER_GPU * world
+    K, W = args.steps, max(args.warmup, 3)
+
+    global N_WEIGHT_SETS
+    N_WEIGHT_SETS = args.weight_sets
+    blk = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=K_TOP, n_layers=N_WEIGHT_SETS,
+                       device=local_rank, rank=rank, world=world, max_tokens=T)
+    for layer in range(N_WEIGHT_SETS):
+        blk.fill_layer_synthetic(layer, SEED, SIGMA)
+    t_dev = moe.synth_normal_bf16(T * H, SEED, synth.tensor_id(synth.TID_ACTIVATION), 1.0).view(T, H)
+    x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    partial = torch.empty_like(x) if world > 1 else None
+
+    def step(i):
+        layer = i % N_WEIGHT_SETS
+        if world == 1:
+            blk.forward(layer, t_dev, x)
+        else:
+            blk.forward_partial(layer, t_dev, partial)
+            dist.all_reduce(partial)
+            x.add_(partial)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(W):
+        step(i)
+    barrier()
+    blk.status()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        ev0.record()
+        for i in range(K):
+            step(i)
+        ev1.record()
+        barrier()
+    blk.status()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        tms = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    value = T * K / (ms * 1e-3)
+
+    # per-stage device time (same steps, events between the stages), for the roofline of the top kernel
+    names = ["route", "mlp1_swiglu", "mlp2", "combine"]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
+    out = partial if world > 1 else x
+    for i in range(K):
+        layer = i % N_WEIGHT_SETS
+        evs[i][0].record()
+        blk.route(layer, t_dev)
+        evs[i][1].record()
+        blk.mlp1_swiglu(layer)
+        evs[i][2].record()
+        blk.mlp2(layer)
+        evs[i][3].record()
+        blk.combine(out, residual=(world == 1))
+        evs[i][4].record()
+    torch.cuda.synchronize()
+    blk.status()
+    stage_ms = {n: sum(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(K)) / K for j, n in enumerate(names)}
+
+    hbm_peak, tf_burst, tf_sust, peak_kind = measured_peaks()
+    n_local = E // world
+    pairs_local = T * K_TOP // world  # expected rows of this rank's experts under uniform routing
+    mlp1_bytes = n_local * (2 * I * H * 2 + 2 * I * 4) + pairs_local * H * 2 + pairs_local * I * 2
+    mlp1_flops = 2 * pairs_local * H * 2 * I
+    mlp1_s = stage_ms["mlp1_swiglu"] * 1e-3
+    hbm_t, tc_t = mlp1_bytes / (hbm_peak * 1e9), mlp1_flops / (tf_burst * 1e12)
+    if hbm_t >= tc_t:
+        roof = {"bound": "hbm", "achieved": mlp1_bytes / mlp1_s / 1e9, "peak": hbm_peak, "unit": "GB/s"}
+    else:
+        roof = {"bound": "tensor", "achieved": mlp1_flops / mlp1_s / 1e12, "peak": tf_burst, "unit": "TFLOP/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = NCU_TRAFFIC_MLP1_BYTES
+    roof.update({"kernel": "grouped_gemm_kernel<2> (gate/up GEMM + SwiGLU)", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)",
+                 "algorithmic_bytes_per_launch": mlp1_bytes, "algorithmic_flops_per_launch": mlp1_flops,
+                 "avg_launch_ms": stage_ms["mlp1_swiglu"], "tensor_frac_of_burst": mlp1_flops / mlp1_s / 1e12 / tf_burst})
+    block_bytes = n_local * 3 * H * I * 2 + n_local * (2 * I + H) * 2 + (H * E + E) * 2 + T * H * 2 + T * H * 8
+    block_flops = FLOP_PER_TOKEN * T / world
+    block_roof_s = max(block_bytes / (hbm_peak * 1e9), block_flops / (tf_sust * 1e12))
+
+    line = {
+        "metric": "batched decode tok/s, gpt-oss-20b MoE FFN block (one layer call per step)",
+        "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "data": "synthetic", "config": workload_config(world, T), "roofline": roof,
+        "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
+                           "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
+                           "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
+        "stage_ms": stage_ms, "gpu_launches": 6 * K,
+    }
+
+    if rank == 0:
+        cs = clocks.summary()
+        line["clocks"] = cs
+
+    # end to end through the host-buffer entry point (single GPU: the C ABI call a host program makes)
+    if args.no_e2e:
+        pass
+    elif world == 1:
+        t_host = torch.empty((T, H), dtype=torch.int16).pin_memory()
+        t_host.copy_(t_dev.view(torch.int16).cpu())
+        x_host = torch.zeros((T, H), dtype=torch.float32).pin_memory()
+        for i in range(3):
+            blk.forward_host(i % N_WEIGHT_SETS, t_host, x_host)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(K):
+            blk.forward_host(i % N_WEIGHT_SETS, t_host, x_host)
+        e2e_s = time.perf_counter() - t0
+        line["e2e"] = {"value": T * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": T * H * 2 + T * H * 4,
+                       "d2h_bytes_per_step": T * H * 4, "ms_per_step": 1e3 * e2e_s / K}
+    else:
+        # each rank copies its inputs in from pinned memory, runs the sharded block + all-reduce, and copies x out
+        t_host = torch.empty((T, H), dtype=torch.int16).pin_memory()
+        t_host.copy_(t_dev.view(torch.int16).cpu())
+        x_host = torch.zeros((T, H), dtype=torch.float32).pin_memory()
+
+        def e2e_step(i):
+            t_dev.view(torch.int16).copy_(t_host, non_blocking=True)
+            x.copy_(x_host, non_blocking=True)
+            step(i)
+            x_host.copy_(x, non_blocking=True)
+            torch.cuda.synchronize()
+
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(K):
+            e2e_step(i)
+        barrier()
+        e2e_s = torch.tensor([time.perf_counter() - t0], device="cuda")
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+        line["e2e"] = {"value": T * K / float(e2e_s.item()), "unit": "tok/s",
+                       "h2d_bytes_per_step": T * H * 2 + T * H * 4, "d2h_bytes_per_step": T * H * 4,
+                       "ms_per_step": 1e3 * float(e2e_s.item()) / K}
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        _, info, _ = cpu_arm(T, target_seconds=12.0, repeats=1, warmup=0)
+        line["cpu_baseline"] = info
+    blk.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
+                    help="distinct layers of weights the steps rotate over (1 keeps a profiling run small)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -455,8 +455,8 @@ int gptoss_topk_softmax(gptoss_ctx *ctx, int T, const float *scores_dev, float *
                         void *stream) {
   if (!ctx) return GPTOSS_ERR_BAD_ARG;
   if (T < 0) return ctx->fail(GPTOSS_ERR_BAD_ARG, "negative T");
+  if (T == 0) return GPTOSS_OK;  // empty batch: nothing to read or write, pointers may be null
   if (!scores_dev || !topk_w_dev || !topk_i_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null pointer");
-  if (T == 0) return GPTOSS_OK;
   CK(cudaSetDevice(ctx->device));
   CK(launch_topk_softmax(scores_dev, T, ctx->d.E, ctx->d.k, topk_w_dev, topk_i_dev, static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
@@ -467,10 +467,11 @@ int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int 
   if (!ctx) return GPTOSS_ERR_BAD_ARG;
   int rc = check_T(ctx, T);
   if (rc) return rc;
-  if (!topk_i_dev || !offsets_dev || !sorted_pair_ids_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null pointer");
+  if (!offsets_dev || (T > 0 && (!topk_i_dev || !sorted_pair_ids_dev)))
+    return ctx->fail(GPTOSS_ERR_BAD_ARG, "null pointer");
   CK(cudaSetDevice(ctx->device));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (T == 0) {
+  if (T == 0) {  // empty batch: all offsets are zero, nothing else is touched
     CK(cudaMemsetAsync(offsets_dev, 0, (ctx->d.E + 1) * sizeof(int), s));
     return GPTOSS_OK;
   }

@@ -395,3 +395,26 @@ void oracle_combine_slots(const float *y_pairs, const float *topk_w, int T, int 
       out[(long long)b * H + i] = acc;
     }
 }
+
+/* ---- seeded synthetic tensors (same stream definition as the Python module `synth`) ------------- */
+static inline uint64_t splitmix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+void oracle_synth_normal_f32(uint64_t seed, uint64_t tensor_id, uint64_t start, uint64_t n, float sigma,
+                             float *out) {
+  const uint64_t key = splitmix64(seed * 0x100000001B3ull + tensor_id);
+  const float scale = (float)((double)sigma / 53509.91992145008); /* sqrt(8 (65536^2 - 1) / 12) */
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; ++i) {
+    const uint64_t a = splitmix64(key + 2ull * (start + (uint64_t)i));
+    const uint64_t b = splitmix64(key + 2ull * (start + (uint64_t)i) + 1ull);
+    int s = 0;
+    for (int sh = 0; sh < 64; sh += 16) s += (int)((a >> sh) & 0xFFFFull) + (int)((b >> sh) & 0xFFFFull);
+    const float z = (float)(s - 4 * 65535) * scale;
+    out[i] = oracle_bf16_to_f32(oracle_f32_to_bf16(z));
+  }
+}

@@ -92,6 +92,11 @@ void oracle_moe_forward(const oracle_dims *d, int mode, int rule, const float *t
  * order); provided so tests can bound that difference separately. */
 void oracle_combine_slots(const float *y_pairs, const float *topk_w, int T, int k, int H, float *out);
 
+/* out[i] = element start+i of the seeded stream (seed, tensor_id): N(0,sigma) rounded to bf16, as fp32.
+ * Same bits as the Python module `synth` and the CUDA generator; multithreaded. */
+void oracle_synth_normal_f32(uint64_t seed, uint64_t tensor_id, uint64_t start, uint64_t n, float sigma,
+                             float *out);
+
 int oracle_num_threads(void);
 
 #ifdef __cplusplus

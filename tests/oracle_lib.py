@@ -56,6 +56,8 @@ class Oracle:
                                          C.c_void_p]
         lib.oracle_combine_slots.argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int, _f32p]
         lib.oracle_num_threads.restype = C.c_int
+        lib.oracle_synth_normal_f32.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float,
+                                                _f32p]
 
     def router_scores(self, t, wr, br):
         T, H = t.shape
@@ -112,6 +114,23 @@ class Oracle:
 
     def num_threads(self):
         return self.lib.oracle_num_threads()
+
+    def synth_normal(self, seed, tensor_id, shape, sigma, start=0):
+        out = np.empty(shape, np.float32)
+        self.lib.oracle_synth_normal_f32(seed, tensor_id, start, out.size, sigma, out.reshape(-1))
+        return out
+
+    def layer_weights(self, H, I, E, seed, layer=0, sigma=0.02):
+        """Same tensors as synth.MoELayerWeights, generated by the multithreaded C generator."""
+        from types import SimpleNamespace
+        tid = lambda kind: kind + 16 * layer  # noqa: E731
+        return SimpleNamespace(
+            router_w=self.synth_normal(seed, tid(2), (E, H), sigma),
+            router_b=self.synth_normal(seed, tid(3), (E,), sigma),
+            mlp1_w=self.synth_normal(seed, tid(4), (E, 2 * I, H), sigma),
+            mlp1_b=self.synth_normal(seed, tid(5), (E, 2 * I), sigma),
+            mlp2_w=self.synth_normal(seed, tid(6), (E, H, I), sigma),
+            mlp2_b=self.synth_normal(seed, tid(7), (E, H), sigma))
 
 
 class Reference:

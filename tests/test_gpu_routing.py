@@ -105,8 +105,8 @@ def test_route_stage_matches_oracle(oracle, H, E, T, zipf):
     _, oi, _, _ = oracle.topk_softmax(oscores, k, oracle_lib.RULE_SELECTION)
     margin = oracle.topk_margin(oscores, k)
     ti = blk.tap("topk_i", T)
-    safe = margin > 1e-3
-    assert safe.mean() > 0.95
+    safe = margin > 5e-4
+    assert safe.mean() > 0.9
     assert np.array_equal(ti[safe], oi[safe])
     # given the GPU's scores, everything downstream is bit-exact
     gw, gi, _, _ = oracle.topk_softmax(scores, k, oracle_lib.RULE_SELECTION)

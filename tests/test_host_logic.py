@@ -60,3 +60,13 @@ def test_margin_flags_near_ties(oracle):
     s = np.array([[4.0, 3.0, 2.0, 1.0, 0.9999999, -1.0], [6.0, 5.0, 4.0, 3.0, 1.0, 0.0]], np.float32)
     m = oracle.topk_margin(s, 4)
     assert m[0] < 1e-6 and abs(m[1] - 1.0) < 1e-6
+
+
+def test_c_generator_matches_numpy_generator(oracle):
+    a = oracle.synth_normal(99, synth.tensor_id(synth.TID_MLP2_W, 2), (1000,), 0.02, start=12345)
+    b = synth.bf16_bits_to_f32(synth.normal_bf16_bits(99, synth.tensor_id(synth.TID_MLP2_W, 2), 1000, 0.02, start=12345))
+    assert np.array_equal(a, b)
+    w = oracle.layer_weights(32, 64, 8, 5)
+    ref = synth.MoELayerWeights(32, 64, 8, 5)
+    for n in ("router_w", "router_b", "mlp1_w", "mlp1_b", "mlp2_w", "mlp2_b"):
+        assert np.array_equal(getattr(w, n), getattr(ref, n)), n
