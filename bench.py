@@ -45,7 +45,7 @@ FLOP_PER_TOKEN = 2 * H * E + 2 * K_TOP * H * (2 * I) + 2 * K_TOP * I * H  # 199,
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM kernel at this workload,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_MLP1_BYTES = None
+NCU_TRAFFIC_MLP1_BYTES = 1_125_318_040  # profiles/grouped_gemm_cfg2_T1024_first.md
 
 
 def measured_peaks():
@@ -70,7 +70,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
