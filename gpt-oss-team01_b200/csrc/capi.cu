@@ -23,7 +23,7 @@ struct LayerWeights {
   float *b1g = nullptr, *b1u = nullptr;  // [E_local][I]
   __nv_bfloat16 *w2 = nullptr;        // [E_local][H][I]
   float *b2 = nullptr;                // [E_local][H]
-  CUtensorMap map_w1, map_w2;
+  CUtensorMap map_w1, map_w2, map_wr;
   bool ready = false;
 };
 
@@ -42,6 +42,10 @@ struct gptoss_ctx {
   int *status = nullptr;              // [kStatusWords]
   __nv_bfloat16 *t_stage = nullptr;   // [max_tokens,H]  device copies for the host-buffer entry point
   float *x_stage = nullptr;           // [max_tokens,H]
+  float *router_partials = nullptr;   // [kRouterMaxSplits][max_tokens][E] split-K partial scores
+  CUtensorMap map_t;                  // tensor map of the caller's activations (re-encoded when they move)
+  const void *map_t_base = nullptr;
+  int map_t_rows = -1;
   float *staging = nullptr;           // fp32 scratch for weight conversion
   size_t staging_elems = 0;
   CUtensorMap map_x, map_h;
@@ -101,6 +105,7 @@ int alloc_layer(gptoss_ctx *ctx, LayerWeights &w) {
   CK(dev_alloc(&w.b2, EL * H));
   CK(encode_weight_map(&w.map_w1, w.w1, H, I, EL * 2));
   CK(encode_weight_map(&w.map_w2, w.w2, I, H, EL));
+  CK(encode_map_2d(&w.map_wr, w.router_w, H, E, (uint32_t)((E + 15) & ~(size_t)15)));
   return GPTOSS_OK;
 }
 
@@ -200,6 +205,7 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->status, kStatusWords));
   A(dev_alloc(&ctx->t_stage, T * H));
   A(dev_alloc(&ctx->x_stage, T * H));
+  A(dev_alloc(&ctx->router_partials, (size_t)kRouterMaxSplits * T * E));
   if (e == cudaSuccess) A(cudaMemset(ctx->status, 0, kStatusWords * sizeof(int)));
   // rows never written by the gather are still read by TMA (their columns are discarded): keep them finite
   if (e == cudaSuccess) A(cudaMemset(ctx->x_packed, 0, P * H * sizeof(__nv_bfloat16)));
@@ -233,6 +239,7 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->status);
   cudaFree(ctx->t_stage);
   cudaFree(ctx->x_stage);
+  cudaFree(ctx->router_partials);
   cudaFree(ctx->staging);
   delete ctx;
   return GPTOSS_OK;
@@ -374,7 +381,26 @@ int gptoss_moe_route(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const LayerWeights &w = ctx->layers[layer];
   const __nv_bfloat16 *t = static_cast<const __nv_bfloat16 *>(t_dev_bf16);
-  CK(launch_router_topk(t, w.router_w, w.router_b, T, ctx->d, ctx->rb, s));
+  if (reinterpret_cast<uintptr_t>(t_dev_bf16) & 15u)
+    return ctx->fail(GPTOSS_ERR_BAD_ARG, "activations must be 16-byte aligned");
+  if (ctx->map_t_base != t_dev_bf16 || ctx->map_t_rows != T) {
+    CK(encode_map_2d(&ctx->map_t, t_dev_bf16, ctx->d.H, T, 128));
+    ctx->map_t_base = t_dev_bf16;
+    ctx->map_t_rows = T;
+  }
+  RouterArgs ra;
+  memset(&ra, 0, sizeof ra);
+  ra.map_t = ctx->map_t;
+  ra.map_wr = w.map_wr;
+  ra.partials = ctx->router_partials;
+  ra.T = T;
+  ra.E = ctx->d.E;
+  ra.n_cols = (ctx->d.E + 15) & ~15;
+  ra.k_blocks = (ctx->d.H + kBlockK - 1) / kBlockK;
+  ra.status = ctx->status;
+  CK(launch_router_gemm(ra, kRouterMaxSplits, s));
+  CK(launch_router_topk(ctx->router_partials, router_splits_for(T, ra.k_blocks, kRouterMaxSplits), w.router_b, T,
+                        ctx->d, ctx->rb, s));
   CK(launch_expert_scan(ctx->rb, T, ctx->d, s));
   CK(launch_scatter_gather(t, ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base, ctx->rb.sorted, ctx->x_packed, s));
   return GPTOSS_OK;

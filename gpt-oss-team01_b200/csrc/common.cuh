@@ -17,7 +17,7 @@ constexpr int kSmCountFallback = 148;
 // GEMM tiling (shared by host launch code and kernels)
 constexpr int kBlockK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
 constexpr int kTileF = 128;        // output features per accumulator tile (UMMA M)
-constexpr int kTokChunk = 64;      // token rows per TMA box of the activation operand
+constexpr int kTokChunk = 32;      // token rows per TMA box of the activation operand
 constexpr int kMaxTileTokens = 256;  // token rows per tile (UMMA N max)
 
 // device status word layout (int[8] in global memory)

@@ -8,8 +8,8 @@
 namespace gptoss {
 
 // routing.cu
-cudaError_t launch_router_topk(const __nv_bfloat16 *t, const __nv_bfloat16 *wr, const float *br, int T,
-                               const Dims &d, const RouteBuffers &rb, cudaStream_t s);
+cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, const Dims &d,
+                               const RouteBuffers &rb, cudaStream_t s);
 cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
                                 cudaStream_t s);
 cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s);
@@ -20,10 +20,28 @@ cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int
 cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
                            int residual, int sm_count, cudaStream_t s);
 
+// router.cu
+struct RouterArgs {
+  CUtensorMap map_t;   // activations t [T,H]: 2-D (k, token), box {64,128}
+  CUtensorMap map_wr;  // router weight [E,H]: 2-D (k, expert), box {64, n_cols}
+  float *partials;     // [splits][T][E]
+  int T, E;
+  int n_cols;          // E rounded up to a multiple of 16 (UMMA N)
+  int k_blocks;        // ceil(H / 64)
+  int *status;
+  // filled by launch_router_gemm
+  int k_blocks_per_split, stages, stage_bytes, tmem_cols;
+};
+constexpr int kRouterMaxSplits = 8;
+cudaError_t launch_router_gemm(RouterArgs a, int max_splits, cudaStream_t s);
+int router_splits_for(int T, int k_blocks, int max_splits);
+// 2-D bf16 map with the 128-byte swizzle and an arbitrary box height (<= 256 rows)
+cudaError_t encode_map_2d(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint32_t box_rows);
+
 // grouped_gemm.cu
 struct GemmArgs {
   CUtensorMap map_w;    // weights: 3-D (k, feature, expert-slab), bf16, 128-byte swizzle, box {64,128,1}
-  CUtensorMap map_act;  // activations: 2-D (k, row), bf16, 128-byte swizzle, box {64,64}
+  CUtensorMap map_act;  // activations: 2-D (k, row), bf16, 128-byte swizzle, box {64,32}
   const int *offsets;    // [E+1] global expert offsets
   const int *tb_prefix;  // [E_local+1]
   int e_begin, n_local;  // local expert range

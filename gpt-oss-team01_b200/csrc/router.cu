@@ -1,0 +1,163 @@
+// Router GEMM on the tensor cores: partial[s][b][e] = sum over the k-blocks of split s of t[b,:] . Wr[e,:]
+// (bf16 x bf16 -> fp32).  Tokens are the UMMA M side (128 per CTA, one TMEM lane each), experts the N side
+// (E rounded up to 16, at most 256), K is split over gridDim.y CTAs so that even T = 1024 keeps ~64 SMs
+// streaming; the splits are summed in a fixed order by the top-k kernel, so the scores are bit-identical
+// on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs.
+#include "kernels.cuh"
+#include "tcgen05.cuh"
+
+namespace gptoss {
+
+namespace {
+
+constexpr int kRouterThreads = 192;
+constexpr int kRouterATile = 128 * kBlockK * 2;  // 16 KiB: 128 tokens x 64 k
+constexpr int kRouterMaxStages = 8;
+constexpr int kRouterSmemBudget = 200 * 1024;
+
+struct RouterCtrl {
+  uint64_t full[kRouterMaxStages];
+  uint64_t empty[kRouterMaxStages];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __grid_constant__ RouterArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  RouterCtrl *ctrl = reinterpret_cast<RouterCtrl *>(smem_raw + (tiles_base - raw) + a.stages * a.stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb0 = blockIdx.y * a.k_blocks_per_split;
+  const int kb1 = min(a.k_blocks, kb0 + a.k_blocks_per_split);
+  const int row0 = blockIdx.x * 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctrl->tmem_full), 1);
+    ctrl->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), a.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, armed = 0, last_par = 0;
+      const uint32_t tx = kRouterATile + a.n_cols * kBlockK * 2;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x1100 | stage);
+        const uint32_t bar = smem_u32(&ctrl->full[stage]);
+        const uint32_t sa = tiles_base + stage * a.stage_bytes;
+        armed |= 1u << stage;
+        last_par = (last_par & ~(1u << stage)) | (phase << stage);
+        mbar_expect_tx(bar, tx);
+        tma_load_2d(sa, &a.map_t, bar, kb * kBlockK, row0);
+        tma_load_2d(sa + kRouterATile, &a.map_wr, bar, kb * kBlockK, 0);
+        if (++stage == a.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      for (int s = 0; s < a.stages; ++s)
+        if (armed & (1u << s)) {
+          const uint32_t par = (last_par >> s) & 1u;
+          for (uint32_t i = 0; i < kSpinLimit; ++i)
+            if (mbar_try_wait(smem_u32(&ctrl->full[s]), par)) break;
+        }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t idesc = umma_idesc(a.n_cols);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x1300 | stage);
+        tc_fence_after();
+        const uint32_t sa = tiles_base + stage * a.stage_bytes;
+        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + kRouterATile);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k)
+          umma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&ctrl->empty[stage]));
+        if (++stage == a.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      umma_commit(smem_u32(&ctrl->tmem_full));
+    }
+  } else {
+    const int q = warp & 3;
+    const int b = row0 + q * 32 + lane;
+    mbar_wait(smem_u32(&ctrl->tmem_full), 0, &ctrl->abort, a.status, 0x1400);
+    tc_fence_after();
+    float *dst = a.partials + ((size_t)blockIdx.y * a.T + b) * a.E;
+    const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16);
+    for (int c0 = 0; c0 < a.n_cols; c0 += 16) {
+      uint32_t r[16];
+      tmem_ld16(tbase + c0, r);
+      tmem_ld_wait();
+      if (b < a.T) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < a.E) dst[c0 + j] = __uint_as_float(r[j]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, a.tmem_cols);
+  }
+}
+
+}  // namespace
+
+// Fills the launch geometry of `a` (splits, stages, shared memory) for T tokens and launches.
+cudaError_t launch_router_gemm(RouterArgs a, int max_splits, cudaStream_t s) {
+  const int n_tiles = (a.T + 127) / 128;
+  int splits = 96 / n_tiles;
+  if (splits < 1) splits = 1;
+  if (splits > max_splits) splits = max_splits;
+  if (splits > a.k_blocks) splits = a.k_blocks;
+  a.k_blocks_per_split = (a.k_blocks + splits - 1) / splits;
+  splits = (a.k_blocks + a.k_blocks_per_split - 1) / a.k_blocks_per_split;
+  a.stage_bytes = kRouterATile + ((a.n_cols * kBlockK * 2 + 1023) & ~1023);
+  a.stages = kRouterSmemBudget / a.stage_bytes;
+  if (a.stages > kRouterMaxStages) a.stages = kRouterMaxStages;
+  if (a.stages > a.k_blocks_per_split) a.stages = a.k_blocks_per_split < 2 ? 2 : a.k_blocks_per_split;
+  a.tmem_cols = 32;
+  while (a.tmem_cols < a.n_cols) a.tmem_cols <<= 1;
+  const size_t smem = (size_t)a.stages * a.stage_bytes + 1024 + sizeof(RouterCtrl);
+  cudaError_t e = cudaFuncSetAttribute(router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  router_gemm_kernel<<<dim3(n_tiles, splits), kRouterThreads, smem, s>>>(a);
+  e = cudaGetLastError();
+  return e;
+}
+
+int router_splits_for(int T, int k_blocks, int max_splits) {
+  const int n_tiles = (T + 127) / 128;
+  int splits = 96 / n_tiles;
+  if (splits < 1) splits = 1;
+  if (splits > max_splits) splits = max_splits;
+  if (splits > k_blocks) splits = k_blocks;
+  const int per = (k_blocks + splits - 1) / splits;
+  return (k_blocks + per - 1) / per;
+}
+
+}  // namespace gptoss

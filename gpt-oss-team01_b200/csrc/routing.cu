@@ -1,4 +1,4 @@
-// Routing side of the MoE block: router GEMM + top-k + softmax, expert histogram / prefix / stable
+// Routing side of the MoE block: router split-K reduction + top-k + softmax, expert histogram / prefix / stable
 // scatter (counting sort of pair ids), row gather, and the slot-ordered combine.
 //
 // Everything here is bandwidth/latency-bound integer and fp32 work: one warp per token, 16-byte
@@ -10,32 +10,6 @@
 namespace gptoss {
 
 namespace {
-
-__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-
-// vals[32] per lane  ->  lane l returns the sum over all lanes of vals[l]; fixed summation tree.
-__device__ __forceinline__ float warp_reduce_transpose32(float (&v)[32], int lane) {
-#pragma unroll
-  for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
-    const bool upper = (lane & off) != 0;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      if (i < n / 2) {
-        const float send = upper ? v[i] : v[i + n / 2];
-        const float keep = upper ? v[i + n / 2] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-      }
-    }
-  }
-  return v[0];
-}
 
 // Top-k of E scores spread over the warp (position p = s*32 + lane holds val[s]) in the exact order
 // the reference kernel produces (layer_hip_batch.cpp:1119-1140): k rounds of "first maximum of
@@ -130,51 +104,30 @@ __device__ __forceinline__ void warp_topk_softmax(float (&val)[SLOTS], int E, in
 
 }  // namespace
 
-// ---- router GEMM + top-k + softmax + per-block expert histogram ------------------------------------
-// One warp per token.  scores[b,e] = sum_h t[b,h] * Wr[e,h] + br[e]  (fp32 accumulation).
+// ---- split-K reduction of the router GEMM + bias + top-k + softmax + per-block expert histogram ---------
+// One warp per token.  scores[b,e] = (partial[0][b,e] + partial[1][b,e] + ...) + br[e], summed in split order.
 template <int GROUPS>
-__global__ void __launch_bounds__(256) router_topk_kernel(const __nv_bfloat16 *__restrict__ t,
-                                                          const __nv_bfloat16 *__restrict__ wr,
+__global__ void __launch_bounds__(256) router_topk_kernel(const float *__restrict__ partials, int n_splits,
                                                           const float *__restrict__ br, int T, Dims d,
                                                           RouteBuffers rb) {
-  extern __shared__ uint4 smem_rows[];
   __shared__ int hist[kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * kTokensPerRouteBlock + warp;
-  const int nchunk = d.H >> 3;
   for (int e = threadIdx.x; e < d.E; e += blockDim.x) hist[e] = 0;
-  uint4 *trow = smem_rows + (size_t)warp * nchunk;
-  if (b < T) {
-    const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)b * d.H);
-    for (int c = lane; c < nchunk; c += 32) trow[c] = __ldg(src + c);
-  }
   __syncthreads();
-
   if (b < T) {
     float score[GROUPS];
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
-      float acc[32];
-#pragma unroll
-      for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-      for (int c = lane; c < nchunk; c += 32) {
-        float tf[8];
-        unpack8(trow[c], tf);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int eg = g * 32 + e;
-          if (eg < d.E) {
-            float wf[8];
-            unpack8(__ldg(reinterpret_cast<const uint4 *>(wr + (size_t)eg * d.H) + c), wf);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[e] = fmaf(tf[i], wf[i], acc[e]);
-          }
-        }
-      }
-      const float s = warp_reduce_transpose32(acc, lane);
       const int eg = g * 32 + lane;
-      score[g] = (eg < d.E) ? s + br[eg] : -INFINITY;
-      if (eg < d.E) rb.scores[(size_t)b * d.E + eg] = score[g];
+      float s = -INFINITY;
+      if (eg < d.E) {
+        s = partials[(size_t)b * d.E + eg];
+        for (int sp = 1; sp < n_splits; ++sp) s += partials[((size_t)sp * T + b) * d.E + eg];
+        s += br[eg];
+        rb.scores[(size_t)b * d.E + eg] = s;
+      }
+      score[g] = s;
     }
     float w;
     int id;
@@ -368,19 +321,14 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
 // ---- launchers -------------------------------------------------------------------------------------------
 static inline int route_blocks(int T) { return (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock; }
 
-cudaError_t launch_router_topk(const __nv_bfloat16 *t, const __nv_bfloat16 *wr, const float *br, int T,
-                               const Dims &d, const RouteBuffers &rb, cudaStream_t s) {
+cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, const Dims &d,
+                               const RouteBuffers &rb, cudaStream_t s) {
   const int groups = (d.E + 31) / 32;
-  const size_t smem = (size_t)kTokensPerRouteBlock * d.H * sizeof(__nv_bfloat16);
   const dim3 grid(route_blocks(T)), block(256);
-#define GPTOSS_ROUTER_CASE(G)                                                                          \
-  case G: {                                                                                            \
-    cudaError_t e = cudaFuncSetAttribute(router_topk_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                   \
-    if (e != cudaSuccess) return e;                                                                    \
-    router_topk_kernel<G><<<grid, block, smem, s>>>(t, wr, br, T, d, rb);                              \
-    break;                                                                                             \
-  }
+#define GPTOSS_ROUTER_CASE(G)                                                            \
+  case G:                                                                                \
+    router_topk_kernel<G><<<grid, block, 0, s>>>(partials, n_splits, br, T, d, rb);      \
+    break;
   switch (groups) {
     GPTOSS_ROUTER_CASE(1)
     GPTOSS_ROUTER_CASE(2)
