@@ -31,7 +31,8 @@ EXPORTS = [
     "gptoss_download_layer", "gptoss_moe_forward", "gptoss_moe_forward_host",
     "gptoss_moe_forward_partial", "gptoss_moe_route", "gptoss_moe_mlp1_swiglu", "gptoss_moe_mlp2",
     "gptoss_moe_combine", "gptoss_topk_softmax", "gptoss_moe_build_offsets", "gptoss_read_tap",
-    "gptoss_synth_normal_bf16", "gptoss_version",
+    "gptoss_synth_normal_bf16", "gptoss_version", "gptoss_moe_build_offsets_noalloc",
+    "gptoss_noalloc_last_error",
 ]
 
 
@@ -96,6 +97,8 @@ def load() -> C.CDLL:
         "gptoss_read_tap": ([ctxp, i32, vp, u64], i32),
         "gptoss_synth_normal_bf16": ([vp, u64, u64, u64, u64, f32, vp], i32),
         "gptoss_version": ([], C.c_char_p),
+        "gptoss_moe_build_offsets_noalloc": ([i32, i32, i32, vp, vp, vp, vp], i32),
+        "gptoss_noalloc_last_error": ([], C.c_char_p),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -4,6 +4,9 @@
 // Everything here is bandwidth/latency-bound integer and fp32 work: one warp per token, 16-byte
 // loads, warp shuffles, no global atomics, deterministic results (all ranks of an expert-parallel
 // group must derive bit-identical routing from the replicated activations).
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -397,4 +400,73 @@ cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const
   return cudaGetLastError();
 }
 
+// ---- allocation-free grouping -----------------------------------------------------------------------------
+// Scratch of gptoss_moe_build_offsets_noalloc: per-block expert histograms, per-block bases and the
+// token-block prefix, in one statically allocated device array (every device that loads the library holds
+// these 1 MiB + 1 KiB until the process exits).  In host code `g_noalloc_scratch` is only a handle: the
+// device address is obtained with cudaGetSymbolAddress, once per device, below.
+constexpr int kNoAllocMaxEntries = 128 * 1024;  // route blocks x experts
+static __device__ __align__(256) int g_noalloc_scratch[2 * kNoAllocMaxEntries + kMaxExperts + 1];
+
 }  // namespace gptoss
+
+namespace {
+thread_local char g_noalloc_error[256] = "";
+int noalloc_fail(int code, const char *msg) {
+  snprintf(g_noalloc_error, sizeof g_noalloc_error, "%s", msg);
+  return code;
+}
+constexpr int kMaxDevices = 64;
+int *g_noalloc_ptr[kMaxDevices];  // device address of g_noalloc_scratch, per device (0 = not resolved yet)
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+extern "C" const char *gptoss_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int gptoss_moe_build_offsets_noalloc(int T, int n_experts, int top_k, const int *topk_i_dev,
+                                                 int *offsets_dev, int *sorted_pair_ids_dev, void *stream) {
+  using namespace gptoss;
+  if (T < 0 || n_experts <= 0 || n_experts > kMaxExperts || top_k <= 0 || top_k > kMaxTopK)
+    return noalloc_fail(GPTOSS_ERR_BAD_ARG, "T, n_experts (1..256) or top_k (1..8) out of range");
+  if (!offsets_dev || (T > 0 && (!topk_i_dev || !sorted_pair_ids_dev)))
+    return noalloc_fail(GPTOSS_ERR_BAD_ARG, "null pointer");
+  const long long n_blocks = ((long long)T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock;
+  if (n_blocks * n_experts > kNoAllocMaxEntries)
+    return noalloc_fail(GPTOSS_ERR_BAD_ARG,
+                        "batch too large for the static scratch: ceil(T/8) * n_experts must not exceed 131072 "
+                        "(use gptoss_moe_build_offsets with a context instead)");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    if (cudaMemsetAsync(offsets_dev, 0, (n_experts + 1) * sizeof(int), s) != cudaSuccess)
+      return noalloc_fail(GPTOSS_ERR_CUDA, "cudaMemsetAsync failed");
+    return GPTOSS_OK;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return noalloc_fail(GPTOSS_ERR_CUDA, "cudaGetDevice failed or device index above 63");
+  int *scratch;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {  // first call on this device: resolve the symbol with this device current
+      void *p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || !p) return noalloc_fail(GPTOSS_ERR_CUDA, "cudaGetSymbolAddress failed");
+      g_noalloc_ptr[dev] = static_cast<int *>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  Dims d{0, 0, n_experts, top_k, 0, n_experts, 0.f};
+  RouteBuffers rb{};
+  rb.blk_hist = scratch;
+  rb.blk_base = scratch + kNoAllocMaxEntries;
+  rb.tb_prefix = scratch + 2 * kNoAllocMaxEntries;
+  rb.offsets = offsets_dev;
+  rb.sorted = sorted_pair_ids_dev;
+  // every entry of the scratch that the scan and the scatter read is first written by this call, so
+  // nothing has to start at zero
+  if (launch_pair_hist(topk_i_dev, T, d, rb.blk_hist, s) != cudaSuccess ||
+      launch_expert_scan(rb, T, d, s) != cudaSuccess ||
+      launch_scatter_gather(nullptr, topk_i_dev, T, d, rb.blk_base, rb.sorted, nullptr, s) != cudaSuccess)
+    return noalloc_fail(GPTOSS_ERR_CUDA, "kernel launch failed");
+  return GPTOSS_OK;
+}

@@ -129,6 +129,23 @@ int gptoss_topk_softmax(gptoss_ctx *ctx, int T, const float *scores_dev, float *
 int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int *offsets_dev,
                              int *sorted_pair_ids_dev, void *stream);
 
+/* Grouping for callers that must not allocate: same result as gptoss_moe_build_offsets, but it needs no
+ * context and calls no cudaMalloc/cudaFree or any other allocating routine.  It has no counterpart in
+ * the reference.  It is meant for hosts that hand all device memory to their own pool at start-up (as
+ * the reference engine does in our_init), so that a later cudaMalloc would fail or stall, and for code
+ * on a serving path where an implicit device synchronisation inside an allocator is not acceptable.
+ * The scratch (block histograms and bases) lives in a fixed 1 MiB device array inside the library, held
+ * on every GPU that loads it until the process exits.  Limit: ceil(T/8) * n_experts <= 131072 (e.g.
+ * T = 8192 with 128 experts); larger batches are rejected with GPTOSS_ERR_BAD_ARG and a message from
+ * gptoss_noalloc_last_error().  Works on the CURRENT device.  The first call on each device resolves
+ * the array's device address; make that first call outside any stream capture.  All calls share the
+ * array, which keeps the previous call's contents (each call overwrites what it reads, nothing needs
+ * clearing): two calls whose kernels may overlap on the GPU (different streams) race — serialise them. */
+int gptoss_moe_build_offsets_noalloc(int T, int n_experts, int top_k, const int *topk_i_dev,
+                                     int *offsets_dev, int *sorted_pair_ids_dev, void *stream);
+/* Message of the last failing gptoss_moe_build_offsets_noalloc call on this host thread ("" if none). */
+const char *gptoss_noalloc_last_error(void);
+
 /* ---- taps (debug/parity; the reference's DEBUG printDebug, getp-csrc/src/model.cpp:205-450) -------- */
 #define GPTOSS_TAP_SCORES 0    /* fp32 [T,E]   router scores incl. bias                            */
 #define GPTOSS_TAP_TOPK_W 1    /* fp32 [T,k]   gate weights                                        */
