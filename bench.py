@@ -7,8 +7,9 @@
 A step is one pass of the block over one batch of synthetic tokens.  N = 1: hidden 2880, 32 experts,
 top-4, T = 1024 tokens (the single-GPU configuration the headline metric is quoted on).  N > 1 (one
 process per GPU under torchrun): the same layer with its experts sharded E/N per GPU and T = 1024*N
-replicated tokens, partial outputs summed with an NCCL all-reduce — per-GPU work is fixed, so the
-scaling is weak.  Weights rotate over several distinct layers (each 1.6 GB >> the 126 MB L2), so
+replicated tokens; the gate-weighted expert rows are pushed to the GPU that owns the token by peer stores
+from the down-GEMM epilogue, summed there and delivered to every rank (an NCCL all-reduce of per-rank
+partials is timed beside it as the baseline) — per-GPU work is fixed, so the scaling is weak.  Weights rotate over several distinct layers (each 1.6 GB >> the 126 MB L2), so
 every step streams its weights from HBM.
 
 Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` goes through the
@@ -153,6 +154,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1; the reference arm uses every host core (set before libgomp loads)
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     T = TOKENS_PER_GPU * args.gpus
     tok_s, info, times = cpu_arm(T, target_seconds=6.0, repeats=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {
@@ -207,14 +210,16 @@ def run_ours(args):
     x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
     partial = torch.empty_like(x) if world > 1 else None
 
-    def step(i):
-        layer = i % N_WEIGHT_SETS
-        if world == 1:
-            blk.forward(layer, t_dev, x)
-        else:
-            blk.forward_partial(layer, t_dev, partial)
-            dist.all_reduce(partial)
-            x.add_(partial)
+    if world > 1:
+        blk.attach_peers()  # CUDA IPC handles of the combine buffers, exchanged over the process group
+
+    def step(i):  # x += MoE(t); N > 1: fused peer-store combine inside forward()
+        blk.forward(i % N_WEIGHT_SETS, t_dev, x)
+
+    def step_nccl(i):  # A/B baseline for N > 1: per-rank partial + NCCL all-reduce + add
+        blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
+        dist.all_reduce(partial)
+        x.add_(partial)
 
     def barrier():
         if world > 1:
@@ -241,10 +246,28 @@ def run_ours(args):
         ms = float(tms.item())
     value = T * K / (ms * 1e-3)
 
+    nccl_ms = None
+    if world > 1:  # the NCCL baseline on the same steps
+        for i in range(3):
+            step_nccl(i)
+        barrier()
+        n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0.record()
+        for i in range(K):
+            step_nccl(i)
+        n1.record()
+        barrier()
+        tn = torch.tensor([n0.elapsed_time(n1)], device="cuda")
+        dist.all_reduce(tn, op=dist.ReduceOp.MAX)
+        nccl_ms = float(tn.item()) / K
+
     # per-stage device time (same steps, events between the stages), for the roofline of the top kernel
-    names = ["route", "mlp1_swiglu", "mlp2", "combine"]
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
-    out = partial if world > 1 else x
+    if world == 1:
+        names = ["route", "mlp1_swiglu", "mlp2", "combine"]
+    else:
+        names = ["route", "mlp1_swiglu", "mlp2_push", "owner_combine", "add_delta"]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(K)]
+    barrier()
     for i in range(K):
         layer = i % N_WEIGHT_SETS
         evs[i][0].record()
@@ -252,11 +275,19 @@ def run_ours(args):
         evs[i][1].record()
         blk.mlp1_swiglu(layer)
         evs[i][2].record()
-        blk.mlp2(layer)
-        evs[i][3].record()
-        blk.combine(out, residual=(world == 1))
-        evs[i][4].record()
-    torch.cuda.synchronize()
+        if world == 1:
+            blk.mlp2(layer)
+            evs[i][3].record()
+            blk.combine(x, residual=True)
+            evs[i][4].record()
+        else:
+            blk.push_to_owners(layer)
+            evs[i][3].record()
+            blk.owner_combine()
+            evs[i][4].record()
+            blk.add_delta(x)
+            evs[i][5].record()
+    barrier()
     blk.status()
     stage_ms = {n: sum(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(K)) / K for j, n in enumerate(names)}
 
@@ -288,8 +319,13 @@ def run_ours(args):
         "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
                            "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
                            "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
-        "stage_ms": stage_ms, "gpu_launches": 6 * K,
+        "stage_ms": stage_ms, "gpu_launches": (6 if world == 1 else 9) * K,
     }
+    if world > 1:
+        comm_ms = stage_ms["owner_combine"] + stage_ms["add_delta"]
+        line["combine"] = {"kind": "peer stores from the down-GEMM epilogue + owner sum + peer delivery (fp32 wire)",
+                           "owner_combine_plus_add_ms": comm_ms, "share_of_step": comm_ms / (ms / K),
+                           "nccl_allreduce_baseline_ms_per_step": nccl_ms}
 
     if rank == 0:
         cs = clocks.summary()

@@ -14,13 +14,14 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 # GPTOSS_B200_LIB points the binding at another build of the same C ABI (e.g. a tuning variant)
 LIB_PATH = Path(os.environ.get("GPTOSS_B200_LIB", CSRC / "libgptoss_b200.so"))
-SOURCES = ["routing.cu", "router.cu", "grouped_gemm.cu", "convert.cu", "capi.cu"]
+SOURCES = ["routing.cu", "router.cu", "grouped_gemm.cu", "comm.cu", "convert.cu", "capi.cu"]
 HEADERS = ["common.cuh", "kernels.cuh", "tcgen05.cuh", "../../include/gptoss_b200.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--threads", "4"]
 
 OK, ERR_BAD_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_STATE = range(6)
 WIRE_F32, WIRE_BF16 = 0, 1
+IPC_HANDLE_BYTES = 64
 (TAP_SCORES, TAP_TOPK_W, TAP_TOPK_I, TAP_OFFSETS, TAP_SORTED, TAP_X_PACKED, TAP_GATE_UP,
  TAP_Y_PAIRS) = range(8)
 
@@ -32,7 +33,9 @@ EXPORTS = [
     "gptoss_moe_forward_partial", "gptoss_moe_route", "gptoss_moe_mlp1_swiglu", "gptoss_moe_mlp2",
     "gptoss_moe_combine", "gptoss_topk_softmax", "gptoss_moe_build_offsets", "gptoss_read_tap",
     "gptoss_synth_normal_bf16", "gptoss_version", "gptoss_moe_build_offsets_noalloc",
-    "gptoss_noalloc_last_error",
+    "gptoss_noalloc_last_error", "gptoss_comm_export", "gptoss_comm_attach",
+    "gptoss_comm_attach_local", "gptoss_comm_set_timeout_ms", "gptoss_moe_push_to_owners",
+    "gptoss_moe_owner_combine", "gptoss_moe_add_delta",
 ]
 
 
@@ -99,6 +102,13 @@ def load() -> C.CDLL:
         "gptoss_version": ([], C.c_char_p),
         "gptoss_moe_build_offsets_noalloc": ([i32, i32, i32, vp, vp, vp, vp], i32),
         "gptoss_noalloc_last_error": ([], C.c_char_p),
+        "gptoss_comm_export": ([ctxp, vp], i32),
+        "gptoss_comm_attach": ([ctxp, vp], i32),
+        "gptoss_comm_attach_local": ([ctxp, C.POINTER(vp)], i32),
+        "gptoss_comm_set_timeout_ms": ([ctxp, i32], i32),
+        "gptoss_moe_push_to_owners": ([ctxp, i32, vp], i32),
+        "gptoss_moe_owner_combine": ([ctxp, vp], i32),
+        "gptoss_moe_add_delta": ([ctxp, vp, vp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -38,7 +38,16 @@ struct gptoss_ctx {
   RouteBuffers rb{};
   __nv_bfloat16 *x_packed = nullptr;  // [P,H]
   __nv_bfloat16 *gate_up = nullptr;   // [P,I]
-  float *y_pairs = nullptr;           // [P,H]
+  float *y_pairs = nullptr;           // [P,H]   (inside `sym`)
+  // symmetric buffer: same layout on every rank, exported to the peers over CUDA IPC
+  //   [flags: 2*kMaxRanks ints, padded to 1 KiB][delta: T*H fp32][y_pairs: P*H fp32]
+  uint8_t *sym = nullptr;
+  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0;
+  int *comm_counter = nullptr;        // last-block counter of the owner combine
+  void *peer_base[kMaxRanks] = {};    // opened IPC mappings (nullptr for the own rank / not attached)
+  PeerTable peers{};
+  bool attached = false;
+  int comm_step = 0;
   int *status = nullptr;              // [kStatusWords]
   __nv_bfloat16 *t_stage = nullptr;   // [max_tokens,H]  device copies for the host-buffer entry point
   float *x_stage = nullptr;           // [max_tokens,H]
@@ -145,6 +154,9 @@ GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
   a.sorted = ctx->rb.sorted;
   a.topk_w = ctx->rb.topk_w;
   a.status = ctx->status;
+  a.n_owners = 1;
+  a.top_k = ctx->d.k;
+  a.slice_tokens = ctx->max_tokens;
   return a;
 }
 
@@ -184,6 +196,7 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->d = Dims{dims->hidden, dims->intermediate, dims->n_experts, dims->top_k, rank * ctx->n_local,
                 (rank + 1) * ctx->n_local, dims->swiglu_limit};
   ctx->layers.resize(dims->n_layers);
+  ctx->peers.timeout_ns = 2000000000ull;
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
   const size_t P = T * k, nblk = (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock;
@@ -201,7 +214,14 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->rb.tb_prefix, E + 1));
   A(dev_alloc(&ctx->x_packed, P * H));
   A(dev_alloc(&ctx->gate_up, P * I));
-  A(dev_alloc(&ctx->y_pairs, P * H));
+  ctx->sym_delta_off = 1024;
+  ctx->sym_y_off = ctx->sym_delta_off + ((T * H * sizeof(float) + 1023) & ~(size_t)1023);
+  ctx->sym_bytes = ctx->sym_y_off + P * H * sizeof(float);
+  A(cudaMalloc(reinterpret_cast<void **>(&ctx->sym), ctx->sym_bytes));
+  if (e == cudaSuccess) A(cudaMemset(ctx->sym, 0, 1024));
+  if (e == cudaSuccess) ctx->y_pairs = reinterpret_cast<float *>(ctx->sym + ctx->sym_y_off);
+  A(dev_alloc(&ctx->comm_counter, 1));
+  if (e == cudaSuccess) A(cudaMemset(ctx->comm_counter, 0, sizeof(int)));
   A(dev_alloc(&ctx->status, kStatusWords));
   A(dev_alloc(&ctx->t_stage, T * H));
   A(dev_alloc(&ctx->x_stage, T * H));
@@ -235,7 +255,10 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->rb.tb_prefix);
   cudaFree(ctx->x_packed);
   cudaFree(ctx->gate_up);
-  cudaFree(ctx->y_pairs);
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
+  cudaFree(ctx->sym);
+  cudaFree(ctx->comm_counter);
   cudaFree(ctx->status);
   cudaFree(ctx->t_stage);
   cudaFree(ctx->x_stage);
@@ -437,6 +460,51 @@ int gptoss_moe_combine(gptoss_ctx *ctx, int T, float *x_dev, int residual, void 
   return GPTOSS_OK;
 }
 
+// ---- stages of the fused cross-GPU combine -------------------------------------------------------------------
+static int check_attached(gptoss_ctx *ctx) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (ctx->world < 2 || !ctx->attached) return ctx->fail(GPTOSS_ERR_STATE, "no peers attached");
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int step = ++ctx->comm_step;
+  GemmArgs a = gemm_args(ctx, ctx->layers[layer], false);
+  a.n_owners = ctx->world;
+  a.slice_tokens = (ctx->cur_T + ctx->world - 1) / ctx->world;
+  for (int r = 0; r < ctx->world; ++r) a.y_owner[r] = ctx->peers.y[r];
+  CK(launch_grouped_mlp2(a, ctx->sm_count, s));
+  CK(launch_signal_pushed(ctx->peers, step, s));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_owner_combine(gptoss_ctx *ctx, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  CK(launch_combine_owner(ctx->peers, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, ctx->status,
+                          ctx->comm_counter, ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if (!x_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null residual pointer");
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  CK(launch_add_delta(ctx->peers, ctx->cur_T, ctx->d.H, ctx->comm_step, x_dev, ctx->status, ctx->sm_count,
+                      static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
 // ---- the per-layer operator --------------------------------------------------------------------------------
 static int forward_common(gptoss_ctx *ctx, int layer, int T, const void *t, float *out, int residual, void *stream) {
   int rc;
@@ -449,9 +517,18 @@ static int forward_common(gptoss_ctx *ctx, int layer, int T, const void *t, floa
 int gptoss_moe_forward(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, float *x_dev, void *stream) {
   if (!ctx) return GPTOSS_ERR_BAD_ARG;
   if (!x_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null residual pointer");
-  if (ctx->world > 1)
+  if (ctx->world == 1) return forward_common(ctx, layer, T, t_dev_bf16, x_dev, 1, stream);
+  if (!ctx->attached)
     return ctx->fail(GPTOSS_ERR_STATE, "world > 1 without attached peers: use gptoss_moe_forward_partial");
-  return forward_common(ctx, layer, T, t_dev_bf16, x_dev, 1, stream);
+  // expert-parallel with peer memory: push rows to their owners from the down-GEMM epilogue, owners
+  // combine their token slice and deliver it to every rank, every rank adds it to its residual
+  int rc;
+  if ((rc = gptoss_moe_route(ctx, layer, T, t_dev_bf16, stream))) return rc;
+  if (T == 0) return GPTOSS_OK;
+  if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
+  if ((rc = gptoss_moe_push_to_owners(ctx, layer, stream))) return rc;
+  if ((rc = gptoss_moe_owner_combine(ctx, stream))) return rc;
+  return gptoss_moe_add_delta(ctx, x_dev, stream);
 }
 
 int gptoss_moe_forward_partial(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, float *partial_dev,
@@ -474,6 +551,76 @@ int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t
   if ((rc = gptoss_moe_forward(ctx, layer, T, ctx->t_stage, ctx->x_stage, nullptr))) return rc;
   CK(cudaMemcpyAsync(x_host, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, 0));
   return gptoss_ctx_status(ctx);
+}
+
+// ---- peer memory ----------------------------------------------------------------------------------------------
+int gptoss_comm_export(gptoss_ctx *ctx, void *handle_out) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (!handle_out) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null handle buffer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == GPTOSS_IPC_HANDLE_BYTES, "IPC handle size");
+  CK(cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  CK(cudaIpcGetMemHandle(&h, ctx->sym));
+  memcpy(handle_out, &h, sizeof h);
+  return GPTOSS_OK;
+}
+
+int gptoss_comm_attach(gptoss_ctx *ctx, const void *handles) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (!handles) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null handle buffer");
+  if (ctx->world > kMaxRanks) return ctx->fail(GPTOSS_ERR_BAD_ARG, "world larger than 16");
+  if (ctx->attached) return ctx->fail(GPTOSS_ERR_STATE, "peers already attached");
+  CK(cudaSetDevice(ctx->device));
+  ctx->peers.rank = ctx->rank;
+  ctx->peers.world = ctx->world;
+  for (int r = 0; r < ctx->world; ++r) {
+    uint8_t *base = ctx->sym;
+    if (r != ctx->rank) {
+      cudaIpcMemHandle_t h;
+      memcpy(&h, static_cast<const uint8_t *>(handles) + (size_t)r * GPTOSS_IPC_HANDLE_BYTES, sizeof h);
+      void *p = nullptr;
+      CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+      ctx->peer_base[r] = p;
+      base = static_cast<uint8_t *>(p);
+    }
+    ctx->peers.flags[r] = reinterpret_cast<int *>(base);
+    ctx->peers.delta[r] = reinterpret_cast<float *>(base + ctx->sym_delta_off);
+    ctx->peers.y[r] = reinterpret_cast<float *>(base + ctx->sym_y_off);
+  }
+  ctx->attached = true;
+  return GPTOSS_OK;
+}
+
+int gptoss_comm_attach_local(gptoss_ctx *ctx, gptoss_ctx *const *all) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (!all) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null context array");
+  if (ctx->world > kMaxRanks) return ctx->fail(GPTOSS_ERR_BAD_ARG, "world larger than 16");
+  if (ctx->attached) return ctx->fail(GPTOSS_ERR_STATE, "peers already attached");
+  CK(cudaSetDevice(ctx->device));
+  ctx->peers.rank = ctx->rank;
+  ctx->peers.world = ctx->world;
+  for (int r = 0; r < ctx->world; ++r) {
+    const gptoss_ctx *p = all[r];
+    if (!p || p->world != ctx->world || p->rank != r || p->sym_bytes != ctx->sym_bytes)
+      return ctx->fail(GPTOSS_ERR_BAD_ARG, "context array does not hold ranks 0..world-1 of the same shape");
+    if (p->device != ctx->device) {
+      cudaError_t e = cudaDeviceEnablePeerAccess(p->device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+      else if (e != cudaSuccess) return ctx->fail(GPTOSS_ERR_CUDA, "cudaDeviceEnablePeerAccess", e);
+    }
+    ctx->peers.flags[r] = reinterpret_cast<int *>(p->sym);
+    ctx->peers.delta[r] = reinterpret_cast<float *>(p->sym + p->sym_delta_off);
+    ctx->peers.y[r] = reinterpret_cast<float *>(p->sym + p->sym_y_off);
+  }
+  ctx->attached = true;
+  return GPTOSS_OK;
+}
+
+int gptoss_comm_set_timeout_ms(gptoss_ctx *ctx, int ms) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  if (ms <= 0 || ms > 60000) return ctx->fail(GPTOSS_ERR_BAD_ARG, "timeout must be in 1..60000 ms");
+  ctx->peers.timeout_ns = (unsigned long long)ms * 1000000ull;
+  return GPTOSS_OK;
 }
 
 // ---- stand-alone routing operators ---------------------------------------------------------------------------

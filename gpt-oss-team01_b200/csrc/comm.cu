@@ -1,0 +1,146 @@
+// Cross-GPU combine of the expert-parallel MoE block over NVLink peer memory (no NCCL, no TMA multicast).
+//
+// Every rank owns a contiguous slice of the tokens.  The down-GEMM epilogue of each rank stores its
+// gate-weighted expert outputs, row by row as the tiles finish, straight into the OWNER's y_pairs buffer
+// (plain peer stores, addressed by pair id = token*k + slot, so every row has exactly one writer).  When a
+// rank has pushed everything it raises flag A on every peer.  The owner waits for flag A of all ranks, sums
+// the k slots of each of its tokens in slot order (the same fixed order as the single-GPU combine, so the
+// result is bit-identical for any number of GPUs), stores the sum into the `delta` buffer of EVERY rank
+// (the all-gather, again by peer stores) and raises flag B everywhere.  Each rank finally waits for flag B
+// of all owners and adds `delta` to its replicated residual stream.
+//
+// Flags carry the step number (monotonic), so nothing is ever reset.  All waits are bounded by wall time;
+// a wait that gives up records a time-out in the status words and the kernel carries on without waiting.
+#include "kernels.cuh"
+
+namespace gptoss {
+
+namespace {
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int *p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int *p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Threads 0..world-1 of the block each wait until flags[r] >= step; then the block synchronises.
+__device__ __forceinline__ void wait_all_ranks(const int *flags, int world, int step, unsigned long long limit_ns,
+                                               int *status, int site) {
+  if ((int)threadIdx.x < world) {
+    const unsigned long long t0 = global_ns();
+    while (ld_acquire_sys(flags + threadIdx.x) < step) {
+      if (*reinterpret_cast<volatile int *>(status) != 0) break;  // some wait already gave up
+      if (global_ns() - t0 > limit_ns) {
+        if (atomicCAS(status, 0, kDevErrTimeout) == 0) {
+          status[1] = site;
+          status[2] = (int)threadIdx.x;
+        }
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+}
+
+// Last block of the grid (all blocks fence + count) raises flag `which` (0 = A, 1 = B) on every rank.
+__device__ __forceinline__ void signal_all_ranks(const PeerTable &pt, int which, int step, int *counter) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int *>(counter), 1u);
+    if (prev == gridDim.x * gridDim.y - 1) {
+      *counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < pt.world; ++r) st_release_sys(pt.flags[r] + which * kMaxRanks + pt.rank, step);
+    }
+  }
+}
+
+}  // namespace
+
+// Raised by the down-GEMM launch when it pushes to owners: a one-block kernel right after it on the same
+// stream (kernel completion orders the GEMM's peer stores before these flag stores).
+__global__ void signal_pushed_kernel(PeerTable pt, int step) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < pt.world; ++r) st_release_sys(pt.flags[r] + pt.rank, step);
+  }
+}
+
+// Owner: delta[b,:] = ((s0+s1)+s2)+s3 for the tokens of this rank's slice, stored to every rank.
+__global__ void __launch_bounds__(256) combine_owner_kernel(PeerTable pt, int T, int H, int k, int step,
+                                                            int *status, int *counter) {
+  wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2100);
+  const int slice = (T + pt.world - 1) / pt.world;
+  const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
+  const int h4 = H >> 2;
+  const size_t total = (size_t)max(0, b1 - b0) * h4;
+  const float4 *y = reinterpret_cast<const float4 *>(pt.y[pt.rank]);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int b = b0 + (int)(i / h4), c = (int)(i % h4);
+    float4 acc = y[((size_t)b * k) * h4 + c];
+    for (int j = 1; j < k; ++j) {
+      const float4 v = y[((size_t)b * k + j) * h4 + c];
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    for (int r = 0; r < pt.world; ++r) reinterpret_cast<float4 *>(pt.delta[r])[(size_t)b * h4 + c] = acc;
+  }
+  signal_all_ranks(pt, 1, step, counter);
+}
+
+// Every rank: x += delta once all owners have delivered their slices.
+__global__ void __launch_bounds__(256) add_delta_kernel(PeerTable pt, int T, int H, int step, float *x, int *status) {
+  wait_all_ranks(pt.flags[pt.rank] + kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2200);
+  const size_t total = (size_t)T * (H >> 2);
+  const float4 *d = reinterpret_cast<const float4 *>(pt.delta[pt.rank]);
+  float4 *xp = reinterpret_cast<float4 *>(x);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float4 o = xp[i];
+    const float4 v = d[i];
+    o.x += v.x;
+    o.y += v.y;
+    o.z += v.z;
+    o.w += v.w;
+    xp[i] = o;
+  }
+}
+
+cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s) {
+  signal_pushed_kernel<<<1, 32, 0, s>>>(pt, step);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_owner(const PeerTable &pt, int T, int H, int k, int step, int *status, int *counter,
+                                 int sm_count, cudaStream_t s) {
+  const int slice = (T + pt.world - 1) / pt.world;
+  const size_t total = (size_t)slice * (H >> 2);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > sm_count * 8) blocks = sm_count * 8;
+  if (blocks < 1) blocks = 1;
+  combine_owner_kernel<<<blocks, 256, 0, s>>>(pt, T, H, k, step, status, counter);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add_delta(const PeerTable &pt, int T, int H, int step, float *x, int *status, int sm_count,
+                             cudaStream_t s) {
+  const size_t total = (size_t)T * (H >> 2);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > sm_count * 8) blocks = sm_count * 8;
+  if (blocks < 1) blocks = 1;
+  add_delta_kernel<<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
+  return cudaGetLastError();
+}
+
+}  // namespace gptoss

@@ -56,8 +56,8 @@ struct Ctrl {
   int max_rows;
   int tbp[kMaxExperts + 1];
   int off[kMaxExperts + 1];
-  int pair_s[2][TileCfg<NA>::kMetaTokens];
-  float w_s[2][TileCfg<NA>::kMetaTokens];
+  float *dst_s[2][TileCfg<NA>::kMetaTokens];  // mlp2: destination row of each token column (local or peer)
+  float w_s[2][TileCfg<NA>::kMetaTokens];     // mlp2: gate weight of each token column
 };
 
 struct Tile {
@@ -74,10 +74,13 @@ __device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, in
   const int r = idx - c->tbp[cur] * nft;
   const int nb = c->tbp[cur + 1] - c->tbp[cur];
   const int ft = r / nb, tb = r - ft * nb;
+  // an expert with more than 256 rows is cut into nb blocks of (almost) equal size, a multiple of 16 rows
+  const int rows = c->off[cur + 1] - c->off[cur];
+  const int blk = (((rows + nb - 1) / nb) + 15) & ~15;
   t.e = cur;
   t.f0 = ft * kTileF;
-  t.row0 = c->off[cur] + tb * kMaxTileTokens;
-  t.n_valid = min(kMaxTileTokens, c->off[cur + 1] - t.row0);
+  t.row0 = c->off[cur] + tb * blk;
+  t.n_valid = min(blk, rows - tb * blk);
   return true;
 }
 
@@ -234,7 +237,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       if constexpr (NA == 1) {
         for (int n = et; n < t.n_valid; n += kEpilogueThreads) {
           const int pair = a.sorted[t.row0 + n];
-          ctrl->pair_s[acc][n] = pair;
+          float *base = a.y_pairs;
+          if (a.n_owners > 1) base = a.y_owner[min(a.n_owners - 1, (pair / a.top_k) / a.slice_tokens)];
+          ctrl->dst_s[acc][n] = base + (size_t)pair * a.n_feat;
           ctrl->w_s[acc][n] = a.topk_w[pair];
         }
         epilogue_bar_sync();
@@ -264,15 +269,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             if (f_ok && c0 + j + 1 < t.n_valid) dst[(size_t)(j + 1) * a.n_feat] = pk.y;
           }
         } else {
-          int pr[16];
+          float *pr[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            pr[j] = ctrl->pair_s[acc][c0 + j];
+            pr[j] = ctrl->dst_s[acc][c0 + j];
             v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (f_ok && c0 + j < t.n_valid) a.y_pairs[(size_t)pr[j] * a.n_feat + f] = v[j];
+            if (f_ok && c0 + j < t.n_valid) pr[j][f] = v[j];
         }
       }
       tc_fence_before();

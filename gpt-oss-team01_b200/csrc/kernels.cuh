@@ -20,6 +20,21 @@ cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int
 cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
                            int residual, int sm_count, cudaStream_t s);
 
+// comm.cu — peer-memory combine across the ranks of one box
+constexpr int kMaxRanks = 16;
+struct PeerTable {
+  int rank, world;
+  unsigned long long timeout_ns;  // limit of every wait on a peer flag
+  float *y[kMaxRanks];      // every rank's y_pairs  [P,H] fp32 (index = own rank: local memory)
+  float *delta[kMaxRanks];  // every rank's delta    [T,H] fp32
+  int *flags[kMaxRanks];    // every rank's flags    [2][kMaxRanks]: A = "rank r pushed", B = "owner r delivered"
+};
+cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s);
+cudaError_t launch_combine_owner(const PeerTable &pt, int T, int H, int k, int step, int *status, int *counter,
+                                 int sm_count, cudaStream_t s);
+cudaError_t launch_add_delta(const PeerTable &pt, int T, int H, int step, float *x, int *status, int sm_count,
+                             cudaStream_t s);
+
 // router.cu
 struct RouterArgs {
   CUtensorMap map_t;   // activations t [T,H]: 2-D (k, token), box {64,128}
@@ -52,7 +67,11 @@ struct GemmArgs {
   const float *bias_a;   // mlp1: gate bias [E_local, I];  mlp2: bias [E_local, H]
   const float *bias_b;   // mlp1: up bias   [E_local, I];  mlp2: unused
   __nv_bfloat16 *gate_up;  // mlp1 out [P, I]
-  float *y_pairs;          // mlp2 out [P, H] by pair id
+  float *y_pairs;          // mlp2 out [P, H] by pair id (local)
+  float *y_owner[kMaxRanks];  // mlp2 with n_owners > 1: y_pairs of the rank that owns the token slice
+  int n_owners;            // 1 = store locally; > 1 = push each row to its owner
+  int slice_tokens;        // tokens per owner slice
+  int top_k;
   const int *sorted;       // mlp2: [P]
   const float *topk_w;     // mlp2: [P] by pair id
   int *status;             // device status words

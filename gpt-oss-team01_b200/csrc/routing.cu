@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
 }
 
 // ---- stable scatter of pair ids (+ optional gather of the token rows of local experts) ---------------
-__global__ void __launch_bounds__(256) scatter_gather_kernel(const __nv_bfloat16 *__restrict__ t,
+__global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat16 *__restrict__ t,
                                                              const int *__restrict__ topk_i, int T, Dims d,
                                                              const int *__restrict__ blk_base,
                                                              int *__restrict__ sorted,
@@ -259,7 +259,11 @@ __global__ void __launch_bounds__(256) scatter_gather_kernel(const __nv_bfloat16
     pos_s[q] = pos;
   }
   __syncthreads();
-  const int b = blockIdx.x * kTokensPerRouteBlock + warp;
+  // gather: blockDim.x / 256 warps share one token row (its 16-byte chunks interleaved), so that a block
+  // keeps enough loads in flight; the row is read once and written to each local slot
+  const int wpt = blockDim.x >> 8;            // warps per token
+  const int tok = warp / wpt, part = warp - tok * wpt;
+  const int b = blockIdx.x * kTokensPerRouteBlock + tok;
   if (t != nullptr && b < T) {
     const int nchunk = d.H >> 3;
     const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)b * d.H);
@@ -269,11 +273,12 @@ __global__ void __launch_bounds__(256) scatter_gather_kernel(const __nv_bfloat16
     for (int j = 0; j < kMaxTopK; ++j) {
       pos[j] = -1;
       if (j < k) {
-        const int e = ids[warp * k + j];
-        if (e >= d.e_begin && e < d.e_end) pos[j] = pos_s[warp * k + j];
+        const int e = ids[tok * k + j];
+        if (e >= d.e_begin && e < d.e_end) pos[j] = pos_s[tok * k + j];
       }
     }
-    for (int c = lane; c < nchunk; c += 32) {
+#pragma unroll 4
+    for (int c = part * 32 + lane; c < nchunk; c += 32 * wpt) {
       const uint4 v = __ldg(src + c);
 #pragma unroll
       for (int j = 0; j < kMaxTopK; ++j)
@@ -385,7 +390,7 @@ cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, cud
 cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int T, const Dims &d,
                                   const int *blk_base, int *sorted, __nv_bfloat16 *x_packed,
                                   cudaStream_t s) {
-  scatter_gather_kernel<<<route_blocks(T), 256, 0, s>>>(t, topk_i, T, d, blk_base, sorted, x_packed);
+  scatter_gather_kernel<<<route_blocks(T), t ? 1024 : 256, 0, s>>>(t, topk_i, T, d, blk_base, sorted, x_packed);
   return cudaGetLastError();
 }
 
@@ -393,7 +398,7 @@ cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const
                            int residual, int sm_count, cudaStream_t s) {
   const size_t total = (size_t)T * (d.H >> 2);
   int blocks = (int)((total + 255) / 256);
-  const int cap = sm_count * 8;
+  const int cap = sm_count * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   combine_kernel<<<blocks, 256, 0, s>>>(y_pairs, topk_i, T, d, x, residual);

@@ -107,6 +107,41 @@ class MoEBlock:
             _ptr(w.mlp2_w), _ptr(w.mlp2_b)))
         return w
 
+    # -- peer memory (fused cross-GPU combine) ----------------------------------------------------------------
+    def attach_peers(self, group=None):
+        """Exchanges the IPC handles of the combine buffers over torch.distributed (one process per GPU)
+        and attaches all ranks; afterwards forward() runs the fused peer-store combine."""
+        import torch.distributed as dist
+        mine = (C.c_uint8 * capi.IPC_HANDLE_BYTES)()
+        self._check(self.lib.gptoss_comm_export(self._ctx, mine))
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, bytes(mine), group=group)
+        blob = b"".join(gathered)
+        assert len(blob) == self.world * capi.IPC_HANDLE_BYTES
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        self._check(self.lib.gptoss_comm_attach(self._ctx, buf))
+        dist.barrier(group=group)
+
+    @staticmethod
+    def attach_local(blocks):
+        """Attaches contexts that live in this process (ranks 0..world-1, in order) to one another."""
+        arr = (C.c_void_p * len(blocks))(*[b._ctx for b in blocks])
+        for b in blocks:
+            b._check(b.lib.gptoss_comm_attach_local(b._ctx, arr))
+
+    def set_peer_timeout_ms(self, ms):
+        self._check(self.lib.gptoss_comm_set_timeout_ms(self._ctx, ms))
+
+    def push_to_owners(self, layer, stream=None):
+        """down GEMM with peer stores into the owners' buffers + "pushed" flag"""
+        self._check(self.lib.gptoss_moe_push_to_owners(self._ctx, layer, _stream(stream)))
+
+    def owner_combine(self, stream=None):
+        self._check(self.lib.gptoss_moe_owner_combine(self._ctx, _stream(stream)))
+
+    def add_delta(self, x, stream=None):
+        self._check(self.lib.gptoss_moe_add_delta(self._ctx, _ptr(x), _stream(stream)))
+
     # -- the per-layer operator -----------------------------------------------------------------------------
     def forward(self, layer, t, x, stream=None):
         """x[T,H] (fp32 cuda) += MoE(t[T,H] (bf16 cuda)), asynchronous on the stream."""

@@ -103,6 +103,36 @@ int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t
 int gptoss_moe_forward_partial(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16,
                                float *partial_dev, void *stream);
 
+/* ---- peer memory for the fused cross-GPU combine -----------------------------------------------------
+ * Replaces the all-pairs hipDeviceEnablePeerAccess of warm_up (getp-csrc/getp_run.cpp:41-48) and the event /
+ * pthread-barrier hand-shake of ring_reduce_agg_quantize_fp8 (getp-csrc/src/parallelism.cpp:1605-1670).
+ * One process (or thread) per GPU: every rank exports a 64-byte handle of its combine buffers, the host
+ * exchanges the handles by any means (the tests use torch.distributed), and every rank attaches all of
+ * them (rank order).  Afterwards gptoss_moe_forward on world > 1 pushes the gate-weighted expert rows
+ * from the down-GEMM epilogue straight into the buffer of the GPU that owns the token (peer stores over
+ * NVLink), the owner sums its slice in slot order and stores it to every rank, and every rank adds it to
+ * its residual stream.  All ranks must call gptoss_moe_forward the same number of times with the same T.
+ * Device-side waits on peers are bounded (2 s) and end as GPTOSS_ERR_TIMEOUT in gptoss_ctx_status. */
+#define GPTOSS_IPC_HANDLE_BYTES 64
+int gptoss_comm_export(gptoss_ctx *ctx, void *handle_out);
+int gptoss_comm_attach(gptoss_ctx *ctx, const void *handles /* world x GPTOSS_IPC_HANDLE_BYTES */);
+/* Same for contexts that live in ONE process (one host thread per GPU, the reference's model,
+ * getp-csrc/submit/getp_run_submit.cpp:176-178): `all` holds the contexts of ranks 0..world-1. */
+int gptoss_comm_attach_local(gptoss_ctx *ctx, gptoss_ctx *const *all);
+/* Limit of every device-side wait on a peer (default 2000 ms). */
+int gptoss_comm_set_timeout_ms(gptoss_ctx *ctx, int ms);
+/* The three stages of the fused combine, in the order gptoss_moe_forward runs them after
+ * gptoss_moe_route and gptoss_moe_mlp1_swiglu (replace moe_mlp2_forward_hip + moe_scatter_aggregate_ep_hip
+ * + ring_reduce_agg_quantize_fp8 + add_vector_batched, getp-csrc/src/model.cpp:384-444):
+ *   push_to_owners : down GEMM whose epilogue stores each gate-weighted row into the owner's buffer,
+ *                    then raises this rank's "pushed" flag on every rank;
+ *   owner_combine  : waits for the "pushed" flags of all ranks, sums the k slots of this rank's token
+ *                    slice in slot order, stores the sums to every rank, raises "delivered" everywhere;
+ *   add_delta      : waits for the "delivered" flags of all ranks, x += delivered sums. */
+int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream);
+int gptoss_moe_owner_combine(gptoss_ctx *ctx, void *stream);
+int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream);
+
 /* ---- stages of the operator (same order as inside gptoss_moe_forward) ------------------------------
  * They work on the context's scratch so that a test can stop after any stage and read the taps. */
 /* router_gemm_v2 + topk_softmax_batched + moe_build_offsets_hip + moe_pack_inputs_hip

@@ -1,0 +1,77 @@
+"""The fused cross-GPU combine (peer stores from the down-GEMM epilogue, owner-side slot-ordered sum,
+delivery to every rank) exercised on ONE GPU: the ranks are contexts of one process attached to one another,
+and their stages are issued in an order in which no kernel ever has to wait for a later one (all pushes, then
+all owner combines, then all adds).  The result must equal the single-context block bit for bit.  A second
+test lets a wait on a peer run out (a rank that never pushes) and checks that it ends as a status code."""
+import numpy as np
+import pytest
+
+from gptoss_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def to_dev_bf16(x):
+    T, H = x.shape
+    return torch.from_numpy(synth.f32_to_bf16_bits(x).view(np.int16).reshape(T, H)).cuda().view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("world,T", [(2, 300), (4, 203), (8, 64)])
+def test_emulated_ranks_match_single_context_bitwise(world, T):
+    from gptoss_b200 import moe
+    H, I, E, k = 256, 192, 16, 4
+    w = synth.MoELayerWeights(H, I, E, 61, sigma=0.05)
+    single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)
+    single.upload_layer(0, w)
+    ranks = [moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, rank=r, world=world)
+             for r in range(world)]
+    for b in ranks:
+        b.upload_layer(0, w)
+    moe.MoEBlock.attach_local(ranks)
+    for step in range(3):  # flags carry the step number: several steps without any reset
+        t = synth.activations(100 + step, T, H)
+        x0 = synth.normal(200 + step, synth.tensor_id(synth.TID_RESIDUAL), (T, H), 1.0)
+        t_dev = to_dev_bf16(t)
+        want = torch.from_numpy(x0.copy()).cuda()
+        single.forward(0, t_dev, want)
+        xs = [torch.from_numpy(x0.copy()).cuda() for _ in range(world)]
+        for b in ranks:
+            b.route(0, t_dev)
+            b.mlp1_swiglu(0)
+            b.push_to_owners(0)
+        for b in ranks:
+            b.owner_combine()
+        for b, x in zip(ranks, xs):
+            b.add_delta(x)
+        for b in ranks:
+            b.status()
+        for x in xs:
+            assert torch.equal(x, want)
+    for b in ranks + [single]:
+        b.close()
+
+
+def test_wait_on_a_silent_peer_times_out_as_status():
+    from gptoss_b200 import capi, moe
+    H, I, E, k, T = 128, 128, 8, 2, 32
+    ranks = [moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, rank=r, world=2)
+             for r in range(2)]
+    for b in ranks:
+        b.fill_layer_synthetic(0, 5, 0.05)
+    moe.MoEBlock.attach_local(ranks)
+    ranks[0].set_peer_timeout_ms(150)
+    t_dev = to_dev_bf16(synth.activations(5, T, H))
+    x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    ranks[0].forward(0, t_dev, x)          # rank 1 never pushes: the owner's wait must give up
+    with pytest.raises(moe.GptossError) as e:
+        ranks[0].status()
+    assert e.value.code == capi.ERR_TIMEOUT
+    ranks[0].status()                      # the error word is cleared, the context stays usable
+    part = torch.empty_like(x)
+    ranks[0].forward_partial(0, t_dev, part)
+    ranks[0].status()
+    assert torch.isfinite(part).all()
+    for b in ranks:
+        b.close()

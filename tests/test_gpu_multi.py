@@ -1,0 +1,73 @@
+"""Fused cross-GPU combine on real peers: one process per GPU, CUDA IPC handles exchanged over gloo.
+Needs at least two GPUs (skipped otherwise).  Every rank's residual stream must equal the single-GPU block
+bit for bit, for several steps in a row."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def _worker(rank, world, port, out_dir):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path[:0] = [str(root), str(root / "tests")]
+    import __graft_entry__ as entry
+    entry.load_package()
+    import torch.distributed as dist
+    from gptoss_b200 import moe, synth
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    H, I, E, k, T = 512, 384, 16, 4, 1000
+    blk = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, device=rank, rank=rank,
+                       world=world)
+    blk.fill_layer_synthetic(0, 9, 0.05)
+    blk.attach_peers()
+    single = None
+    if rank == 0:
+        single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, device=0)
+        single.fill_layer_synthetic(0, 9, 0.05)
+    ok = True
+    for step in range(4):
+        t = synth.activations(300 + step, T, H)
+        t_dev = torch.from_numpy(synth.f32_to_bf16_bits(t).view(np.int16).reshape(T, H)).cuda().view(torch.bfloat16)
+        x = torch.ones((T, H), dtype=torch.float32, device="cuda")
+        blk.forward(0, t_dev, x)
+        blk.status()
+        got = x.cpu()
+        if rank == 0:
+            want = torch.ones((T, H), dtype=torch.float32, device="cuda")
+            single.forward(0, t_dev, want)
+            want = want.cpu()
+        else:
+            want = torch.empty_like(got)
+        dist.broadcast(want, src=0)
+        ok = ok and bool(torch.equal(got, want))
+    dist.barrier()
+    blk.close()
+    if single:
+        single.close()
+    (Path(out_dir) / f"rank{rank}.txt").write_text("ok" if ok else "mismatch")
+    dist.destroy_process_group()
+
+
+def test_fused_combine_across_processes_matches_single_gpu(tmp_path):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2 if n < 4 else 4
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
