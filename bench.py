@@ -166,7 +166,7 @@ def run_reference(args):
         "config": workload_config(args.gpus, T), "cpu_baseline": info,
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    print_line(line)
 
 
 def workload_config(n_gpus, T):
@@ -319,7 +319,7 @@ def run_ours(args):
         "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
                            "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
                            "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
-        "stage_ms": stage_ms, "gpu_launches": (6 if world == 1 else 9) * K,
+        "stage_ms": stage_ms, "gpu_launches": (7 if world == 1 else 10) * K,  # router GEMM, top-k, scan, scatter, 2 GEMMs, combine (+ signal, owner, add)
     }
     if world > 1:
         comm_ms = stage_ms["owner_combine"] + stage_ms["add_delta"]
@@ -378,12 +378,19 @@ def run_ours(args):
         line["cpu_baseline"] = info
     blk.close()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print_line(line)
     if world > 1:
         dist.destroy_process_group()
 
 
 def main():
+    # libraries (NCCL's version banner) may write to stdout; keep fd 1 for the ONE JSON line
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    global print_line
+    def print_line(obj):
+        real_stdout.write(json.dumps(obj) + "\n")
+        real_stdout.flush()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=40)

@@ -55,6 +55,9 @@ struct gptoss_ctx {
   CUtensorMap map_t;                  // tensor map of the caller's activations (re-encoded when they move)
   const void *map_t_base = nullptr;
   int map_t_rows = -1;
+  cudaStream_t s_main = nullptr, s_copy = nullptr;  // streams of the host-buffer entry point (created on first use)
+  cudaEvent_t ev_x = nullptr, ev_t = nullptr;
+  int *status_host = nullptr;         // pinned copy of the status words
   float *staging = nullptr;           // fp32 scratch for weight conversion
   size_t staging_elems = 0;
   CUtensorMap map_x, map_h;
@@ -264,6 +267,11 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->x_stage);
   cudaFree(ctx->router_partials);
   cudaFree(ctx->staging);
+  if (ctx->s_main) cudaStreamDestroy(ctx->s_main);
+  if (ctx->s_copy) cudaStreamDestroy(ctx->s_copy);
+  if (ctx->ev_x) cudaEventDestroy(ctx->ev_x);
+  if (ctx->ev_t) cudaEventDestroy(ctx->ev_t);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
   delete ctx;
   return GPTOSS_OK;
 }
@@ -545,12 +553,36 @@ int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t
   if (!t_host || !x_host) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
   if (T == 0) return GPTOSS_OK;
   CK(cudaSetDevice(ctx->device));
+  if (!ctx->s_main) {
+    CK(cudaStreamCreateWithFlags(&ctx->s_main, cudaStreamNonBlocking));
+    CK(cudaStreamCreateWithFlags(&ctx->s_copy, cudaStreamNonBlocking));
+    CK(cudaEventCreateWithFlags(&ctx->ev_x, cudaEventDisableTiming));
+    CK(cudaEventCreateWithFlags(&ctx->ev_t, cudaEventDisableTiming));
+    CK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), kStatusWords * sizeof(int), cudaHostAllocDefault));
+  }
   const size_t n = (size_t)T * ctx->d.H;
-  CK(cudaMemcpyAsync(ctx->t_stage, t_host, n * sizeof(uint16_t), cudaMemcpyHostToDevice, 0));
-  CK(cudaMemcpyAsync(ctx->x_stage, x_host, n * sizeof(float), cudaMemcpyHostToDevice, 0));
-  if ((rc = gptoss_moe_forward(ctx, layer, T, ctx->t_stage, ctx->x_stage, nullptr))) return rc;
-  CK(cudaMemcpyAsync(x_host, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, 0));
-  return gptoss_ctx_status(ctx);
+  // activations first (the routing needs them at once); the residual is needed only by the last kernel, so
+  // its upload follows on a second stream and runs beside the routing and the GEMMs
+  CK(cudaMemcpyAsync(ctx->t_stage, t_host, n * sizeof(uint16_t), cudaMemcpyHostToDevice, ctx->s_main));
+  CK(cudaEventRecord(ctx->ev_t, ctx->s_main));
+  CK(cudaStreamWaitEvent(ctx->s_copy, ctx->ev_t, 0));
+  CK(cudaMemcpyAsync(ctx->x_stage, x_host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
+  CK(cudaEventRecord(ctx->ev_x, ctx->s_copy));
+  if (ctx->world == 1) {
+    if ((rc = gptoss_moe_route(ctx, layer, T, ctx->t_stage, ctx->s_main))) return rc;
+    if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, ctx->s_main))) return rc;
+    if ((rc = gptoss_moe_mlp2(ctx, layer, ctx->s_main))) return rc;
+    CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
+    if ((rc = gptoss_moe_combine(ctx, T, ctx->x_stage, 1, ctx->s_main))) return rc;
+  } else {
+    CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
+    if ((rc = gptoss_moe_forward(ctx, layer, T, ctx->t_stage, ctx->x_stage, ctx->s_main))) return rc;
+  }
+  CK(cudaMemcpyAsync(x_host, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_main));
+  CK(cudaMemcpyAsync(ctx->status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_main));
+  CK(cudaStreamSynchronize(ctx->s_main));
+  if (ctx->status_host[0] != 0) return gptoss_ctx_status(ctx);  // formats the message and clears the word
+  return GPTOSS_OK;
 }
 
 // ---- peer memory ----------------------------------------------------------------------------------------------

@@ -246,3 +246,59 @@ def test_config2_full_size_sampled_against_oracle(oracle):
     blk.forward(0, to_dev_bf16(t), x2)
     assert np.array_equal(x2.cpu().numpy(), got)
     blk.close()
+
+
+def test_config3_full_size_skewed_routing_sampled(oracle):
+    """20B layer, T = 8192, Zipf-skewed router bias (hottest expert first): experts receive very different
+    row counts (several token blocks for the hot ones, a handful of rows for the cold ones)."""
+    H = I = 2880
+    E, k, T = 32, 4, 8192
+    blk = make_block(H, I, E, k, T)
+    blk.fill_layer_synthetic(0, seed=33, sigma=0.02)
+    blk.set_router_bias(0, synth.zipf_router_bias(33, 0, E, 1.2))
+    t = synth.activations(33, T, H)
+    x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    blk.forward(0, to_dev_bf16(t), x)
+    blk.status()
+    got = x.cpu().numpy()
+    off, srt = blk.tap("offsets", T), blk.tap("sorted", T)
+    ti, tw = blk.tap("topk_i", T), blk.tap("topk_w", T)
+    rows = np.diff(off)
+    assert rows[0] > 4 * rows[-1] and rows.sum() == T * k  # skew is really there
+    ooff, osrt, _ = oracle.counting_sort(ti, E)
+    assert np.array_equal(off, ooff) and np.array_equal(srt, osrt)
+    _, oi, _, _ = oracle.topk_softmax(blk.tap("scores", T), k, oracle_lib.RULE_SELECTION)
+    assert np.array_equal(ti, oi)
+    w = blk.download_layer(0)
+    sample = np.random.default_rng(1).choice(T, 16, replace=False)
+    want = oracle.moe_block(np.ascontiguousarray(t[sample]), np.ascontiguousarray(tw[sample]),
+                            np.ascontiguousarray(ti[sample]), w, mode=oracle_lib.MODE_GPU_BF16)
+    assert rel_l2(got[sample], want) < REL_L2_BLOCK
+    blk.close()
+
+
+def test_config5_shard_128_experts_sampled(oracle):
+    """gpt-oss-120b dims: 128 experts, this rank (3 of 8) holds experts 48..63; T = 2048 tokens."""
+    H = I = 2880
+    E, k, T, world, rank = 128, 4, 2048, 8, 3
+    blk = make_block(H, I, E, k, T, rank=rank, world=world)
+    blk.fill_layer_synthetic(0, seed=55, sigma=0.02)
+    t = synth.activations(55, T, H)
+    part = torch.full((T, H), 3.0, dtype=torch.float32, device="cuda")
+    blk.forward_partial(0, to_dev_bf16(t), part)
+    blk.status()
+    got = part.cpu().numpy()
+    ti, tw = blk.tap("topk_i", T), blk.tap("topk_w", T)
+    _, oi, _, _ = oracle.topk_softmax(blk.tap("scores", T), k, oracle_lib.RULE_SELECTION)
+    assert np.array_equal(ti, oi)
+    ooff, osrt, _ = oracle.counting_sort(ti, E)
+    assert np.array_equal(blk.tap("offsets", T), ooff) and np.array_equal(blk.tap("sorted", T), osrt)
+    e0 = rank * (E // world)
+    local = ((ti >= e0) & (ti < e0 + E // world)).any(axis=1)
+    assert np.all(got[~local] == 0.0)  # tokens without a local expert get an exact zero partial
+    w = blk.download_layer(0)          # the 16 local experts only
+    sample = np.flatnonzero(local)[:48]
+    want = oracle.moe_block(np.ascontiguousarray(t[sample]), np.ascontiguousarray(tw[sample]),
+                            np.ascontiguousarray(ti[sample] - e0), w, mode=oracle_lib.MODE_GPU_BF16)
+    assert rel_l2(got[sample], want) < REL_L2_BLOCK
+    blk.close()
