@@ -46,7 +46,7 @@ FLOP_PER_TOKEN = 2 * H * E + 2 * K_TOP * H * (2 * I) + 2 * K_TOP * I * H  # 199,
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM kernel at this workload,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_MLP1_BYTES = 1_125_318_040  # profiles/grouped_gemm_cfg2_T1024_first.md
+NCU_TRAFFIC_MLP1_BYTES = 1_124_969_080  # profiles/moe_block_cfg2_T1024.md (dram read 1.101467 GB + write 23.50 MB)
 
 
 def measured_peaks():
