@@ -203,7 +203,8 @@ def run_ours(args):
     global N_WEIGHT_SETS
     N_WEIGHT_SETS = args.weight_sets
     blk = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=K_TOP, n_layers=N_WEIGHT_SETS,
-                       device=local_rank, rank=rank, world=world, max_tokens=T)
+                       device=local_rank, rank=rank, world=world, max_tokens=T,
+                       wire={"f32": 0, "bf16": 1}[args.wire])
     for layer in range(N_WEIGHT_SETS):
         blk.fill_layer_synthetic(layer, SEED, SIGMA)
     t_dev = moe.synth_normal_bf16(T * H, SEED, synth.tensor_id(synth.TID_ACTIVATION), 1.0).view(T, H)
@@ -303,7 +304,7 @@ def run_ours(args):
     else:
         roof = {"bound": "tensor", "achieved": mlp1_flops / mlp1_s / 1e12, "peak": tf_burst, "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = NCU_TRAFFIC_MLP1_BYTES
+    roof["traffic"] = NCU_TRAFFIC_MLP1_BYTES if world == 1 else None  # captured at the N=1 workload only
     roof.update({"kernel": "grouped_gemm_kernel<2> (gate/up GEMM + SwiGLU)", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)",
                  "algorithmic_bytes_per_launch": mlp1_bytes, "algorithmic_flops_per_launch": mlp1_flops,
                  "avg_launch_ms": stage_ms["mlp1_swiglu"], "tensor_frac_of_burst": mlp1_flops / mlp1_s / 1e12 / tf_burst})
@@ -323,7 +324,8 @@ def run_ours(args):
     }
     if world > 1:
         comm_ms = stage_ms["owner_combine"] + stage_ms["add_delta"]
-        line["combine"] = {"kind": "peer stores from the down-GEMM epilogue + owner sum + peer delivery (fp32 wire)",
+        line["combine"] = {"kind": "peer stores (fp32) from the down-GEMM epilogue to the token owner + owner sum in slot "
+                                   f"order + peer delivery of the sums ({args.wire})",
                            "owner_combine_plus_add_ms": comm_ms, "share_of_step": comm_ms / (ms / K),
                            "nccl_allreduce_baseline_ms_per_step": nccl_ms}
 
@@ -397,6 +399,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
+                    help="N > 1: format in which owners deliver the summed rows (rows travel to the owner in fp32)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
                     help="distinct layers of weights the steps rotate over (1 keeps a profiling run small)")

@@ -497,7 +497,7 @@ int gptoss_moe_owner_combine(gptoss_ctx *ctx, void *stream) {
   if (rc) return rc;
   CK(cudaSetDevice(ctx->device));
   if (ctx->cur_T == 0) return GPTOSS_OK;
-  CK(launch_combine_owner(ctx->peers, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, ctx->status,
+  CK(launch_combine_owner(ctx->peers, ctx->wire == GPTOSS_WIRE_BF16, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, ctx->status,
                           ctx->comm_counter, ctx->sm_count, static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }
@@ -508,7 +508,7 @@ int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream) {
   if (!x_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null residual pointer");
   CK(cudaSetDevice(ctx->device));
   if (ctx->cur_T == 0) return GPTOSS_OK;
-  CK(launch_add_delta(ctx->peers, ctx->cur_T, ctx->d.H, ctx->comm_step, x_dev, ctx->status, ctx->sm_count,
+  CK(launch_add_delta(ctx->peers, ctx->wire == GPTOSS_WIRE_BF16, ctx->cur_T, ctx->d.H, ctx->comm_step, x_dev, ctx->status, ctx->sm_count,
                       static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }

@@ -76,39 +76,61 @@ __global__ void signal_pushed_kernel(PeerTable pt, int step) {
   }
 }
 
-// Owner: delta[b,:] = ((s0+s1)+s2)+s3 for the tokens of this rank's slice, stored to every rank.
+__device__ __forceinline__ uint2 pack_bf16x4(const float4 &v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  return make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+}
+__device__ __forceinline__ float4 unpack_bf16x4(const uint2 &u) {
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                     __uint_as_float(u.y & 0xffff0000u));
+}
+
+// Owner: delta[b,:] = ((s0+s1)+s2)+s3 for the tokens of this rank's slice, stored to every rank (fp32, or
+// rounded to bf16 when the wire format is bf16 — the owner then reads back the rounded value like everyone
+// else, so the replicated residual streams stay bit-identical).
+template <bool BF16>
 __global__ void __launch_bounds__(256) combine_owner_kernel(PeerTable pt, int T, int H, int k, int step,
                                                             int *status, int *counter) {
   wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2100);
   const int slice = (T + pt.world - 1) / pt.world;
   const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
-  const int h4 = H >> 2;
-  const size_t total = (size_t)max(0, b1 - b0) * h4;
+  const int h8 = H >> 3;  // 8 elements per thread: two float4 loads per slot, one 16-byte (bf16) or two (fp32) stores per rank
+  const size_t total = (size_t)max(0, b1 - b0) * h8;
   const float4 *y = reinterpret_cast<const float4 *>(pt.y[pt.rank]);
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int b = b0 + (int)(i / h4), c = (int)(i % h4);
-    float4 acc = y[((size_t)b * k) * h4 + c];
+    const int b = b0 + (int)(i / h8), c = (int)(i % h8);
+    const size_t row4 = (size_t)b * k * (2 * h8) + 2 * c;
+    float4 a0 = y[row4], a1 = y[row4 + 1];
     for (int j = 1; j < k; ++j) {
-      const float4 v = y[((size_t)b * k + j) * h4 + c];
-      acc.x += v.x;
-      acc.y += v.y;
-      acc.z += v.z;
-      acc.w += v.w;
+      const float4 v0 = y[row4 + (size_t)j * 2 * h8], v1 = y[row4 + (size_t)j * 2 * h8 + 1];
+      a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
+      a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
     }
-    for (int r = 0; r < pt.world; ++r) reinterpret_cast<float4 *>(pt.delta[r])[(size_t)b * h4 + c] = acc;
+    const size_t o = (size_t)b * h8 + c;
+    if (BF16) {
+      const uint2 p0 = pack_bf16x4(a0), p1 = pack_bf16x4(a1);
+      const uint4 pk = make_uint4(p0.x, p0.y, p1.x, p1.y);
+      for (int r = 0; r < pt.world; ++r) reinterpret_cast<uint4 *>(pt.delta[r])[o] = pk;
+    } else {
+      for (int r = 0; r < pt.world; ++r) {
+        reinterpret_cast<float4 *>(pt.delta[r])[2 * o] = a0;
+        reinterpret_cast<float4 *>(pt.delta[r])[2 * o + 1] = a1;
+      }
+    }
   }
   signal_all_ranks(pt, 1, step, counter);
 }
 
 // Every rank: x += delta once all owners have delivered their slices.
+template <bool BF16>
 __global__ void __launch_bounds__(256) add_delta_kernel(PeerTable pt, int T, int H, int step, float *x, int *status) {
   wait_all_ranks(pt.flags[pt.rank] + kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2200);
   const size_t total = (size_t)T * (H >> 2);
-  const float4 *d = reinterpret_cast<const float4 *>(pt.delta[pt.rank]);
   float4 *xp = reinterpret_cast<float4 *>(x);
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     float4 o = xp[i];
-    const float4 v = d[i];
+    const float4 v = BF16 ? unpack_bf16x4(reinterpret_cast<const uint2 *>(pt.delta[pt.rank])[i])
+                          : reinterpret_cast<const float4 *>(pt.delta[pt.rank])[i];
     o.x += v.x;
     o.y += v.y;
     o.z += v.z;
@@ -122,24 +144,30 @@ cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s) 
   return cudaGetLastError();
 }
 
-cudaError_t launch_combine_owner(const PeerTable &pt, int T, int H, int k, int step, int *status, int *counter,
-                                 int sm_count, cudaStream_t s) {
+cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
+                                 int *counter, int sm_count, cudaStream_t s) {
   const int slice = (T + pt.world - 1) / pt.world;
-  const size_t total = (size_t)slice * (H >> 2);
+  const size_t total = (size_t)slice * (H >> 3);
   int blocks = (int)((total + 255) / 256);
-  if (blocks > sm_count * 8) blocks = sm_count * 8;
+  if (blocks > sm_count * 16) blocks = sm_count * 16;
   if (blocks < 1) blocks = 1;
-  combine_owner_kernel<<<blocks, 256, 0, s>>>(pt, T, H, k, step, status, counter);
+  if (bf16_wire)
+    combine_owner_kernel<true><<<blocks, 256, 0, s>>>(pt, T, H, k, step, status, counter);
+  else
+    combine_owner_kernel<false><<<blocks, 256, 0, s>>>(pt, T, H, k, step, status, counter);
   return cudaGetLastError();
 }
 
-cudaError_t launch_add_delta(const PeerTable &pt, int T, int H, int step, float *x, int *status, int sm_count,
-                             cudaStream_t s) {
+cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, int step, float *x, int *status,
+                             int sm_count, cudaStream_t s) {
   const size_t total = (size_t)T * (H >> 2);
   int blocks = (int)((total + 255) / 256);
-  if (blocks > sm_count * 8) blocks = sm_count * 8;
+  if (blocks > sm_count * 16) blocks = sm_count * 16;
   if (blocks < 1) blocks = 1;
-  add_delta_kernel<<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
+  if (bf16_wire)
+    add_delta_kernel<true><<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
+  else
+    add_delta_kernel<false><<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
   return cudaGetLastError();
 }
 

@@ -43,4 +43,12 @@ struct Dims {
   float limit;
 };
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream is still running; pdl_wait() returns once the predecessor has
+// completed and its writes are visible (a no-op for a normal launch), pdl_launch_dependents() lets the
+// successor's blocks be scheduled as soon as resources free up.  Every kernel of the chain waits BEFORE it
+// releases its successor, so completion of all earlier kernels is implied transitively.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace gptoss

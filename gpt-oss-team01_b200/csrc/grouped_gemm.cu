@@ -152,12 +152,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       int stage = 0, cur = 0;
       uint32_t phase = 0, armed = 0, last_par = 0;
       Tile t;
+      // Head start: the weights do not depend on the kernel before this one, so the weight tiles of the first
+      // ring fill are requested before waiting for it; its outputs (the activation rows) are loaded after.
+      int pre = 0;
+      if ((int)blockIdx.x < total_tiles && decode_tile(blockIdx.x, ctrl, n_local, nft, cur, t)) {
+        const int n_chunks = (max(16, (t.n_valid + 15) & ~15) + kTokChunk - 1) / kTokChunk;
+        pre = min(n_stages, a.k_blocks);
+        for (int kb = 0; kb < pre; ++kb) {
+          const uint32_t bar = smem_u32(&ctrl->full[kb]);
+          const uint32_t sa = ring + kb * stage_bytes;
+          armed |= 1u << kb;
+          mbar_expect_tx(bar, Cfg::kAStageBytes + n_chunks * kBChunkBytes);
+          tma_load_3d(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA);
+          if (NA == 2) tma_load_3d(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1);
+        }
+        pdl_wait();
+        pdl_launch_dependents();
+        for (int kb = 0; kb < pre; ++kb)
+          for (int c = 0; c < n_chunks; ++c)
+            tma_load_2d(ring + kb * stage_bytes + Cfg::kAStageBytes + c * kBChunkBytes, &a.map_act,
+                        smem_u32(&ctrl->full[kb]), kb * kBlockK, t.row0 + c * kTokChunk);
+        stage = pre % n_stages;
+        phase = (pre == n_stages) ? 1u : 0u;
+        cur = 0;
+      } else {
+        pdl_wait();
+        pdl_launch_dependents();
+      }
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
         if (!decode_tile(idx, ctrl, n_local, nft, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const int n_chunks = (n_mma + kTokChunk - 1) / kTokChunk;
         const uint32_t tx = Cfg::kAStageBytes + n_chunks * kBChunkBytes;
-        for (int kb = 0; kb < a.k_blocks; ++kb) {
+        for (int kb = (idx == (int)blockIdx.x) ? pre : 0; kb < a.k_blocks; ++kb) {
           mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x100 | stage);
           const uint32_t bar = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = ring + stage * stage_bytes;
@@ -304,8 +331,7 @@ cudaError_t launch_grouped(const GemmArgs &a, int sm_count, cudaStream_t s) {
   static_assert(kRingBytes >= 2 * (2 * kATileBytes + kMaxTileTokens * kBlockK * 2), "ring must hold two full stages");
   cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  grouped_gemm_kernel<NA><<<sm_count, kGemmThreads, smem, s>>>(a);
-  return cudaGetLastError();
+  return launch_chain(grouped_gemm_kernel<NA>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

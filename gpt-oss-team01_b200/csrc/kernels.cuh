@@ -3,9 +3,36 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
+#include <utility>
+
 #include "common.cuh"
 
 namespace gptoss {
+
+// Launch with the programmatic-serialization attribute (see pdl_wait in common.cuh); GPTOSS_NO_PDL=1 in the
+// environment falls back to plain stream order.
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char *v = std::getenv("GPTOSS_NO_PDL");
+    return !(v && v[0] == '1');
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // routing.cu
 cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, const Dims &d,
@@ -26,14 +53,14 @@ struct PeerTable {
   int rank, world;
   unsigned long long timeout_ns;  // limit of every wait on a peer flag
   float *y[kMaxRanks];      // every rank's y_pairs  [P,H] fp32 (index = own rank: local memory)
-  float *delta[kMaxRanks];  // every rank's delta    [T,H] fp32
+  float *delta[kMaxRanks];  // every rank's delta    [T,H] fp32, or bf16 in the same storage (bf16 wire)
   int *flags[kMaxRanks];    // every rank's flags    [2][kMaxRanks]: A = "rank r pushed", B = "owner r delivered"
 };
 cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s);
-cudaError_t launch_combine_owner(const PeerTable &pt, int T, int H, int k, int step, int *status, int *counter,
-                                 int sm_count, cudaStream_t s);
-cudaError_t launch_add_delta(const PeerTable &pt, int T, int H, int step, float *x, int *status, int sm_count,
-                             cudaStream_t s);
+cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
+                                 int *counter, int sm_count, cudaStream_t s);
+cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, int step, float *x, int *status,
+                             int sm_count, cudaStream_t s);
 
 // router.cu
 struct RouterArgs {

@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
 
   if (warp == 0) {
     if (lane == 0) {
+      pdl_wait();  // the activations may come from the kernel just before this one
+      pdl_launch_dependents();
       int stage = 0;
       uint32_t phase = 0, armed = 0, last_par = 0;
       const uint32_t tx = kRouterATile + a.n_cols * kBlockK * 2;
@@ -145,9 +147,7 @@ cudaError_t launch_router_gemm(RouterArgs a, int max_splits, cudaStream_t s) {
   const size_t smem = (size_t)a.stages * a.stage_bytes + 1024 + sizeof(RouterCtrl);
   cudaError_t e = cudaFuncSetAttribute(router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  router_gemm_kernel<<<dim3(n_tiles, splits), kRouterThreads, smem, s>>>(a);
-  e = cudaGetLastError();
-  return e;
+  return launch_chain(router_gemm_kernel, dim3(n_tiles, splits), dim3(kRouterThreads), smem, s, a);
 }
 
 int router_splits_for(int T, int k_blocks, int max_splits) {

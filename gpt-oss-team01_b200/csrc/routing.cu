@@ -117,6 +117,8 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float *__restric
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * kTokensPerRouteBlock + warp;
   for (int e = threadIdx.x; e < d.E; e += blockDim.x) hist[e] = 0;
+  pdl_wait();
+  pdl_launch_dependents();
   __syncthreads();
   if (b < T) {
     float score[GROUPS];
@@ -191,6 +193,8 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
   const int E = d.E;
   const int nseg = 1024 / E;
   const int tid = threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   const int seg = tid / E, e = tid % E;
   const bool active = seg < nseg;
   const int per = (n_blocks + nseg - 1) / nseg;
@@ -244,6 +248,8 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
   const int k = d.k;
   const int first = blockIdx.x * kTokensPerRouteBlock * k;
   const int n = min(kTokensPerRouteBlock, T - blockIdx.x * kTokensPerRouteBlock) * k;
+  pdl_wait();
+  pdl_launch_dependents();
   for (int q = threadIdx.x; q < kTokensPerRouteBlock * k; q += blockDim.x)
     ids[q] = (q < n) ? topk_i[first + q] : -1;
   __syncthreads();
@@ -293,6 +299,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
                                                       float *__restrict__ x, int residual) {
   const int h4 = d.H >> 2;
   const size_t total = (size_t)T * h4;
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int b = (int)(i / h4), c = (int)(i % h4);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -333,9 +341,10 @@ cudaError_t launch_router_topk(const float *partials, int n_splits, const float 
                                const RouteBuffers &rb, cudaStream_t s) {
   const int groups = (d.E + 31) / 32;
   const dim3 grid(route_blocks(T)), block(256);
+  cudaError_t err = cudaSuccess;
 #define GPTOSS_ROUTER_CASE(G)                                                            \
   case G:                                                                                \
-    router_topk_kernel<G><<<grid, block, 0, s>>>(partials, n_splits, br, T, d, rb);      \
+    err = launch_chain(router_topk_kernel<G>, grid, block, 0, s, partials, n_splits, br, T, d, rb); \
     break;
   switch (groups) {
     GPTOSS_ROUTER_CASE(1)
@@ -350,7 +359,7 @@ cudaError_t launch_router_topk(const float *partials, int n_splits, const float 
       return cudaErrorInvalidValue;
   }
 #undef GPTOSS_ROUTER_CASE
-  return cudaGetLastError();
+  return err;
 }
 
 cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
@@ -383,15 +392,14 @@ cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_h
 }
 
 cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, cudaStream_t s) {
-  expert_scan_kernel<<<1, 1024, 0, s>>>(rb, route_blocks(T), d);
-  return cudaGetLastError();
+  return launch_chain(expert_scan_kernel, dim3(1), dim3(1024), 0, s, rb, route_blocks(T), d);
 }
 
 cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int T, const Dims &d,
                                   const int *blk_base, int *sorted, __nv_bfloat16 *x_packed,
                                   cudaStream_t s) {
-  scatter_gather_kernel<<<route_blocks(T), t ? 1024 : 256, 0, s>>>(t, topk_i, T, d, blk_base, sorted, x_packed);
-  return cudaGetLastError();
+  return launch_chain(scatter_gather_kernel, dim3(route_blocks(T)), dim3(t ? 1024 : 256), 0, s, t, topk_i, T, d,
+                      blk_base, sorted, x_packed);
 }
 
 cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
@@ -401,8 +409,7 @@ cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const
   const int cap = sm_count * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  combine_kernel<<<blocks, 256, 0, s>>>(y_pairs, topk_i, T, d, x, residual);
-  return cudaGetLastError();
+  return launch_chain(combine_kernel, dim3(blocks), dim3(256), 0, s, y_pairs, topk_i, T, d, x, residual);
 }
 
 // ---- allocation-free grouping -----------------------------------------------------------------------------

@@ -31,7 +31,11 @@ extern "C" {
 #define GPTOSS_ERR_UNSUPPORTED 4 /* device is not compute capability 10.x                            */
 #define GPTOSS_ERR_STATE 5       /* call out of order (e.g. forward before the layer has weights)    */
 
-/* wire format of the cross-GPU combine payload */
+/* wire format of the cross-GPU combine: the gate-weighted rows always travel to the owner in fp32 and are
+ * summed there in fp32; this selects the format in which the owner delivers the summed rows to every rank.
+ * F32: the result equals the single-GPU block bit for bit.  BF16: half the delivered bytes; every rank
+ * (the owner included) adds the same bf16-rounded sums, so the replicated residual streams stay identical.
+ * (The reference sends e5m2 and also ACCUMULATES in it at every hop, parallelism.cpp:53-68.) */
 #define GPTOSS_WIRE_F32 0
 #define GPTOSS_WIRE_BF16 1
 

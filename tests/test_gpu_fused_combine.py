@@ -75,3 +75,35 @@ def test_wait_on_a_silent_peer_times_out_as_status():
     assert torch.isfinite(part).all()
     for b in ranks:
         b.close()
+
+
+def test_bf16_delivery_keeps_ranks_identical_and_close_to_fp32():
+    from gptoss_b200 import capi, moe
+    H, I, E, k, T, world = 256, 192, 16, 4, 300, 4
+    w = synth.MoELayerWeights(H, I, E, 71, sigma=0.05)
+    single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)
+    single.upload_layer(0, w)
+    ranks = [moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, rank=r, world=world,
+                          wire=capi.WIRE_BF16) for r in range(world)]
+    for b in ranks:
+        b.upload_layer(0, w)
+    moe.MoEBlock.attach_local(ranks)
+    t_dev = to_dev_bf16(synth.activations(72, T, H))
+    want = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    single.forward(0, t_dev, want)
+    xs = [torch.zeros((T, H), dtype=torch.float32, device="cuda") for _ in range(world)]
+    for b in ranks:
+        b.route(0, t_dev)
+        b.mlp1_swiglu(0)
+        b.push_to_owners(0)
+    for b in ranks:
+        b.owner_combine()
+    for b, x in zip(ranks, xs):
+        b.add_delta(x)
+        b.status()
+    for x in xs[1:]:
+        assert torch.equal(x, xs[0])                      # replicated residual streams stay identical
+    # exactly the fp32 result rounded to bf16 (x started at zero)
+    assert torch.equal(xs[0], want.to(torch.bfloat16).to(torch.float32))
+    for b in ranks + [single]:
+        b.close()
