@@ -14,7 +14,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 # GPTOSS_B200_LIB points the binding at another build of the same C ABI (e.g. a tuning variant)
 LIB_PATH = Path(os.environ.get("GPTOSS_B200_LIB", CSRC / "libgptoss_b200.so"))
-SOURCES = ["routing.cu", "router.cu", "grouped_gemm.cu", "comm.cu", "convert.cu", "capi.cu"]
+SOURCES = ["routing.cu", "router.cu", "grouped_gemm.cu", "comm.cu", "convert.cu", "capi.cu", "model_kernels.cu",
+           "model.cu"]
 HEADERS = ["common.cuh", "kernels.cuh", "tcgen05.cuh", "../../include/gptoss_b200.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--threads", "4"]
@@ -35,8 +36,19 @@ EXPORTS = [
     "gptoss_synth_normal_bf16", "gptoss_version", "gptoss_moe_build_offsets_noalloc",
     "gptoss_noalloc_last_error", "gptoss_comm_export", "gptoss_comm_attach",
     "gptoss_comm_attach_local", "gptoss_comm_set_timeout_ms", "gptoss_moe_push_to_owners",
-    "gptoss_moe_owner_combine", "gptoss_moe_add_delta",
+    "gptoss_moe_owner_combine", "gptoss_moe_add_delta", "gptoss_model_create", "gptoss_model_destroy",
+    "gptoss_model_last_error", "gptoss_model_load_bin", "gptoss_model_fill_synthetic", "gptoss_model_step",
+    "gptoss_model_read_logits",
 ]
+
+
+class ModelConfig(C.Structure):
+    """The 15-field checkpoint header (run.cpp:25-45)."""
+    _fields_ = [(n, C.c_int) for n in ("vocab_size", "hidden_dim", "n_experts", "experts_per_token",
+                                       "intermediate_dim", "n_layers", "head_dim", "n_attn_heads", "n_kv_heads",
+                                       "seq_len", "initial_context_length")] + \
+               [("rope_theta", C.c_float), ("rope_scaling_factor", C.c_float), ("sliding_window", C.c_int),
+                ("swiglu_limit", C.c_float)]
 
 
 class MoEDims(C.Structure):
@@ -109,6 +121,13 @@ def load() -> C.CDLL:
         "gptoss_moe_push_to_owners": ([ctxp, i32, vp], i32),
         "gptoss_moe_owner_combine": ([ctxp, vp], i32),
         "gptoss_moe_add_delta": ([ctxp, vp, vp], i32),
+        "gptoss_model_create": ([C.POINTER(ModelConfig), i32, i32, i32, C.POINTER(vp)], i32),
+        "gptoss_model_destroy": ([vp], i32),
+        "gptoss_model_last_error": ([vp], C.c_char_p),
+        "gptoss_model_load_bin": ([vp, C.c_char_p], i32),
+        "gptoss_model_fill_synthetic": ([vp, u64, f32], i32),
+        "gptoss_model_step": ([vp, vp, i32, i32, vp], i32),
+        "gptoss_model_read_logits": ([vp, i32, vp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         }
         epilogue_bar_sync();
       }
-      const float bias0 = f_ok ? a.bias_a[(size_t)t.e * a.n_feat + f] : 0.f;
+      const float bias0 = (f_ok && a.bias_a) ? a.bias_a[(size_t)t.e * a.n_feat + f] : 0.f;  // a null bias means none
       const float bias1 = (NA == 2 && f_ok) ? a.bias_b[(size_t)t.e * a.n_feat + f] : 0.f;
       mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
       tc_fence_after();

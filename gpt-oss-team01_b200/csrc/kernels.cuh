@@ -110,6 +110,18 @@ cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s)
 cudaError_t encode_weight_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs);
 cudaError_t encode_act_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows);
 
+// model_kernels.cu — the kernels around the MoE block that a decode step needs
+cudaError_t launch_embed(const int *tokens, const __nv_bfloat16 *table, int B, int H, int vocab, float *x, cudaStream_t s);
+cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, int B, int H, __nv_bfloat16 *out,
+                                    cudaStream_t s);
+cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
+                                  int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
+                                  cudaStream_t s);
+cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
+                             int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s);
+cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s);
+cudaError_t launch_iota_ones(int *iota, float *ones, int n, cudaStream_t s);
+
 // convert.cu
 cudaError_t launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t s);
 cudaError_t launch_bf16_to_f32(const __nv_bfloat16 *src, float *dst, size_t n, cudaStream_t s);

@@ -1,0 +1,402 @@
+// Whole-model decode step around the MoE block: the B200 counterpart of forward_gpu_20b_batched
+// (getp-csrc/src/model.cpp:6-151) and of the CPU forward() (run.cpp:501-717), for ONE GPU.
+//
+// Per step (all sequences at the same position, prompt tokens force-fed by the caller — the reference's
+// lock-step decode): embedding -> per layer [RMSNorm -> QKV GEMM -> RoPE + KV store -> single-query attention
+// with sinks / sliding window -> o-proj GEMM -> residual + RMSNorm -> MoE block] -> final RMSNorm ->
+// classifier GEMM -> argmax.  The dense GEMMs (QKV, o-proj, classifier) run on the same tcgen05 kernel as the
+// expert down-projection: one "expert" holding every row, identity permutation, weight 1.
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+
+using namespace gptoss;
+
+struct gptoss_model {
+  gptoss_model_config c;
+  int device = 0, max_batch = 0, S = 0, sm_count = kSmCountFallback;
+  gptoss_ctx *moe = nullptr;
+  // weights
+  __nv_bfloat16 *emb = nullptr, *unemb = nullptr, *w_qkv = nullptr, *w_o = nullptr;
+  float *attn_norm = nullptr, *mlp_norm = nullptr, *final_norm = nullptr, *b_qkv = nullptr, *b_o = nullptr, *sinks = nullptr;
+  std::vector<CUtensorMap> map_qkv, map_o;
+  CUtensorMap map_unemb, map_t, map_att;
+  float *cos_t = nullptr, *sin_t = nullptr;
+  __nv_bfloat16 *k_cache = nullptr, *v_cache = nullptr;
+  // scratch
+  float *x = nullptr, *qkv = nullptr, *q = nullptr, *proj = nullptr, *logits = nullptr, *ones = nullptr, *staging = nullptr;
+  __nv_bfloat16 *t = nullptr, *att = nullptr;
+  int *tokens_dev = nullptr, *next_dev = nullptr, *iota = nullptr, *dense_off = nullptr, *dense_tbp = nullptr, *status = nullptr;
+  int cur_B = -1;
+  cudaStream_t stream = nullptr;
+  bool weights_ready = false;
+  std::string err;
+  int fail(int code, const char *what, cudaError_t e = cudaSuccess) {
+    char buf[512];
+    if (e != cudaSuccess)
+      snprintf(buf, sizeof buf, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    else
+      snprintf(buf, sizeof buf, "%s", what);
+    err = buf;
+    return code;
+  }
+  int qkv_dim() const { return c.head_dim * (c.n_attn_heads + 2 * c.n_kv_heads); }
+};
+
+#define MK(call)                                                       \
+  do {                                                                 \
+    cudaError_t e_ = (call);                                           \
+    if (e_ != cudaSuccess) return m->fail(GPTOSS_ERR_CUDA, #call, e_); \
+  } while (0)
+
+namespace {
+
+constexpr size_t kStagingElems = 16u << 20;  // 64 MiB of fp32
+
+template <typename T>
+cudaError_t dalloc(T **p, size_t n) {
+  return cudaMalloc(reinterpret_cast<void **>(p), (n ? n : 1) * sizeof(T));
+}
+
+// host fp32 -> device bf16 / fp32 through the staging buffer
+int upload_bf16(gptoss_model *m, __nv_bfloat16 *dst, const float *src, size_t n) {
+  for (size_t o = 0; o < n; o += kStagingElems) {
+    const size_t c = n - o < kStagingElems ? n - o : kStagingElems;
+    MK(cudaMemcpy(m->staging, src + o, c * sizeof(float), cudaMemcpyHostToDevice));
+    MK(launch_f32_to_bf16(m->staging, dst + o, c, 0));
+  }
+  return GPTOSS_OK;
+}
+int upload_f32(gptoss_model *m, float *dst, const float *src, size_t n, bool round_bf16) {
+  MK(cudaMemcpy(dst, src, n * sizeof(float), cudaMemcpyHostToDevice));
+  if (round_bf16) MK(launch_round_bf16_f32(dst, dst, n, 0));
+  return GPTOSS_OK;
+}
+
+// cos/sin table with YaRN scaling (run.cpp:404-470), float arithmetic as in the reference
+void rope_tables(const gptoss_model_config &c, int S, std::vector<float> &cs, std::vector<float> &sn) {
+  const int half = c.head_dim / 2;
+  std::vector<float> inv(half);
+  float concentration = 1.0f;
+  const float base = c.rope_theta, scaling = c.rope_scaling_factor, init_ctx = (float)c.initial_context_length;
+  const float ntk_beta = 32.0f, ntk_alpha = 1.0f;
+  if (scaling > 1.0f) {
+    concentration = 0.1f * logf(scaling) + 1.0f;
+    const float low = half * logf(init_ctx / (ntk_beta * 2.0f * (float)M_PI)) / logf(base);
+    const float high = half * logf(init_ctx / (ntk_alpha * 2.0f * (float)M_PI)) / logf(base);
+    for (int i = 0; i < half; ++i) {
+      const float freq = powf(base, ((float)(2 * i)) / (float)c.head_dim);
+      const float interpolation = 1.0f / (scaling * freq), extrapolation = 1.0f / freq;
+      float ramp = ((float)i - low) / (high - low);
+      ramp = ramp < 0 ? 0 : (ramp > 1 ? 1 : ramp);
+      const float mask = 1.0f - ramp;
+      inv[i] = interpolation * (1.0f - mask) + extrapolation * mask;
+    }
+  } else {
+    for (int i = 0; i < half; ++i) inv[i] = 1.0f / powf(base, ((float)(2 * i)) / (float)c.head_dim);
+  }
+  cs.resize((size_t)S * half);
+  sn.resize((size_t)S * half);
+  for (int p = 0; p < S; ++p)
+    for (int j = 0; j < half; ++j) {
+      const float v = (float)p * inv[j];
+      cs[(size_t)p * half + j] = cosf(v) * concentration;
+      sn[(size_t)p * half + j] = sinf(v) * concentration;
+    }
+}
+
+// out[B, n_out] (fp32) = act[B, K] (bf16) . W[n_out, K]^T + bias — the down-GEMM kernel with one "expert"
+int dense(gptoss_model *m, const CUtensorMap &map_w, const CUtensorMap &map_act, int K, int n_out, const float *bias,
+          float *out) {
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.map_w = map_w;
+  a.map_act = map_act;
+  a.offsets = m->dense_off;
+  a.tb_prefix = m->dense_tbp;
+  a.e_begin = 0;
+  a.n_local = 1;
+  a.n_feat = n_out;
+  a.n_feat_tiles = (n_out + kTileF - 1) / kTileF;
+  a.k_blocks = (K + kBlockK - 1) / kBlockK;
+  a.bias_a = bias;
+  a.y_pairs = out;
+  a.sorted = m->iota;
+  a.topk_w = m->ones;
+  a.status = m->status;
+  a.n_owners = 1;
+  a.top_k = 1;
+  a.slice_tokens = m->max_batch;
+  MK(launch_grouped_mlp2(a, m->sm_count, m->stream));
+  return GPTOSS_OK;
+}
+
+int set_batch(gptoss_model *m, int B) {
+  if (m->cur_B == B) return GPTOSS_OK;
+  const int off[2] = {0, B}, tbp[2] = {0, (B + kMaxTileTokens - 1) / kMaxTileTokens};
+  MK(cudaMemcpyAsync(m->dense_off, off, sizeof off, cudaMemcpyHostToDevice, m->stream));
+  MK(cudaMemcpyAsync(m->dense_tbp, tbp, sizeof tbp, cudaMemcpyHostToDevice, m->stream));
+  MK(cudaStreamSynchronize(m->stream));
+  MK(encode_map_2d(&m->map_t, m->t, m->c.hidden_dim, B, (uint32_t)kTokChunk));
+  MK(encode_map_2d(&m->map_att, m->att, (uint64_t)m->c.head_dim * m->c.n_attn_heads, B, (uint32_t)kTokChunk));
+  m->cur_B = B;
+  return GPTOSS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batch, int max_seq, gptoss_model **out) {
+  if (!cfg || !out) return GPTOSS_ERR_BAD_ARG;
+  *out = nullptr;
+  const gptoss_model_config &c = *cfg;
+  if (c.vocab_size <= 0 || c.hidden_dim <= 0 || c.hidden_dim % 8 || c.n_layers <= 0 || c.head_dim <= 0 || c.head_dim % 8 ||
+      c.head_dim > 64 || c.n_attn_heads <= 0 || c.n_kv_heads <= 0 || c.n_attn_heads % c.n_kv_heads ||
+      c.n_attn_heads / c.n_kv_heads > 8 || max_batch <= 0 || max_seq <= 0 || max_seq > c.seq_len)
+    return GPTOSS_ERR_BAD_ARG;
+  gptoss_model *m = new (std::nothrow) gptoss_model();
+  if (!m) return GPTOSS_ERR_CUDA;
+  m->c = c;
+  m->device = device;
+  m->max_batch = max_batch;
+  m->S = max_seq;
+  gptoss_moe_dims d{c.hidden_dim, c.intermediate_dim, c.n_experts, c.experts_per_token, c.n_layers, c.swiglu_limit};
+  int rc = gptoss_ctx_create(&d, device, 0, 1, max_batch, GPTOSS_WIRE_F32, &m->moe);
+  if (rc) {
+    delete m;
+    return rc;
+  }
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, device);
+  m->sm_count = prop.multiProcessorCount;
+  const size_t L = c.n_layers, H = c.hidden_dim, V = c.vocab_size, B = max_batch, S = max_seq;
+  const size_t qd = (size_t)c.head_dim * c.n_attn_heads, kvd = (size_t)c.head_dim * c.n_kv_heads, qkvd = qd + 2 * kvd;
+  cudaError_t e = cudaSuccess;
+  auto A = [&](cudaError_t r) {
+    if (e == cudaSuccess) e = r;
+  };
+  A(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+  A(dalloc(&m->emb, V * H));
+  A(dalloc(&m->unemb, V * H));
+  A(dalloc(&m->attn_norm, L * H));
+  A(dalloc(&m->mlp_norm, L * H));
+  A(dalloc(&m->final_norm, H));
+  A(dalloc(&m->w_qkv, L * qkvd * H));
+  A(dalloc(&m->b_qkv, L * qkvd));
+  A(dalloc(&m->w_o, L * H * qd));
+  A(dalloc(&m->b_o, L * H));
+  A(dalloc(&m->sinks, L * c.n_attn_heads));
+  A(dalloc(&m->cos_t, S * (c.head_dim / 2)));
+  A(dalloc(&m->sin_t, S * (c.head_dim / 2)));
+  A(dalloc(&m->k_cache, L * B * S * kvd));
+  A(dalloc(&m->v_cache, L * B * S * kvd));
+  A(dalloc(&m->x, B * H));
+  A(dalloc(&m->t, B * H));
+  A(dalloc(&m->qkv, B * qkvd));
+  A(dalloc(&m->q, B * qd));
+  A(dalloc(&m->att, B * qd));
+  A(dalloc(&m->proj, B * H));
+  A(dalloc(&m->logits, B * V));
+  A(dalloc(&m->tokens_dev, B));
+  A(dalloc(&m->next_dev, B));
+  A(dalloc(&m->iota, B));
+  A(dalloc(&m->ones, B));
+  A(dalloc(&m->dense_off, 2));
+  A(dalloc(&m->dense_tbp, 2));
+  A(dalloc(&m->status, kStatusWords));
+  A(dalloc(&m->staging, kStagingElems));
+  if (e == cudaSuccess) A(cudaMemset(m->status, 0, kStatusWords * sizeof(int)));
+  if (e == cudaSuccess) A(cudaMemset(m->k_cache, 0, L * B * S * kvd * sizeof(__nv_bfloat16)));
+  if (e == cudaSuccess) A(cudaMemset(m->v_cache, 0, L * B * S * kvd * sizeof(__nv_bfloat16)));
+  if (e == cudaSuccess) A(launch_iota_ones(m->iota, m->ones, (int)B, 0));
+  m->map_qkv.resize(L);
+  m->map_o.resize(L);
+  for (size_t l = 0; l < L && e == cudaSuccess; ++l) {
+    A(encode_weight_map(&m->map_qkv[l], m->w_qkv + l * qkvd * H, H, qkvd, 1));
+    A(encode_weight_map(&m->map_o[l], m->w_o + l * H * qd, qd, H, 1));
+  }
+  if (e == cudaSuccess) A(encode_weight_map(&m->map_unemb, m->unemb, H, V, 1));
+  if (e == cudaSuccess) {
+    std::vector<float> cs, sn;
+    rope_tables(c, (int)S, cs, sn);
+    A(cudaMemcpy(m->cos_t, cs.data(), cs.size() * sizeof(float), cudaMemcpyHostToDevice));
+    A(cudaMemcpy(m->sin_t, sn.data(), sn.size() * sizeof(float), cudaMemcpyHostToDevice));
+  }
+  if (e == cudaSuccess) A(cudaDeviceSynchronize());
+  if (e != cudaSuccess) {
+    gptoss_model_destroy(m);
+    return GPTOSS_ERR_CUDA;
+  }
+  *out = m;
+  return GPTOSS_OK;
+}
+
+int gptoss_model_destroy(gptoss_model *m) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  cudaSetDevice(m->device);
+  cudaDeviceSynchronize();
+  if (m->moe) gptoss_ctx_destroy(m->moe);
+  void *ptrs[] = {m->emb, m->unemb, m->attn_norm, m->mlp_norm, m->final_norm, m->w_qkv, m->b_qkv, m->w_o, m->b_o, m->sinks,
+                  m->cos_t, m->sin_t, m->k_cache, m->v_cache, m->x, m->t, m->qkv, m->q, m->att, m->proj, m->logits,
+                  m->tokens_dev, m->next_dev, m->iota, m->ones, m->dense_off, m->dense_tbp, m->status, m->staging};
+  for (void *p : ptrs) cudaFree(p);
+  if (m->stream) cudaStreamDestroy(m->stream);
+  delete m;
+  return GPTOSS_OK;
+}
+
+const char *gptoss_model_last_error(const gptoss_model *m) {
+  if (!m) return "null model";
+  if (!m->err.empty()) return m->err.c_str();
+  return gptoss_last_error(m->moe);
+}
+
+// Loads every tensor of a flat checkpoint (header + fp32 tensors in the order of run.cpp:194-233); the header
+// must match the configuration the model was created with.
+int gptoss_model_load_bin(gptoss_model *m, const char *path) {
+  if (!m || !path) return GPTOSS_ERR_BAD_ARG;
+  MK(cudaSetDevice(m->device));
+  const int fd = open(path, O_RDONLY);
+  if (fd < 0) return m->fail(GPTOSS_ERR_BAD_ARG, "cannot open checkpoint");
+  struct stat st;
+  fstat(fd, &st);
+  void *map = mmap(nullptr, st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+  close(fd);
+  if (map == MAP_FAILED) return m->fail(GPTOSS_ERR_BAD_ARG, "mmap of checkpoint failed");
+  int rc = GPTOSS_OK;
+  const gptoss_model_config &c = m->c;
+  gptoss_model_config hdr;
+  memcpy(&hdr, map, sizeof hdr);
+  const size_t L = c.n_layers, H = c.hidden_dim, V = c.vocab_size, E = c.n_experts, I = c.intermediate_dim;
+  const size_t qd = (size_t)c.head_dim * c.n_attn_heads, kvd = (size_t)c.head_dim * c.n_kv_heads, qkvd = qd + 2 * kvd;
+  const size_t need = sizeof hdr + 4 * (2 * V * H + 2 * L * H + H + L * qkvd * H + L * qkvd + L * H * qd + L * H +
+                                        L * c.n_attn_heads + L * E * H + L * E + L * E * 2 * I * H + L * E * 2 * I +
+                                        L * E * H * I + L * E * H);
+  if (memcmp(&hdr, &c, 9 * sizeof(int)) != 0 || hdr.sliding_window != c.sliding_window || (size_t)st.st_size != need) {
+    munmap(map, st.st_size);
+    return m->fail(GPTOSS_ERR_BAD_ARG, "checkpoint header or size does not match the model configuration");
+  }
+  const float *p = reinterpret_cast<const float *>(static_cast<const char *>(map) + sizeof hdr);
+  auto take = [&](size_t n) {
+    const float *r = p;
+    p += n;
+    return r;
+  };
+  const float *emb = take(V * H), *unemb = take(V * H), *an = take(L * H), *mn = take(L * H), *fn = take(H);
+  const float *wqkv = take(L * qkvd * H), *bqkv = take(L * qkvd), *wo = take(L * H * qd), *bo = take(L * H);
+  const float *sinks = take(L * c.n_attn_heads), *wr = take(L * E * H), *br = take(L * E);
+  const float *w1 = take(L * E * 2 * I * H), *b1 = take(L * E * 2 * I), *w2 = take(L * E * H * I), *b2 = take(L * E * H);
+  if (!rc) rc = upload_bf16(m, m->emb, emb, V * H);
+  if (!rc) rc = upload_bf16(m, m->unemb, unemb, V * H);
+  if (!rc) rc = upload_f32(m, m->attn_norm, an, L * H, false);  // norm scales stay fp32 (alloc.cpp:17)
+  if (!rc) rc = upload_f32(m, m->mlp_norm, mn, L * H, false);
+  if (!rc) rc = upload_f32(m, m->final_norm, fn, H, false);
+  if (!rc) rc = upload_bf16(m, m->w_qkv, wqkv, L * qkvd * H);
+  if (!rc) rc = upload_f32(m, m->b_qkv, bqkv, L * qkvd, true);
+  if (!rc) rc = upload_bf16(m, m->w_o, wo, L * H * qd);
+  if (!rc) rc = upload_f32(m, m->b_o, bo, L * H, true);
+  if (!rc) rc = upload_f32(m, m->sinks, sinks, L * c.n_attn_heads, true);
+  for (size_t l = 0; l < L && !rc; ++l) {
+    rc = gptoss_upload_layer(m->moe, (int)l, wr + l * E * H, br + l * E, w1 + l * E * 2 * I * H, b1 + l * E * 2 * I,
+                             w2 + l * E * H * I, b2 + l * E * H);
+    if (rc) m->fail(rc, gptoss_last_error(m->moe));
+  }
+  cudaDeviceSynchronize();
+  munmap(map, st.st_size);
+  if (!rc) m->weights_ready = true;
+  return rc;
+}
+
+// Random-init weights generated on the device (N(0, sigma) rounded to bf16, RMSNorm scales 1.0); meant for
+// throughput runs of architectures whose checkpoint would not fit on the host.
+int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  MK(cudaSetDevice(m->device));
+  const gptoss_model_config &c = m->c;
+  const size_t L = c.n_layers, H = c.hidden_dim, V = c.vocab_size;
+  const size_t qd = (size_t)c.head_dim * c.n_attn_heads, kvd = (size_t)c.head_dim * c.n_kv_heads, qkvd = qd + 2 * kvd;
+  MK(launch_synth_normal(m->emb, V * H, seed, 64, 0, sigma, 0));
+  MK(launch_synth_normal(m->unemb, V * H, seed, 65, 0, sigma, 0));
+  std::vector<float> ones((L * H > H ? L * H : H), 1.0f);
+  MK(cudaMemcpy(m->attn_norm, ones.data(), L * H * sizeof(float), cudaMemcpyHostToDevice));
+  MK(cudaMemcpy(m->mlp_norm, ones.data(), L * H * sizeof(float), cudaMemcpyHostToDevice));
+  MK(cudaMemcpy(m->final_norm, ones.data(), H * sizeof(float), cudaMemcpyHostToDevice));
+  MK(launch_synth_normal(m->w_qkv, L * qkvd * H, seed, 69, 0, sigma, 0));
+  MK(launch_synth_normal_f32(m->b_qkv, L * qkvd, seed, 70, 0, sigma, 0));
+  MK(launch_synth_normal(m->w_o, L * H * qd, seed, 71, 0, sigma, 0));
+  MK(launch_synth_normal_f32(m->b_o, L * H, seed, 72, 0, sigma, 0));
+  MK(launch_synth_normal_f32(m->sinks, L * c.n_attn_heads, seed, 73, 0, sigma, 0));
+  for (size_t l = 0; l < L; ++l) {
+    int rc = gptoss_fill_layer_synthetic(m->moe, (int)l, seed, sigma);
+    if (rc) return m->fail(rc, gptoss_last_error(m->moe));
+  }
+  MK(cudaDeviceSynchronize());
+  m->weights_ready = true;
+  return GPTOSS_OK;
+}
+
+// One lock-step decode step: tokens[B] at position `pos` -> greedy next tokens[B]
+// (forward_gpu_20b_batched, getp-csrc/src/model.cpp:6-151; CPU: forward + sample_argmax, run.cpp:501,739).
+int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (!tokens_host || !next_tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
+  if (B <= 0 || B > m->max_batch || pos < 0 || pos >= m->S) return m->fail(GPTOSS_ERR_BAD_ARG, "batch or position out of range");
+  if (!m->weights_ready) return m->fail(GPTOSS_ERR_STATE, "model has no weights yet");
+  MK(cudaSetDevice(m->device));
+  int rc = set_batch(m, B);
+  if (rc) return rc;
+  const gptoss_model_config &c = m->c;
+  const size_t L = c.n_layers, H = c.hidden_dim, S = m->S;
+  const int nq = c.n_attn_heads, nkv = c.n_kv_heads, hd = c.head_dim;
+  const size_t qd = (size_t)hd * nq, kvd = (size_t)hd * nkv, qkvd = qd + 2 * kvd;
+  cudaStream_t s = m->stream;
+  MK(cudaMemcpyAsync(m->tokens_dev, tokens_host, B * sizeof(int), cudaMemcpyHostToDevice, s));
+  MK(launch_embed(m->tokens_dev, m->emb, B, (int)H, c.vocab_size, m->x, s));
+  for (size_t l = 0; l < L; ++l) {
+    MK(launch_residual_rmsnorm(m->x, nullptr, m->attn_norm + l * H, B, (int)H, m->t, s));
+    if ((rc = dense(m, m->map_qkv[l], m->map_t, (int)H, (int)qkvd, m->b_qkv + l * qkvd, m->qkv))) return rc;
+    __nv_bfloat16 *kc = m->k_cache + l * (size_t)m->max_batch * S * kvd, *vc = m->v_cache + l * (size_t)m->max_batch * S * kvd;
+    MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, s));
+    const bool windowed = c.sliding_window > 0 && (l % 2 == 0);  // run.cpp:582
+    const int t_lo = windowed ? (pos - c.sliding_window + 1 > 0 ? pos - c.sliding_window + 1 : 0) : 0;
+    MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, s));
+    if ((rc = dense(m, m->map_o[l], m->map_att, (int)qd, (int)H, m->b_o + l * H, m->proj))) return rc;
+    MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
+    if ((rc = gptoss_moe_forward(m->moe, (int)l, B, m->t, m->x, s))) return m->fail(rc, gptoss_last_error(m->moe));
+  }
+  MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, (int)H, m->t, s));
+  if ((rc = dense(m, m->map_unemb, m->map_t, (int)H, c.vocab_size, nullptr, m->logits))) return rc;
+  MK(launch_argmax(m->logits, B, c.vocab_size, m->next_dev, s));
+  MK(cudaMemcpyAsync(next_tokens_host, m->next_dev, B * sizeof(int), cudaMemcpyDeviceToHost, s));
+  int st[kStatusWords];
+  MK(cudaMemcpyAsync(st, m->status, sizeof st, cudaMemcpyDeviceToHost, s));
+  MK(cudaStreamSynchronize(s));
+  if (st[0] != 0) {
+    cudaMemset(m->status, 0, sizeof st);
+    return m->fail(GPTOSS_ERR_TIMEOUT, "device-side bounded wait gave up in a dense GEMM");
+  }
+  return gptoss_ctx_status(m->moe);
+}
+
+// Copies the logits of one sequence of the last step to the host (debug/parity tap).
+int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out) {
+  if (!m || !host_out) return GPTOSS_ERR_BAD_ARG;
+  if (row < 0 || row >= m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "row out of range");
+  MK(cudaSetDevice(m->device));
+  MK(cudaMemcpy(host_out, m->logits + (size_t)row * m->c.vocab_size, (size_t)m->c.vocab_size * sizeof(float),
+                cudaMemcpyDeviceToHost));
+  return GPTOSS_OK;
+}
+
+}  // extern "C"

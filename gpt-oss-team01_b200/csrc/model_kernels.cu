@@ -1,0 +1,251 @@
+// Bandwidth-bound kernels around the MoE block that a decode step needs end to end: embedding gather,
+// RMSNorm (with the residual add fused), QKV split + rotary embedding + KV-cache store, single-query
+// attention with learned sinks and a sliding window, and the per-row argmax of the logits.
+//
+// Each restates a piece of the reference CPU model (run.cpp) with the rounding points of the reference GPU
+// engine: activations that feed a GEMM are bf16, the residual stream, norms, softmax and accumulations fp32,
+// the KV cache bf16 (config.hpp KV16).
+#include <cfloat>
+
+#include "kernels.cuh"
+
+namespace gptoss {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+
+// x[b,:] = float(embedding[token_b,:])   (run.cpp:515-517)
+__global__ void __launch_bounds__(256) embed_kernel(const int *__restrict__ tokens, const __nv_bfloat16 *__restrict__ table,
+                                                    int H, int vocab, float *__restrict__ x) {
+  const int b = blockIdx.x;
+  int tok = tokens[b];
+  tok = min(max(tok, 0), vocab - 1);
+  const uint16_t *row = reinterpret_cast<const uint16_t *>(table) + (size_t)tok * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_f32(row[i]);
+}
+
+// Optional residual update followed by RMSNorm (run.cpp:304-317, 611-623):
+//   if (add) x[b,:] += add[b,:]            (projection output incl. its bias)
+//   out[b,:] = bf16( w[:] * (x[b,:] * rsqrt(mean(x^2) + 1e-5)) )
+// One block per row; the sum of squares is accumulated in fp32 per thread and reduced in double.
+__global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ add,
+                                                               const float *__restrict__ w, int H,
+                                                               __nv_bfloat16 *__restrict__ out) {
+  __shared__ double part[8];
+  const int b = blockIdx.x;
+  float *xr = x + (size_t)b * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = xr[i];
+    if (add) {
+      v += add[(size_t)b * H + i];
+      xr[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)ss;
+  __syncthreads();
+  double tot = 0.0;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
+  const float inv = 1.0f / sqrtf((float)(tot / H + 1e-5));
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)b * H + i] = __float2bfloat16_rn(w[i] * (inv * xr[i]));
+}
+
+// qkv[b, :] = (q heads | k heads | v heads), bias already added (run.cpp:534-557).  Rotates q and k with the
+// cos/sin of position `pos` (half-split pairs: element i pairs with i + hd/2), writes q as fp32 and k, v as
+// bf16 into the caches at [b, pos, kv_head*hd + i].
+__global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__restrict__ qkv, const float *__restrict__ cos_t,
+                                                             const float *__restrict__ sin_t, int pos, int nq, int nkv,
+                                                             int hd, int S, float *__restrict__ q_out,
+                                                             __nv_bfloat16 *__restrict__ k_cache,
+                                                             __nv_bfloat16 *__restrict__ v_cache) {
+  const int b = blockIdx.x;
+  const int half = hd >> 1;
+  const int qdim = nq * hd, kvdim = nkv * hd;
+  const float *row = qkv + (size_t)b * (qdim + 2 * kvdim);
+  const float *cs = cos_t + (size_t)pos * half, *sn = sin_t + (size_t)pos * half;
+  for (int i = threadIdx.x; i < (nq + nkv) * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;  // heads 0..nq-1 are q, nq.. are k
+    const float *src = row + (size_t)h * hd;
+    const float x1 = src[j], x2 = src[j + half], c = cs[j], s = sn[j];
+    const float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
+    if (h < nq) {
+      q_out[(size_t)b * qdim + h * hd + j] = o1;
+      q_out[(size_t)b * qdim + h * hd + j + half] = o2;
+    } else {
+      __nv_bfloat16 *dst = k_cache + ((size_t)b * S + pos) * kvdim + (h - nq) * hd;
+      dst[j] = __float2bfloat16_rn(o1);
+      dst[j + half] = __float2bfloat16_rn(o2);
+    }
+  }
+  const float *vsrc = row + qdim + kvdim;
+  __nv_bfloat16 *vdst = v_cache + ((size_t)b * S + pos) * kvdim;
+  for (int i = threadIdx.x; i < kvdim; i += blockDim.x) vdst[i] = __float2bfloat16_rn(vsrc[i]);
+}
+
+// Single-query attention for one (sequence, kv head): the kv_mul query heads that share the kv head are one
+// warp each (run.cpp:565-607).  Positions [t_lo, pos] (t_lo > 0 on sliding-window layers); one lane per
+// position for the scores, online softmax per 32 positions, lanes over the head dimension for the values;
+// the learned sink joins the softmax denominator only.  hd <= 64, hd % 8 == 0.
+__global__ void __launch_bounds__(256) attention_kernel(const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
+                                                        const __nv_bfloat16 *__restrict__ v_cache,
+                                                        const float *__restrict__ sinks, int pos, int t_lo, int nq,
+                                                        int nkv, int hd, int S, __nv_bfloat16 *__restrict__ out) {
+  extern __shared__ float q_s[];  // [kv_mul][hd]
+  const int b = blockIdx.x, kvh = blockIdx.y;
+  const int kv_mul = nq / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvdim = nkv * hd;
+  for (int i = threadIdx.x; i < kv_mul * hd; i += blockDim.x)
+    q_s[i] = q[(size_t)b * nq * hd + (size_t)kvh * kv_mul * hd + i];
+  __syncthreads();
+  if (warp >= kv_mul) return;
+  const int h = kvh * kv_mul + warp;
+  const float *qv = q_s + warp * hd;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * hd;
+  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * hd;
+
+  float m = -FLT_MAX, l = 0.f;
+  float acc0 = 0.f, acc1 = 0.f;  // output dims lane and lane + 32
+  for (int t0 = t_lo; t0 <= pos; t0 += 32) {
+    const int t = t0 + lane;
+    float s = -FLT_MAX;
+    if (t <= pos) {
+      const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)t * kvdim);
+      float dot = 0.f;
+      for (int c = 0; c < (hd >> 3); ++c) {
+        const uint4 kv4 = kr[c];
+        const uint32_t w[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          dot = fmaf(qv[c * 8 + 2 * e], __uint_as_float(w[e] << 16), dot);
+          dot = fmaf(qv[c * 8 + 2 * e + 1], __uint_as_float(w[e] & 0xffff0000u), dot);
+        }
+      }
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = __expf(m - m_new);
+    const float p = (t <= pos) ? __expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+    acc0 *= corr;
+    acc1 *= corr;
+    const int n_here = min(32, pos - t0 + 1);
+    for (int tt = 0; tt < n_here; ++tt) {
+      const float pt = __shfl_sync(0xffffffffu, p, tt);
+      const uint16_t *vr = vbase + (size_t)(t0 + tt) * kvdim;
+      if (lane < hd) acc0 = fmaf(pt, bf16_bits_to_f32(vr[lane]), acc0);
+      if (lane + 32 < hd) acc1 = fmaf(pt, bf16_bits_to_f32(vr[lane + 32]), acc1);
+    }
+    m = m_new;
+  }
+  // the sink is one more logit in the softmax whose value row is dropped (run.cpp:588-591)
+  const float sink = sinks[h];
+  const float m_fin = fmaxf(m, sink);
+  const float corr = __expf(m - m_fin);
+  const float denom = l * corr + __expf(sink - m_fin);
+  const float inv = corr / denom;
+  __nv_bfloat16 *o = out + (size_t)b * nq * hd + (size_t)h * hd;
+  if (lane < hd) o[lane] = __float2bfloat16_rn(acc0 * inv);
+  if (lane + 32 < hd) o[lane + 32] = __float2bfloat16_rn(acc1 * inv);
+}
+
+// next[b] = index of the FIRST maximum of logits[b,:]   (run.cpp:739-750)
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ next) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const int b = blockIdx.x;
+  const float *row = logits + (size_t)b * V;
+  float best = -FLT_MAX;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) {  // ascending i per thread: strict '>' keeps the lowest index
+      best = v;
+      idx = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) {
+      best = ov;
+      idx = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    bv[threadIdx.x >> 5] = best;
+    bi[threadIdx.x >> 5] = idx;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = (threadIdx.x < (blockDim.x >> 5)) ? bv[threadIdx.x] : -FLT_MAX;
+    idx = (threadIdx.x < (blockDim.x >> 5)) ? bi[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+      }
+    }
+    if (threadIdx.x == 0) next[b] = idx;
+  }
+}
+
+__global__ void iota_ones_kernel(int *__restrict__ iota, float *__restrict__ ones, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    iota[i] = i;
+    ones[i] = 1.0f;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_embed(const int *tokens, const __nv_bfloat16 *table, int B, int H, int vocab, float *x, cudaStream_t s) {
+  embed_kernel<<<B, 256, 0, s>>>(tokens, table, H, vocab, x);
+  return cudaGetLastError();
+}
+cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, int B, int H, __nv_bfloat16 *out,
+                                    cudaStream_t s) {
+  residual_rmsnorm_kernel<<<B, 256, 0, s>>>(x, add, w, H, out);
+  return cudaGetLastError();
+}
+cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
+                                  int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
+                                  cudaStream_t s) {
+  qkv_rope_store_kernel<<<B, 256, 0, s>>>(qkv, cos_t, sin_t, pos, nq, nkv, hd, S, q_out, k_cache, v_cache);
+  return cudaGetLastError();
+}
+cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
+                             int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s) {
+  const int kv_mul = nq / nkv;  // <= 8 (checked when the model is created): one warp per query head of the group
+  attention_kernel<<<dim3(B, nkv), kv_mul * 32, (size_t)kv_mul * hd * sizeof(float), s>>>(q, k_cache, v_cache, sinks, pos, t_lo,
+                                                                                        nq, nkv, hd, S, out);
+  return cudaGetLastError();
+}
+cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s) {
+  argmax_kernel<<<B, 1024, 0, s>>>(logits, V, next);
+  return cudaGetLastError();
+}
+cudaError_t launch_iota_ones(int *iota, float *ones, int n, cudaStream_t s) {
+  iota_ones_kernel<<<(n + 255) / 256, 256, 0, s>>>(iota, ones, n);
+  return cudaGetLastError();
+}
+
+}  // namespace gptoss

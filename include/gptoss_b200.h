@@ -198,6 +198,39 @@ int gptoss_read_tap(gptoss_ctx *ctx, int tap, void *host_dst, uint64_t bytes);
 int gptoss_synth_normal_bf16(void *dst_dev_bf16, uint64_t n, uint64_t seed, uint64_t tensor_id,
                              uint64_t start, float sigma, void *stream);
 
+/* ---- whole-model decode step (the callers either side of the MoE block) --------------------------------
+ * The checkpoint header (15 four-byte fields, run.cpp:25-45), field for field. */
+typedef struct {
+  int vocab_size, hidden_dim, n_experts, experts_per_token, intermediate_dim, n_layers, head_dim, n_attn_heads,
+      n_kv_heads, seq_len, initial_context_length;
+  float rope_theta, rope_scaling_factor;
+  int sliding_window;
+  float swiglu_limit;
+} gptoss_model_config;
+
+typedef struct gptoss_model gptoss_model;
+
+/* One GPU holding the whole model (weights bf16, KV cache bf16 [layer][sequence][position][kv_dim], scratch
+ * for max_batch sequences of at most max_seq positions).  Replaces build_transformer + our_init for the
+ * single-GPU (20B-style, data-parallel replica) engine: run.cpp:283, getp-csrc/src/alloc.cpp:1035.
+ * Limits: head_dim <= 64 and a multiple of 8, at most 8 query heads per kv head. */
+int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batch, int max_seq, gptoss_model **out);
+int gptoss_model_destroy(gptoss_model *m);
+const char *gptoss_model_last_error(const gptoss_model *m);
+/* load_checkpoint (run.cpp:235-281): reads a flat model.bin (header + fp32 tensors in the order of
+ * run.cpp:194-233); the header must match the configuration the model was created with. */
+int gptoss_model_load_bin(gptoss_model *m, const char *path);
+/* Random-init weights generated on the device (N(0,sigma) rounded to bf16, RMSNorm scales 1.0), for
+ * throughput runs of architectures whose fp32 checkpoint would not fit on the host. */
+int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma);
+/* One lock-step decode step for B sequences at position pos: host token ids in, greedy next token ids out
+ * (forward_gpu_20b_batched, getp-csrc/src/model.cpp:6-151 / include/model.hpp:9; CPU: forward +
+ * sample_argmax, run.cpp:501,739).  Prompt tokens are force-fed by the caller, one position per step, as
+ * in getp-csrc/submit/getp_run_submit.cpp:60-87.  Synchronous. */
+int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host);
+/* Logits (fp32 [vocab]) of one sequence of the last step; debug/parity tap (PRINT_LOGITS, getp_run.cpp:236). */
+int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out);
+
 /* Library build info: "gptoss_b200 <version> sm_100a". */
 const char *gptoss_version(void);
 

@@ -6,7 +6,8 @@ reference's run.cpp is compiled by oracle/Makefile into oracle/_ref/libref_cpu.s
 (export_model_bin/gpt-oss-7m/config.json).  After each position the state left by the last layer's
 MoE block (run.cpp:622-704) is captured: block input t, router scores, top-k ids, softmaxed gate
 weights and the block output e_agg.  The greedy continuation (32 random prompt ids, 64 generated
-tokens) is stored too.
+tokens) is stored too, together with, per position, the argmax token, the gap between the two largest
+logits and the logits at 64 fixed vocabulary ids (for the whole-model parity test).
 
 Run from the repository root:   python tests/golden/make_golden.py
 """
@@ -45,10 +46,14 @@ def main():
         sha = hashlib.sha256(path.read_bytes()).hexdigest()
         prompt = synth.uniform_ids(SEED, PROMPT_STREAM, N_PROMPT, cfg.vocab_size)
         h = ref.open(path)
-        ts, vs, ids, aggs, scs, gen = [], [], [], [], [], []
+        ts, vs, ids, aggs, scs, gen, nxts, margins, probes = [], [], [], [], [], [], [], [], []
+        logits = np.empty(cfg.vocab_size, np.float32)
+        probe_idx = synth.uniform_ids(SEED, PROMPT_STREAM + 1, 64, cfg.vocab_size)
         tok = int(prompt[0])
         for pos in range(N_PROMPT + N_GEN - 1):
-            nxt = ref.forward(h, tok, pos)
+            nxt = ref.forward(h, tok, pos, logits)
+            top2 = np.partition(logits, -2)[-2:]
+            nxts.append(nxt), margins.append(float(top2[1] - top2[0])), probes.append(logits[probe_idx].copy())
             t, v, i, agg, sc = ref.last_moe_state(h, H, E, k)
             ts.append(t), vs.append(v), ids.append(i), aggs.append(agg), scs.append(sc)
             if pos + 1 < N_PROMPT:
@@ -61,7 +66,9 @@ def main():
     np.savez_compressed(
         out, seed=SEED, layer=L - 1, checkpoint_sha256=np.frombuffer(bytes.fromhex(sha), np.uint8),
         prompt=prompt, generated=np.array(gen, np.int32), t=np.stack(ts), topk_v=np.stack(vs),
-        topk_i=np.stack(ids), e_agg=np.stack(aggs), router_score=np.stack(scs))
+        topk_i=np.stack(ids), e_agg=np.stack(aggs), router_score=np.stack(scs),
+        next_token=np.array(nxts, np.int32), top2_margin=np.array(margins, np.float32),
+        probe_idx=probe_idx, probe_logits=np.stack(probes))
     print(f"wrote {out} ({out.stat().st_size} bytes): {len(ts)} positions, {len(gen)} generated tokens")
     print("generated:", gen[:16], "...")
 
