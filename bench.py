@@ -385,6 +385,39 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """Whole-model batched greedy decode of the gpt-oss-20b architecture on ONE GPU (random-init weights generated
+    on the device): 1024 sequences of 128 random prompt ids force-fed one position per step, then 256 generated
+    tokens — BASELINE config 4 at N = 1.  Reported like the reference's getp mode: generated tokens / wall time of
+    the whole inference loop (getp-csrc/getp_eval.cpp:125-131)."""
+    import torch
+    from gptoss_b200 import binfmt, model
+    B, n_prompt, n_gen = args.decode_batch, args.decode_prompt, args.decode_gen
+    cfg = binfmt.config_20b(seq_len=1024)
+    if args.decode_layers:
+        cfg.n_layers = args.decode_layers
+    torch.cuda.set_device(0)
+    m = model.Model(cfg, device=0, max_batch=B, max_seq=n_prompt + n_gen)
+    m.fill_synthetic(SEED, SIGMA)
+    prompts = synth.uniform_ids(SEED, 11, B * n_prompt, cfg.vocab_size).reshape(B, n_prompt)
+    m.generate(prompts[:, :2], 2)  # warm-up: 3 steps
+    with ClockSampler(0) as clocks:
+        t0 = time.perf_counter()
+        out = m.generate(prompts, n_gen)
+        dt = time.perf_counter() - t0
+    steps = n_prompt + n_gen - 1
+    line = {"metric": "batched decode tok/s, gpt-oss-20b arch (whole model, greedy, lock-step)", "value": B * n_gen / dt,
+            "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": 1e3 * dt / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": f"gpt-oss-20b architecture, {cfg.n_layers} layers, batch {B} x {n_prompt} random prompt "
+                                   f"ids, greedy decode {n_gen} tokens; tokens in/out over host memory every step",
+                       "positions_per_second": B * steps / dt, "seed": SEED},
+            "clocks": clocks.summary(), "distinct_tokens_generated": int(len(np.unique(out)))}
+    m.close()
+    print_line(line)
+
+
 def main():
     # libraries (NCCL's version banner) may write to stdout; keep fd 1 for the ONE JSON line
     real_stdout = os.fdopen(os.dup(1), "w")
@@ -401,12 +434,20 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
                     help="N > 1: format in which owners deliver the summed rows (rows travel to the owner in fp32)")
+    ap.add_argument("--workload", choices=["moe_layer", "decode20b"], default="moe_layer",
+                    help="moe_layer: the MoE block (headline); decode20b: whole-model greedy decode on one GPU")
+    ap.add_argument("--decode-batch", type=int, default=1024)
+    ap.add_argument("--decode-prompt", type=int, default=128)
+    ap.add_argument("--decode-gen", type=int, default=256)
+    ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count (0 = 24)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
                     help="distinct layers of weights the steps rotate over (1 keeps a profiling run small)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode20b":
+        run_decode(args)
     else:
         run_ours(args)
 

@@ -116,3 +116,17 @@ def read(path: str):
     if off != mm.size:
         raise ValueError(f"{path}: expected {off} floats after the header, file holds {mm.size}")
     return c, out
+
+
+def write_synthetic_tokenizer(path: str, vocab_size: int) -> None:
+    """A stand-in ``tokenizer.bin`` in the reference's binary format (export_tokenizer_bin.py:128-138, reader
+    tokenizer.cpp:49-102): ``int32 max_token_length`` then, per token, ``float32 score, int32 len, bytes``.
+    The real vocabulary cannot be obtained offline, so tokens 0..255 are the single raw bytes (the reference
+    looks pieces up by their raw bytes, tokenizer.cpp:129-134,170-176; every text then encodes to its UTF-8
+    bytes, id = byte value) and the rest are unmergeable fillers (score -1e30, tokenizer.cpp:160-161)."""
+    with open(path, "wb") as f:
+        f.write(struct.pack("<i", 24))
+        for i in range(vocab_size):
+            s = bytes([i]) if i < 256 else f"<|synthetic_{i}|>".encode()
+            f.write(struct.pack("<fi", 0.0 if i < 256 else -1e30, len(s)))
+            f.write(s)

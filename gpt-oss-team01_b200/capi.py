@@ -37,7 +37,7 @@ EXPORTS = [
     "gptoss_noalloc_last_error", "gptoss_comm_export", "gptoss_comm_attach",
     "gptoss_comm_attach_local", "gptoss_comm_set_timeout_ms", "gptoss_moe_push_to_owners",
     "gptoss_moe_owner_combine", "gptoss_moe_add_delta", "gptoss_model_create", "gptoss_model_destroy",
-    "gptoss_model_last_error", "gptoss_model_load_bin", "gptoss_model_fill_synthetic", "gptoss_model_step",
+    "gptoss_model_last_error", "gptoss_model_load_bin", "gptoss_model_load_mem", "gptoss_model_fill_synthetic", "gptoss_model_step",
     "gptoss_model_read_logits",
 ]
 
@@ -125,6 +125,7 @@ def load() -> C.CDLL:
         "gptoss_model_destroy": ([vp], i32),
         "gptoss_model_last_error": ([vp], C.c_char_p),
         "gptoss_model_load_bin": ([vp, C.c_char_p], i32),
+        "gptoss_model_load_mem": ([vp, vp, u64], i32),
         "gptoss_model_fill_synthetic": ([vp, u64, f32], i32),
         "gptoss_model_step": ([vp, vp, i32, i32, vp], i32),
         "gptoss_model_read_logits": ([vp, i32, vp], i32),

@@ -262,32 +262,25 @@ const char *gptoss_model_last_error(const gptoss_model *m) {
   return gptoss_last_error(m->moe);
 }
 
-// Loads every tensor of a flat checkpoint (header + fp32 tensors in the order of run.cpp:194-233); the header
-// must match the configuration the model was created with.
-int gptoss_model_load_bin(gptoss_model *m, const char *path) {
-  if (!m || !path) return GPTOSS_ERR_BAD_ARG;
+// Loads every tensor of a flat checkpoint image already in host memory (header + fp32 tensors in the order of
+// run.cpp:194-233), e.g. the mapping the reference's load_checkpoint made (Transformer::data, run.cpp:274);
+// the header must match the configuration the model was created with.
+int gptoss_model_load_mem(gptoss_model *m, const void *image, uint64_t bytes) {
+  if (!m || !image) return GPTOSS_ERR_BAD_ARG;
   MK(cudaSetDevice(m->device));
-  const int fd = open(path, O_RDONLY);
-  if (fd < 0) return m->fail(GPTOSS_ERR_BAD_ARG, "cannot open checkpoint");
-  struct stat st;
-  fstat(fd, &st);
-  void *map = mmap(nullptr, st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
-  close(fd);
-  if (map == MAP_FAILED) return m->fail(GPTOSS_ERR_BAD_ARG, "mmap of checkpoint failed");
   int rc = GPTOSS_OK;
   const gptoss_model_config &c = m->c;
   gptoss_model_config hdr;
-  memcpy(&hdr, map, sizeof hdr);
+  if (bytes < sizeof hdr) return m->fail(GPTOSS_ERR_BAD_ARG, "checkpoint image shorter than its header");
+  memcpy(&hdr, image, sizeof hdr);
   const size_t L = c.n_layers, H = c.hidden_dim, V = c.vocab_size, E = c.n_experts, I = c.intermediate_dim;
   const size_t qd = (size_t)c.head_dim * c.n_attn_heads, kvd = (size_t)c.head_dim * c.n_kv_heads, qkvd = qd + 2 * kvd;
   const size_t need = sizeof hdr + 4 * (2 * V * H + 2 * L * H + H + L * qkvd * H + L * qkvd + L * H * qd + L * H +
                                         L * c.n_attn_heads + L * E * H + L * E + L * E * 2 * I * H + L * E * 2 * I +
                                         L * E * H * I + L * E * H);
-  if (memcmp(&hdr, &c, 9 * sizeof(int)) != 0 || hdr.sliding_window != c.sliding_window || (size_t)st.st_size != need) {
-    munmap(map, st.st_size);
+  if (memcmp(&hdr, &c, 9 * sizeof(int)) != 0 || hdr.sliding_window != c.sliding_window || bytes != need)
     return m->fail(GPTOSS_ERR_BAD_ARG, "checkpoint header or size does not match the model configuration");
-  }
-  const float *p = reinterpret_cast<const float *>(static_cast<const char *>(map) + sizeof hdr);
+  const float *p = reinterpret_cast<const float *>(static_cast<const char *>(image) + sizeof hdr);
   auto take = [&](size_t n) {
     const float *r = p;
     p += n;
@@ -313,8 +306,22 @@ int gptoss_model_load_bin(gptoss_model *m, const char *path) {
     if (rc) m->fail(rc, gptoss_last_error(m->moe));
   }
   cudaDeviceSynchronize();
-  munmap(map, st.st_size);
   if (!rc) m->weights_ready = true;
+  return rc;
+}
+
+// load_checkpoint (run.cpp:235-281): maps the file and loads it.
+int gptoss_model_load_bin(gptoss_model *m, const char *path) {
+  if (!m || !path) return GPTOSS_ERR_BAD_ARG;
+  const int fd = open(path, O_RDONLY);
+  if (fd < 0) return m->fail(GPTOSS_ERR_BAD_ARG, "cannot open checkpoint");
+  struct stat st;
+  fstat(fd, &st);
+  void *map = mmap(nullptr, st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+  close(fd);
+  if (map == MAP_FAILED) return m->fail(GPTOSS_ERR_BAD_ARG, "mmap of checkpoint failed");
+  const int rc = gptoss_model_load_mem(m, map, (uint64_t)st.st_size);
+  munmap(map, st.st_size);
   return rc;
 }
 

@@ -1,0 +1,145 @@
+// Drop-in replacement for the reference's getp-csrc/getp_run.cpp on NVIDIA B200: defines the three functions
+// the fixed harness getp-csrc/getp_eval.cpp declares and calls (getp_eval.cpp:97-145) —
+//     void warm_up(Transformer *, Tokenizer *);
+//     long long inference(Transformer *, Tokenizer *, Sampler *, Requests *);
+//     void finish(Transformer *, Tokenizer *);
+// — on top of the gptoss_b200 C ABI.  Like the file it replaces it is textually included by run.cpp
+// (run.cpp:1071-1072), so it sees the reference's Transformer/Config (run.cpp:25-117), Requests
+// (getp_eval.cpp:9-15) and encode() (tokenizer.hpp:45).
+//
+// Scheduling follows the reference's 20B engine (getp-csrc/submit/getp_run_submit.cpp:4-104): requests are
+// cut into batches, each batch decodes in lock-step from position 0, prompt tokens are force-fed one per
+// step, the first generated token lands at index 0 of the request's output row, a sequence stops at the
+// end-of-sequence ids 199999 / 200002, and each output row is terminated by -1 after generated_len + 1 ids.
+// Batches are spread over the visible GPUs as data-parallel replicas, one host thread and one model per GPU
+// (DP_20B, getp-csrc/include/config.hpp:16-19).  Batch size: environment GPTOSS_BATCH (default 1024).
+#include "getp_eval.cpp"
+
+#include <algorithm>
+#include <atomic>
+#include <thread>
+#include <vector>
+
+extern "C" {
+#include "gptoss_b200.h"
+}
+
+#ifndef GETP_RUN
+#define GETP_RUN
+
+namespace {
+
+std::vector<gptoss_model *> g_models;  // one per GPU
+int g_batch = 1024;
+int g_max_seq = 0;
+
+void die(const char *what, gptoss_model *m) {
+  fprintf(stderr, "gptoss_b200: %s: %s\n", what, m ? gptoss_model_last_error(m) : "");
+  exit(EXIT_FAILURE);
+}
+
+gptoss_model_config to_config(const Config &c) {
+  gptoss_model_config g;
+  static_assert(sizeof(gptoss_model_config) == sizeof(Config), "checkpoint header layout");
+  memcpy(&g, &c, sizeof g);
+  return g;
+}
+
+// One batch of requests [first, first + n) on one model, in lock-step.  Returns the token count the
+// reference reports (generated_len + 1 per request).
+long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg, Requests *reqs, int first, int n) {
+  const int max_seq_len = reqs->max_seq_len;
+  std::vector<std::vector<int>> prompt(n);
+  for (int i = 0; i < n; ++i) {
+    const char *text = get_str_req_ptr(reqs, first + i);
+    std::vector<int> buf(strlen(text) + 3);
+    int count = 0;
+    encode(tokenizer, text, -1, -1, buf.data(), &count, cfg.initial_context_length);
+    if (count < 1) {
+      fprintf(stderr, "something is wrong, expected at least 1 prompt token\n");
+      exit(EXIT_FAILURE);
+    }
+    prompt[i].assign(buf.begin(), buf.begin() + count);
+  }
+  std::vector<int> cur(n), next(n), pos_of(n, 0);
+  std::vector<char> active(n, 1);
+  int n_active = n;
+  for (int i = 0; i < n; ++i) cur[i] = prompt[i][0];
+  for (int pos = 0; pos < max_seq_len - 1 && n_active > 0; ++pos) {
+    if (gptoss_model_step(model, cur.data(), pos, n, next.data())) die("decode step failed", model);
+    for (int i = 0; i < n; ++i) {
+      if (!active[i]) continue;
+      int tok = next[i];
+      const int n_prompt = (int)prompt[i].size();
+      if (pos_of[i] < n_prompt - 1)
+        tok = prompt[i][pos_of[i] + 1];  // still inside the prompt: force-feed
+      else
+        get_tok_gen_ptr(reqs, first + i)[pos_of[i] - (n_prompt - 1)] = tok;
+      if (tok == 199999 || tok == 200002) {
+        active[i] = 0;
+        --n_active;
+      }
+      cur[i] = tok;
+      ++pos_of[i];
+    }
+  }
+  long long count = 0;
+  for (int i = 0; i < n; ++i) {
+    const int generated_len = std::max(0, pos_of[i] - (int)prompt[i].size());
+    get_tok_gen_ptr(reqs, first + i)[generated_len + 1] = -1;
+    count += generated_len + 1;
+  }
+  return count;
+}
+
+}  // namespace
+
+void warm_up(Transformer *transformer, Tokenizer *tokenizer) {
+  (void)tokenizer;
+  if (const char *b = getenv("GPTOSS_BATCH")) g_batch = std::max(1, atoi(b));
+  int n_gpus = 1;
+  if (const char *g = getenv("GPTOSS_GPUS")) n_gpus = std::max(1, atoi(g));
+  const Config &c = transformer->config;
+  g_max_seq = c.seq_len;
+  if (const char *s = getenv("GPTOSS_MAX_SEQ")) g_max_seq = std::min(c.seq_len, std::max(2, atoi(s)));
+  const gptoss_model_config gc = to_config(c);
+  for (int g = 0; g < n_gpus; ++g) {
+    gptoss_model *m = nullptr;
+    if (gptoss_model_create(&gc, g, g_batch, g_max_seq, &m)) die("cannot create the model (GPU count, memory, dimensions)", nullptr);
+    // the reference keeps the whole file mapped: header first, then the tensors (run.cpp:274-280)
+    if (gptoss_model_load_mem(m, transformer->data, (uint64_t)transformer->file_size)) die("cannot load the checkpoint", m);
+    g_models.push_back(m);
+  }
+}
+
+long long inference(Transformer *transformer, Tokenizer *tokenizer, Sampler *sampler, Requests *requests) {
+  (void)sampler;  // greedy, like the reference engine (argmax on the device)
+  const Config &cfg = transformer->config;
+  if (requests->max_seq_len > g_max_seq) {
+    fprintf(stderr, "gptoss_b200: %d steps requested but the KV cache holds %d positions (GPTOSS_MAX_SEQ)\n",
+            requests->max_seq_len, g_max_seq);
+    exit(EXIT_FAILURE);
+  }
+  const int n_batches = (requests->num_reqs + g_batch - 1) / g_batch;
+  std::atomic<int> next_batch{0};
+  std::atomic<long long> total{0};
+  std::vector<std::thread> workers;
+  for (gptoss_model *model : g_models)
+    workers.emplace_back([&, model] {
+      for (int b = next_batch++; b < n_batches; b = next_batch++) {
+        const int first = b * g_batch, n = std::min(g_batch, requests->num_reqs - first);
+        total += run_batch(model, tokenizer, cfg, requests, first, n);
+      }
+    });
+  for (auto &w : workers) w.join();
+  return total;
+}
+
+void finish(Transformer *transformer, Tokenizer *tokenizer) {
+  (void)transformer;
+  (void)tokenizer;
+  for (gptoss_model *m : g_models) gptoss_model_destroy(m);
+  g_models.clear();
+}
+
+#endif  // GETP_RUN

@@ -220,6 +220,9 @@ const char *gptoss_model_last_error(const gptoss_model *m);
 /* load_checkpoint (run.cpp:235-281): reads a flat model.bin (header + fp32 tensors in the order of
  * run.cpp:194-233); the header must match the configuration the model was created with. */
 int gptoss_model_load_bin(gptoss_model *m, const char *path);
+/* Same from a checkpoint image already in host memory — the mapping the reference keeps in
+ * Transformer::data (run.cpp:274,279: the header sits in front of the tensors). */
+int gptoss_model_load_mem(gptoss_model *m, const void *image, uint64_t bytes);
 /* Random-init weights generated on the device (N(0,sigma) rounded to bf16, RMSNorm scales 1.0), for
  * throughput runs of architectures whose fp32 checkpoint would not fit on the host. */
 int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma);

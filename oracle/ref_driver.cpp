@@ -107,6 +107,16 @@ int ref_moe_rows(const float *t, int row_begin, int row_end, const float *w_rout
   return row_end - row_begin;
 }
 
+// ---- tokenizer: read_tokenizer (tokenizer.cpp:49) + encode (tokenizer.cpp:268) ---------------------------------
+int ref_encode(const char *tokenizer_path, int vocab_size, const char *text, int *out, int max_tokens) {
+  Tokenizer t;
+  read_tokenizer(&t, tokenizer_path, vocab_size);
+  int n = 0;
+  encode(&t, text, -1, -1, out, &n, max_tokens);
+  free_tokenizer(&t);
+  return n;
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -149,6 +149,15 @@ class Reference:
                                      C.c_void_p]
         lib.ref_moe_rows.restype = C.c_int
         lib.ref_num_threads.restype = C.c_int
+        lib.ref_encode.argtypes = [C.c_char_p, C.c_int, C.c_char_p, C.c_void_p, C.c_int]
+        lib.ref_encode.restype = C.c_int
+
+    def encode(self, tokenizer_path, vocab_size, text, max_tokens=4096):
+        """read_tokenizer + encode of the reference (tokenizer.cpp:49,268), no BOS/EOS."""
+        out = np.zeros(max_tokens, np.int32)
+        n = self.lib.ref_encode(str(tokenizer_path).encode(), vocab_size, text.encode(), out.ctypes.data_as(C.c_void_p),
+                                max_tokens)
+        return out[:n].tolist()
 
     def open(self, path):
         return self.lib.ref_open(str(path).encode())

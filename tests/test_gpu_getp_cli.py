@@ -1,0 +1,67 @@
+"""The reference's own command line (run.cpp + tokenizer.cpp + getp_eval.cpp) linked with this repository's
+getp_run.cpp: `run_b200 model.bin -z tokenizer.bin -m getp -i in.txt -o out.txt -n steps` must write the
+token ids that the same model produces when driven step by step from Python with the scheduler's rules
+(lock-step positions, prompt tokens force-fed, first generated token at index 0, -1 terminator)."""
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from gptoss_b200 import binfmt
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+EXE = Path(__file__).resolve().parent.parent / "gpt-oss-team01_b200" / "host" / "_ref_build" / "run_b200"
+
+
+@pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")
+def test_getp_mode_writes_the_tokens_of_the_stepwise_decode(tmp_path):
+    from gptoss_b200 import model
+    cfg = binfmt.config_7m()
+    ckpt, tok, inp, out = (tmp_path / n for n in ("m.bin", "tokenizer.bin", "in.txt", "out.txt"))
+    binfmt.write_synthetic(str(ckpt), cfg, 4242)
+    binfmt.write_synthetic_tokenizer(str(tok), cfg.vocab_size)
+    prompts = ["hello world", "a", "The quick brown fox", "B200", "mixture of experts"]
+    inp.write_text(f"{len(prompts)}\n" + "\n".join(prompts) + "\n")
+    steps = 40
+    r = subprocess.run([str(EXE), str(ckpt), "-z", str(tok), "-m", "getp", "-i", str(inp), "-o", str(out), "-n", str(steps)],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
+                       env={"GPTOSS_BATCH": "4", "GPTOSS_MAX_SEQ": str(steps), "PATH": "/usr/bin:/bin"})
+    assert r.returncode == 0, r.stdout[-2000:]
+    assert "achieved throughput TPS" in r.stdout
+    got = [[int(x) for x in line.split()] for line in out.read_text().splitlines()]
+    assert len(got) == len(prompts)
+
+    # the same schedule from Python: batches of 4 (GPTOSS_BATCH), positions 0 .. steps-2
+    m = model.Model(cfg, max_batch=4, max_seq=steps)
+    m.load_bin(ckpt)
+    want = []
+    for first in range(0, len(prompts), 4):
+        batch = [list(p.encode()) for p in prompts[first:first + 4]]
+        n = len(batch)
+        cur = np.array([b[0] for b in batch], np.int32)
+        pos_of, active, outs = [0] * n, [True] * n, [[] for _ in range(n)]
+        for pos in range(steps - 1):
+            if not any(active):
+                break
+            nxt = m.step(cur, pos)
+            for i in range(n):
+                if not active[i]:
+                    continue
+                t = int(nxt[i])
+                if pos_of[i] < len(batch[i]) - 1:
+                    t = batch[i][pos_of[i] + 1]
+                else:
+                    outs[i].append(t)
+                if t in (199999, 200002):
+                    active[i] = False
+                cur[i] = t
+                pos_of[i] += 1
+        for i in range(n):
+            gen_len = max(0, pos_of[i] - len(batch[i]))
+            want.append(outs[i][:gen_len + 1])
+    m.close()
+    assert got == want

@@ -70,3 +70,11 @@ def test_c_generator_matches_numpy_generator(oracle):
     ref = synth.MoELayerWeights(32, 64, 8, 5)
     for n in ("router_w", "router_b", "mlp1_w", "mlp1_b", "mlp2_w", "mlp2_b"):
         assert np.array_equal(getattr(w, n), getattr(ref, n)), n
+
+
+def test_synthetic_tokenizer_file_encodes_text_to_its_bytes_with_the_reference_encoder(reference, tmp_path):
+    from gptoss_b200 import binfmt
+    p = tmp_path / "tokenizer.bin"
+    binfmt.write_synthetic_tokenizer(str(p), 201088)
+    for text in ["hello world", "The quick brown fox", "x 12345 y", "B200"]:
+        assert reference.encode(p, 201088, text) == list(text.encode())
