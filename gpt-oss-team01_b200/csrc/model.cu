@@ -161,9 +161,10 @@ int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batc
   if (!cfg || !out) return GPTOSS_ERR_BAD_ARG;
   *out = nullptr;
   const gptoss_model_config &c = *cfg;
-  if (c.vocab_size <= 0 || c.hidden_dim <= 0 || c.hidden_dim % 8 || c.n_layers <= 0 || c.head_dim <= 0 || c.head_dim % 8 ||
-      c.head_dim > 64 || c.n_attn_heads <= 0 || c.n_kv_heads <= 0 || c.n_attn_heads % c.n_kv_heads ||
-      c.n_attn_heads / c.n_kv_heads > 8 || max_batch <= 0 || max_seq <= 0 || max_seq > c.seq_len)
+  if (c.vocab_size <= 0 || c.hidden_dim <= 0 || c.hidden_dim % 8 || c.n_layers <= 0 || (c.head_dim != 32 && c.head_dim != 64) ||
+      c.n_attn_heads <= 0 || c.n_kv_heads <= 0 || c.n_attn_heads % c.n_kv_heads ||
+      (c.n_attn_heads / c.n_kv_heads != 1 && c.n_attn_heads / c.n_kv_heads != 2 && c.n_attn_heads / c.n_kv_heads != 4 &&
+       c.n_attn_heads / c.n_kv_heads != 8) || max_batch <= 0 || max_seq <= 0 || max_seq > c.seq_len)
     return GPTOSS_ERR_BAD_ARG;
   gptoss_model *m = new (std::nothrow) gptoss_model();
   if (!m) return GPTOSS_ERR_CUDA;
@@ -357,7 +358,7 @@ int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma) {
 // (forward_gpu_20b_batched, getp-csrc/src/model.cpp:6-151; CPU: forward + sample_argmax, run.cpp:501,739).
 int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host) {
   if (!m) return GPTOSS_ERR_BAD_ARG;
-  if (!tokens_host || !next_tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
+  if (!tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
   if (B <= 0 || B > m->max_batch || pos < 0 || pos >= m->S) return m->fail(GPTOSS_ERR_BAD_ARG, "batch or position out of range");
   if (!m->weights_ready) return m->fail(GPTOSS_ERR_STATE, "model has no weights yet");
   MK(cudaSetDevice(m->device));
@@ -382,10 +383,12 @@ int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, i
     MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
     if ((rc = gptoss_moe_forward(m->moe, (int)l, B, m->t, m->x, s))) return m->fail(rc, gptoss_last_error(m->moe));
   }
-  MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, (int)H, m->t, s));
-  if ((rc = dense(m, m->map_unemb, m->map_t, (int)H, c.vocab_size, nullptr, m->logits))) return rc;
-  MK(launch_argmax(m->logits, B, c.vocab_size, m->next_dev, s));
-  MK(cudaMemcpyAsync(next_tokens_host, m->next_dev, B * sizeof(int), cudaMemcpyDeviceToHost, s));
+  if (next_tokens_host) {  // a step whose outputs are all overridden by prompt tokens needs no logits
+    MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, (int)H, m->t, s));
+    if ((rc = dense(m, m->map_unemb, m->map_t, (int)H, c.vocab_size, nullptr, m->logits))) return rc;
+    MK(launch_argmax(m->logits, B, c.vocab_size, m->next_dev, s));
+    MK(cudaMemcpyAsync(next_tokens_host, m->next_dev, B * sizeof(int), cudaMemcpyDeviceToHost, s));
+  }
   int st[kStatusWords];
   MK(cudaMemcpyAsync(st, m->status, sizeof st, cudaMemcpyDeviceToHost, s));
   MK(cudaStreamSynchronize(s));

@@ -95,72 +95,125 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
   for (int i = threadIdx.x; i < kvdim; i += blockDim.x) vdst[i] = __float2bfloat16_rn(vsrc[i]);
 }
 
-// Single-query attention for one (sequence, kv head): the kv_mul query heads that share the kv head are one
-// warp each (run.cpp:565-607).  Positions [t_lo, pos] (t_lo > 0 on sliding-window layers); one lane per
-// position for the scores, online softmax per 32 positions, lanes over the head dimension for the values;
-// the learned sink joins the softmax denominator only.  hd <= 64, hd % 8 == 0.
-__global__ void __launch_bounds__(256) attention_kernel(const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
+// Single-query attention for one (sequence, kv head) (run.cpp:565-607).  Memory-bound: every K and V row of
+// the cache is read once per kv head and serves all kv_mul query heads of the group from registers.  The
+// positions [t_lo, pos] (t_lo > 0 on sliding-window layers) are dealt out in chunks of 32 to the 4 warps of
+// the block; within a chunk one lane owns one position for the scores (its K row in registers, the queries
+// broadcast from shared memory) and the lanes own the head dimension for the values; online softmax per
+// head; the warps' partial (max, sum, accumulator) are merged through shared memory, where the learned sink
+// joins the denominator only (run.cpp:588-591).  HD = head_dim (32 or 64), KVM = query heads per kv head.
+template <int HD, int KVM>
+__global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
                                                         const __nv_bfloat16 *__restrict__ v_cache,
                                                         const float *__restrict__ sinks, int pos, int t_lo, int nq,
-                                                        int nkv, int hd, int S, __nv_bfloat16 *__restrict__ out) {
-  extern __shared__ float q_s[];  // [kv_mul][hd]
+                                                        int nkv, int S, __nv_bfloat16 *__restrict__ out) {
+  constexpr int DPL = HD / 32;  // output dims per lane
+  constexpr int NW = 4;
+  __shared__ __align__(16) float q_s[KVM * HD];
+  __shared__ float m_s[NW][KVM], l_s[NW][KVM], acc_s[NW][KVM][HD];
   const int b = blockIdx.x, kvh = blockIdx.y;
-  const int kv_mul = nq / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvdim = nkv * hd;
-  for (int i = threadIdx.x; i < kv_mul * hd; i += blockDim.x)
-    q_s[i] = q[(size_t)b * nq * hd + (size_t)kvh * kv_mul * hd + i];
+  const int kvdim = nkv * HD;
+  for (int i = threadIdx.x; i < KVM * HD; i += blockDim.x) q_s[i] = q[(size_t)b * nq * HD + (size_t)kvh * KVM * HD + i];
   __syncthreads();
-  if (warp >= kv_mul) return;
-  const int h = kvh * kv_mul + warp;
-  const float *qv = q_s + warp * hd;
-  const float scale = 1.0f / sqrtf((float)hd);
-  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * hd;
-  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * hd;
+  const float scale = 1.0f / sqrtf((float)HD);
+  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * HD;
+  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * HD;
 
-  float m = -FLT_MAX, l = 0.f;
-  float acc0 = 0.f, acc1 = 0.f;  // output dims lane and lane + 32
-  for (int t0 = t_lo; t0 <= pos; t0 += 32) {
+  float m[KVM], l[KVM], acc[KVM][DPL];
+#pragma unroll
+  for (int h = 0; h < KVM; ++h) {
+    m[h] = -FLT_MAX;
+    l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
+  }
+  for (int t0 = t_lo + 32 * warp; t0 <= pos; t0 += 32 * NW) {
     const int t = t0 + lane;
-    float s = -FLT_MAX;
-    if (t <= pos) {
+    const bool valid = t <= pos;
+    float kf[HD];
+    if (valid) {
       const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)t * kvdim);
-      float dot = 0.f;
-      for (int c = 0; c < (hd >> 3); ++c) {
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
         const uint4 kv4 = kr[c];
         const uint32_t w[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          dot = fmaf(qv[c * 8 + 2 * e], __uint_as_float(w[e] << 16), dot);
-          dot = fmaf(qv[c * 8 + 2 * e + 1], __uint_as_float(w[e] & 0xffff0000u), dot);
+          kf[c * 8 + 2 * e] = __uint_as_float(w[e] << 16);
+          kf[c * 8 + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
         }
       }
-      s = dot * scale;
+    } else {
+#pragma unroll
+      for (int i = 0; i < HD; ++i) kf[i] = 0.f;
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float corr = __expf(m - m_new);
-    const float p = (t <= pos) ? __expf(s - m_new) : 0.f;
-    l = l * corr + warp_sum(p);
-    acc0 *= corr;
-    acc1 *= corr;
+    float p[KVM];
+#pragma unroll
+    for (int h = 0; h < KVM; ++h) {
+      const float4 *q4 = reinterpret_cast<const float4 *>(q_s + h * HD);
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < HD / 4; ++c) {
+        const float4 qv = q4[c];
+        dot = fmaf(qv.x, kf[4 * c], dot);
+        dot = fmaf(qv.y, kf[4 * c + 1], dot);
+        dot = fmaf(qv.z, kf[4 * c + 2], dot);
+        dot = fmaf(qv.w, kf[4 * c + 3], dot);
+      }
+      const float sc = valid ? dot * scale : -FLT_MAX;
+      const float m_new = fmaxf(m[h], warp_max(sc));
+      const float corr = __expf(m[h] - m_new);
+      p[h] = valid ? __expf(sc - m_new) : 0.f;
+      l[h] = l[h] * corr + warp_sum(p[h]);
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
+      m[h] = m_new;
+    }
     const int n_here = min(32, pos - t0 + 1);
     for (int tt = 0; tt < n_here; ++tt) {
-      const float pt = __shfl_sync(0xffffffffu, p, tt);
       const uint16_t *vr = vbase + (size_t)(t0 + tt) * kvdim;
-      if (lane < hd) acc0 = fmaf(pt, bf16_bits_to_f32(vr[lane]), acc0);
-      if (lane + 32 < hd) acc1 = fmaf(pt, bf16_bits_to_f32(vr[lane + 32]), acc1);
+      float v[DPL];
+      if (DPL == 2) {
+        const uint32_t vv = *reinterpret_cast<const uint32_t *>(vr + 2 * lane);
+        v[0] = __uint_as_float(vv << 16);
+        v[DPL - 1] = __uint_as_float(vv & 0xffff0000u);
+      } else {
+        v[0] = bf16_bits_to_f32(vr[lane]);
+      }
+#pragma unroll
+      for (int h = 0; h < KVM; ++h) {
+        const float pt = __shfl_sync(0xffffffffu, p[h], tt);
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pt, v[d], acc[h][d]);
+      }
     }
-    m = m_new;
   }
-  // the sink is one more logit in the softmax whose value row is dropped (run.cpp:588-591)
-  const float sink = sinks[h];
-  const float m_fin = fmaxf(m, sink);
-  const float corr = __expf(m - m_fin);
-  const float denom = l * corr + __expf(sink - m_fin);
-  const float inv = corr / denom;
-  __nv_bfloat16 *o = out + (size_t)b * nq * hd + (size_t)h * hd;
-  if (lane < hd) o[lane] = __float2bfloat16_rn(acc0 * inv);
-  if (lane + 32 < hd) o[lane + 32] = __float2bfloat16_rn(acc1 * inv);
+#pragma unroll
+  for (int h = 0; h < KVM; ++h) {
+    if (lane == 0) {
+      m_s[warp][h] = m[h];
+      l_s[warp][h] = l[h];
+    }
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc_s[warp][h][DPL * lane + d] = acc[h][d];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < KVM * HD; i += blockDim.x) {
+    const int h = i / HD, d = i - h * HD;
+    const float sink = sinks[kvh * KVM + h];
+    float mx = sink;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) mx = fmaxf(mx, m_s[w][h]);
+    float denom = __expf(sink - mx), num = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float c = __expf(m_s[w][h] - mx);
+      denom += l_s[w][h] * c;
+      num += acc_s[w][h][d] * c;
+    }
+    out[(size_t)b * nq * HD + (size_t)(kvh * KVM + h) * HD + d] = __float2bfloat16_rn(num / denom);
+  }
 }
 
 // next[b] = index of the FIRST maximum of logits[b,:]   (run.cpp:739-750)
@@ -171,9 +224,20 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
   const float *row = logits + (size_t)b * V;
   float best = -FLT_MAX;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  const int v4 = ((reinterpret_cast<uintptr_t>(row) & 15) == 0) ? (V >> 2) : 0;  // 16-byte loads where the row allows
+  for (int i = threadIdx.x; i < v4; i += blockDim.x) {
+    const float4 q = reinterpret_cast<const float4 *>(row)[i];
+    const float vals[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (vals[e] > best) {  // ascending index per thread: strict '>' keeps the lowest index
+        best = vals[e];
+        idx = 4 * i + e;
+      }
+  }
+  for (int i = 4 * v4 + threadIdx.x; i < V; i += blockDim.x) {
     const float v = row[i];
-    if (v > best) {  // ascending i per thread: strict '>' keeps the lowest index
+    if (v > best) {
       best = v;
       idx = i;
     }
@@ -234,10 +298,23 @@ cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const fl
 }
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
                              int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s) {
-  const int kv_mul = nq / nkv;  // <= 8 (checked when the model is created): one warp per query head of the group
-  attention_kernel<<<dim3(B, nkv), kv_mul * 32, (size_t)kv_mul * hd * sizeof(float), s>>>(q, k_cache, v_cache, sinks, pos, t_lo,
-                                                                                        nq, nkv, hd, S, out);
-  return cudaGetLastError();
+  const int kv_mul = nq / nkv;
+  const dim3 grid(B, nkv);
+#define GPTOSS_ATT_CASE(HD, KVM)                                                                                    \
+  if (hd == HD && kv_mul == KVM) {                                                                                  \
+    attention_kernel<HD, KVM><<<grid, 128, 0, s>>>(q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv, S, out);         \
+    return cudaGetLastError();                                                                                      \
+  }
+  GPTOSS_ATT_CASE(64, 8)
+  GPTOSS_ATT_CASE(64, 4)
+  GPTOSS_ATT_CASE(64, 2)
+  GPTOSS_ATT_CASE(64, 1)
+  GPTOSS_ATT_CASE(32, 8)
+  GPTOSS_ATT_CASE(32, 4)
+  GPTOSS_ATT_CASE(32, 2)
+  GPTOSS_ATT_CASE(32, 1)
+#undef GPTOSS_ATT_CASE
+  return cudaErrorInvalidValue;  // head_dim must be 32 or 64, 1/2/4/8 query heads per kv head
 }
 cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s) {
   argmax_kernel<<<B, 1024, 0, s>>>(logits, V, next);

@@ -66,7 +66,9 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
   int n_active = n;
   for (int i = 0; i < n; ++i) cur[i] = prompt[i][0];
   for (int pos = 0; pos < max_seq_len - 1 && n_active > 0; ++pos) {
-    if (gptoss_model_step(model, cur.data(), pos, n, next.data())) die("decode step failed", model);
+    bool need_next = false;  // does any running sequence take the model's token this step?
+    for (int i = 0; i < n && !need_next; ++i) need_next = active[i] && pos_of[i] >= (int)prompt[i].size() - 1;
+    if (gptoss_model_step(model, cur.data(), pos, n, need_next ? next.data() : nullptr)) die("decode step failed", model);
     for (int i = 0; i < n; ++i) {
       if (!active[i]) continue;
       int tok = next[i];

@@ -47,12 +47,12 @@ class Model:
     def fill_synthetic(self, seed, sigma=0.02):
         self._check(self.lib.gptoss_model_fill_synthetic(self._m, seed, sigma))
 
-    def step(self, tokens, pos):
-        """tokens: int32 [B] -> greedy next tokens int32 [B]"""
+    def step(self, tokens, pos, need_next=True):
+        """tokens: int32 [B] -> greedy next tokens int32 [B] (None with need_next=False: the classifier is skipped)"""
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)
-        nxt = np.empty_like(tokens)
+        nxt = np.empty_like(tokens) if need_next else None
         self._check(self.lib.gptoss_model_step(self._m, tokens.ctypes.data_as(C.c_void_p), int(pos), tokens.size,
-                                               nxt.ctypes.data_as(C.c_void_p)))
+                                               nxt.ctypes.data_as(C.c_void_p) if need_next else None))
         return nxt
 
     def logits(self, row=0):
@@ -70,7 +70,7 @@ class Model:
         done = np.zeros(B, bool)
         tok = prompts[:, 0].copy()
         for pos in range(n_prompt + n_generate - 1):
-            nxt = self.step(tok, pos)
+            nxt = self.step(tok, pos, need_next=pos + 1 >= n_prompt)
             if pos + 1 < n_prompt:
                 tok = prompts[:, pos + 1].copy()
             else:

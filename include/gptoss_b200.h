@@ -213,7 +213,7 @@ typedef struct gptoss_model gptoss_model;
 /* One GPU holding the whole model (weights bf16, KV cache bf16 [layer][sequence][position][kv_dim], scratch
  * for max_batch sequences of at most max_seq positions).  Replaces build_transformer + our_init for the
  * single-GPU (20B-style, data-parallel replica) engine: run.cpp:283, getp-csrc/src/alloc.cpp:1035.
- * Limits: head_dim <= 64 and a multiple of 8, at most 8 query heads per kv head. */
+ * Limits: head_dim 32 or 64; 1, 2, 4 or 8 query heads per kv head. */
 int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batch, int max_seq, gptoss_model **out);
 int gptoss_model_destroy(gptoss_model *m);
 const char *gptoss_model_last_error(const gptoss_model *m);
@@ -229,7 +229,9 @@ int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma);
 /* One lock-step decode step for B sequences at position pos: host token ids in, greedy next token ids out
  * (forward_gpu_20b_batched, getp-csrc/src/model.cpp:6-151 / include/model.hpp:9; CPU: forward +
  * sample_argmax, run.cpp:501,739).  Prompt tokens are force-fed by the caller, one position per step, as
- * in getp-csrc/submit/getp_run_submit.cpp:60-87.  Synchronous. */
+ * in getp-csrc/submit/getp_run_submit.cpp:60-87.  next_tokens_host may be NULL for a step whose outputs the
+ * caller would discard anyway (every sequence still inside its prompt): the KV caches are updated, the
+ * final norm, classifier and argmax are skipped.  Synchronous. */
 int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host);
 /* Logits (fp32 [vocab]) of one sequence of the last step; debug/parity tap (PRINT_LOGITS, getp_run.cpp:236). */
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out);
