@@ -170,20 +170,27 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
       for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
       m[h] = m_new;
     }
+    // values: all rows of the chunk are requested before the first is used (the loads are independent; issued
+    // one by one behind their uses they would serialise on memory latency)
     const int n_here = min(32, pos - t0 + 1);
-    for (int tt = 0; tt < n_here; ++tt) {
-      const uint16_t *vr = vbase + (size_t)(t0 + tt) * kvdim;
+    uint32_t vv[32];
+#pragma unroll
+    for (int tt = 0; tt < 32; ++tt) {
+      const uint16_t *vr = vbase + (size_t)(t0 + min(tt, n_here - 1)) * kvdim;
+      vv[tt] = (DPL == 2) ? *reinterpret_cast<const uint32_t *>(vr + 2 * lane) : (uint32_t)vr[lane];
+    }
+#pragma unroll
+    for (int tt = 0; tt < 32; ++tt) {
       float v[DPL];
       if (DPL == 2) {
-        const uint32_t vv = *reinterpret_cast<const uint32_t *>(vr + 2 * lane);
-        v[0] = __uint_as_float(vv << 16);
-        v[DPL - 1] = __uint_as_float(vv & 0xffff0000u);
+        v[0] = __uint_as_float(vv[tt] << 16);
+        v[DPL - 1] = __uint_as_float(vv[tt] & 0xffff0000u);
       } else {
-        v[0] = bf16_bits_to_f32(vr[lane]);
+        v[0] = __uint_as_float(vv[tt] << 16);
       }
 #pragma unroll
       for (int h = 0; h < KVM; ++h) {
-        const float pt = __shfl_sync(0xffffffffu, p[h], tt);
+        const float pt = __shfl_sync(0xffffffffu, p[h], tt);  // zero for positions beyond pos
 #pragma unroll
         for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pt, v[d], acc[h][d]);
       }
