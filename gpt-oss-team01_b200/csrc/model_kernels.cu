@@ -96,23 +96,28 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
 }
 
 // Single-query attention for one (sequence, kv head) (run.cpp:565-607).  Memory-bound: every K and V row of
-// the cache is read once per kv head and serves all kv_mul query heads of the group from registers.  The
-// positions [t_lo, pos] (t_lo > 0 on sliding-window layers) are dealt out in chunks of 32 to the 4 warps of
-// the block; within a chunk one lane owns one position for the scores (its K row in registers, the queries
-// broadcast from shared memory) and the lanes own the head dimension for the values; online softmax per
-// head; the warps' partial (max, sum, accumulator) are merged through shared memory, where the learned sink
-// joins the denominator only (run.cpp:588-591).  HD = head_dim (32 or 64), KVM = query heads per kv head.
-template <int HD, int KVM>
+// the cache is read once per kv head and serves the query heads of the group from registers.  The block's
+// 4 warps are laid out as HS head groups x (4/HS) position groups: with a long context (HS = 1) every warp
+// serves all KVM query heads and the positions [t_lo, pos] are dealt out in chunks of 32; with a short one the
+// heads are split over the warps instead, so that no warp idles.  Within a chunk one lane owns one position
+// for the scores (its K row in registers, the queries broadcast from shared memory) and the lanes own the head
+// dimension for the values; online softmax per head; the partial (max, sum, accumulator) of the position
+// groups are merged through shared memory, where the learned sink joins the denominator only
+// (run.cpp:588-591).  HD = head_dim (32 or 64), KVM = query heads per kv head.
+template <int HD, int KVM, int HS>
 __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
                                                         const __nv_bfloat16 *__restrict__ v_cache,
                                                         const float *__restrict__ sinks, int pos, int t_lo, int nq,
                                                         int nkv, int S, __nv_bfloat16 *__restrict__ out) {
-  constexpr int DPL = HD / 32;  // output dims per lane
+  constexpr int DPL = HD / 32;   // output dims per lane
   constexpr int NW = 4;
+  constexpr int PS = NW / HS;    // position groups
+  constexpr int HPW = KVM / HS;  // query heads per warp
   __shared__ __align__(16) float q_s[KVM * HD];
-  __shared__ float m_s[NW][KVM], l_s[NW][KVM], acc_s[NW][KVM][HD];
+  __shared__ float m_s[PS][KVM], l_s[PS][KVM], acc_s[PS][KVM][HD];
   const int b = blockIdx.x, kvh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hs = warp % HS, ps = warp / HS, h0 = hs * HPW;
   const int kvdim = nkv * HD;
   for (int i = threadIdx.x; i < KVM * HD; i += blockDim.x) q_s[i] = q[(size_t)b * nq * HD + (size_t)kvh * KVM * HD + i];
   __syncthreads();
@@ -120,17 +125,18 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * HD;
   const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * HD;
 
-  float m[KVM], l[KVM], acc[KVM][DPL];
+  float m[HPW], l[HPW], acc[HPW][DPL];
 #pragma unroll
-  for (int h = 0; h < KVM; ++h) {
+  for (int h = 0; h < HPW; ++h) {
     m[h] = -FLT_MAX;
     l[h] = 0.f;
 #pragma unroll
     for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
   }
-  for (int t0 = t_lo + 32 * warp; t0 <= pos; t0 += 32 * NW) {
+  for (int t0 = t_lo + 32 * ps; t0 <= pos; t0 += 32 * PS) {
     const int t = t0 + lane;
     const bool valid = t <= pos;
+    const int n_here = min(32, pos - t0 + 1);
     float kf[HD];
     if (valid) {
       const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)t * kvdim);
@@ -148,10 +154,18 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
 #pragma unroll
       for (int i = 0; i < HD; ++i) kf[i] = 0.f;
     }
-    float p[KVM];
+    // values: all rows of the chunk are requested before the first is used (the loads are independent; issued
+    // one by one behind their uses they would serialise on memory latency)
+    uint32_t vv[32];
 #pragma unroll
-    for (int h = 0; h < KVM; ++h) {
-      const float4 *q4 = reinterpret_cast<const float4 *>(q_s + h * HD);
+    for (int tt = 0; tt < 32; ++tt) {
+      const uint16_t *vr = vbase + (size_t)(t0 + min(tt, n_here - 1)) * kvdim;
+      vv[tt] = (DPL == 2) ? *reinterpret_cast<const uint32_t *>(vr + 2 * lane) : (uint32_t)vr[lane];
+    }
+    float p[HPW];
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+      const float4 *q4 = reinterpret_cast<const float4 *>(q_s + (h0 + h) * HD);
       float dot = 0.f;
 #pragma unroll
       for (int c = 0; c < HD / 4; ++c) {
@@ -170,40 +184,29 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
       for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
       m[h] = m_new;
     }
-    // values: all rows of the chunk are requested before the first is used (the loads are independent; issued
-    // one by one behind their uses they would serialise on memory latency)
-    const int n_here = min(32, pos - t0 + 1);
-    uint32_t vv[32];
 #pragma unroll
     for (int tt = 0; tt < 32; ++tt) {
-      const uint16_t *vr = vbase + (size_t)(t0 + min(tt, n_here - 1)) * kvdim;
-      vv[tt] = (DPL == 2) ? *reinterpret_cast<const uint32_t *>(vr + 2 * lane) : (uint32_t)vr[lane];
-    }
-#pragma unroll
-    for (int tt = 0; tt < 32; ++tt) {
-      float v[DPL];
-      if (DPL == 2) {
+      if (tt < n_here) {
+        float v[DPL];
         v[0] = __uint_as_float(vv[tt] << 16);
-        v[DPL - 1] = __uint_as_float(vv[tt] & 0xffff0000u);
-      } else {
-        v[0] = __uint_as_float(vv[tt] << 16);
-      }
+        if (DPL == 2) v[DPL - 1] = __uint_as_float(vv[tt] & 0xffff0000u);
 #pragma unroll
-      for (int h = 0; h < KVM; ++h) {
-        const float pt = __shfl_sync(0xffffffffu, p[h], tt);  // zero for positions beyond pos
+        for (int h = 0; h < HPW; ++h) {
+          const float pt = __shfl_sync(0xffffffffu, p[h], tt);
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pt, v[d], acc[h][d]);
+          for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pt, v[d], acc[h][d]);
+        }
       }
     }
   }
 #pragma unroll
-  for (int h = 0; h < KVM; ++h) {
+  for (int h = 0; h < HPW; ++h) {
     if (lane == 0) {
-      m_s[warp][h] = m[h];
-      l_s[warp][h] = l[h];
+      m_s[ps][h0 + h] = m[h];
+      l_s[ps][h0 + h] = l[h];
     }
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) acc_s[warp][h][DPL * lane + d] = acc[h][d];
+    for (int d = 0; d < DPL; ++d) acc_s[ps][h0 + h][DPL * lane + d] = acc[h][d];
   }
   __syncthreads();
   for (int i = threadIdx.x; i < KVM * HD; i += blockDim.x) {
@@ -211,10 +214,10 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
     const float sink = sinks[kvh * KVM + h];
     float mx = sink;
 #pragma unroll
-    for (int w = 0; w < NW; ++w) mx = fmaxf(mx, m_s[w][h]);
+    for (int w = 0; w < PS; ++w) mx = fmaxf(mx, m_s[w][h]);
     float denom = __expf(sink - mx), num = 0.f;
 #pragma unroll
-    for (int w = 0; w < NW; ++w) {
+    for (int w = 0; w < PS; ++w) {
       const float c = __expf(m_s[w][h] - mx);
       denom += l_s[w][h] * c;
       num += acc_s[w][h][d] * c;
@@ -306,20 +309,28 @@ cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const fl
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
                              int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s) {
   const int kv_mul = nq / nkv;
+  const int n_chunks = (pos - t_lo) / 32 + 1;
+  int hs = n_chunks >= 4 ? 1 : (n_chunks >= 2 ? 2 : 4);  // short context: split the heads over the warps
+  if (hs > kv_mul) hs = kv_mul;
   const dim3 grid(B, nkv);
-#define GPTOSS_ATT_CASE(HD, KVM)                                                                                    \
-  if (hd == HD && kv_mul == KVM) {                                                                                  \
-    attention_kernel<HD, KVM><<<grid, 128, 0, s>>>(q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv, S, out);         \
-    return cudaGetLastError();                                                                                      \
+#define GPTOSS_ATT_CASE(HD, KVM, HS)                                                                                 \
+  if (hd == HD && kv_mul == KVM && hs == HS) {                                                                       \
+    attention_kernel<HD, KVM, HS><<<grid, 128, 0, s>>>(q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv, S, out);      \
+    return cudaGetLastError();                                                                                       \
   }
-  GPTOSS_ATT_CASE(64, 8)
-  GPTOSS_ATT_CASE(64, 4)
-  GPTOSS_ATT_CASE(64, 2)
-  GPTOSS_ATT_CASE(64, 1)
-  GPTOSS_ATT_CASE(32, 8)
-  GPTOSS_ATT_CASE(32, 4)
-  GPTOSS_ATT_CASE(32, 2)
-  GPTOSS_ATT_CASE(32, 1)
+#define GPTOSS_ATT_HD(HD)    \
+  GPTOSS_ATT_CASE(HD, 8, 1)  \
+  GPTOSS_ATT_CASE(HD, 8, 2)  \
+  GPTOSS_ATT_CASE(HD, 8, 4)  \
+  GPTOSS_ATT_CASE(HD, 4, 1)  \
+  GPTOSS_ATT_CASE(HD, 4, 2)  \
+  GPTOSS_ATT_CASE(HD, 4, 4)  \
+  GPTOSS_ATT_CASE(HD, 2, 1)  \
+  GPTOSS_ATT_CASE(HD, 2, 2)  \
+  GPTOSS_ATT_CASE(HD, 1, 1)
+  GPTOSS_ATT_HD(64)
+  GPTOSS_ATT_HD(32)
+#undef GPTOSS_ATT_HD
 #undef GPTOSS_ATT_CASE
   return cudaErrorInvalidValue;  // head_dim must be 32 or 64, 1/2/4/8 query heads per kv head
 }
