@@ -152,6 +152,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       int stage = 0, cur = 0;
       uint32_t phase = 0, armed = 0, last_par = 0;
       Tile t;
+      const uint64_t pol_w = l2_policy_evict_first();  // each weight byte is used once per launch
       // Head start: the weights do not depend on the kernel before this one, so the weight tiles of the first
       // ring fill are requested before waiting for it; its outputs (the activation rows) are loaded after.
       int pre = 0;
@@ -163,8 +164,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           const uint32_t sa = ring + kb * stage_bytes;
           armed |= 1u << kb;
           mbar_expect_tx(bar, Cfg::kAStageBytes + n_chunks * kBChunkBytes);
-          tma_load_3d(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA);
-          if (NA == 2) tma_load_3d(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1);
+          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA, pol_w);
+          if (NA == 2) tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1, pol_w);
         }
         pdl_wait();
         pdl_launch_dependents();
@@ -191,8 +192,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           armed |= 1u << stage;
           last_par = (last_par & ~(1u << stage)) | (phase << stage);
           mbar_expect_tx(bar, tx);
-          tma_load_3d(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA);
-          if (NA == 2) tma_load_3d(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1);
+          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA, pol_w);
+          if (NA == 2) tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1, pol_w);
           const uint32_t sb = sa + Cfg::kAStageBytes;
           for (int c = 0; c < n_chunks; ++c)
             tma_load_2d(sb + c * kBChunkBytes, &a.map_act, bar, kb * kBlockK, t.row0 + c * kTokChunk);
@@ -257,6 +258,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     int cur = 0, acc = 0;
     uint32_t acc_phase = 0;
     Tile t;
+    const uint64_t pol_keep = l2_policy_evict_last();  // the outputs are read again by the next kernel
     for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
       if (!decode_tile(idx, ctrl, n_local, nft, cur, t)) break;
       const int f = t.f0 + q * 32 + lane;
@@ -292,8 +294,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
             const __nv_bfloat162 pk = __floats2bfloat162_rn(v[j], v[j + 1]);
-            if (f_ok && c0 + j < t.n_valid) dst[(size_t)j * a.n_feat] = pk.x;
-            if (f_ok && c0 + j + 1 < t.n_valid) dst[(size_t)(j + 1) * a.n_feat] = pk.y;
+            if (f_ok && c0 + j < t.n_valid) st_b16_hint(dst + (size_t)j * a.n_feat, __bfloat16_as_ushort(pk.x), pol_keep);
+            if (f_ok && c0 + j + 1 < t.n_valid) st_b16_hint(dst + (size_t)(j + 1) * a.n_feat, __bfloat16_as_ushort(pk.y), pol_keep);
           }
         } else {
           float *pr[16];
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (f_ok && c0 + j < t.n_valid) pr[j][f] = v[j];
+            if (f_ok && c0 + j < t.n_valid) st_f32_hint(pr[j] + f, v[j], pol_keep);
         }
       }
       tc_fence_before();
