@@ -247,7 +247,20 @@ def run_ours(args):
         ms = float(tms.item())
     value = T * K / (ms * 1e-3)
 
-    nccl_ms = None
+    nccl_ms = stub_ms = None
+    if world > 1:  # the same kernels with the exchange stubbed: per-rank partial only (no push, no delivery, no add)
+        for i in range(3):
+            blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for i in range(K):
+            blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
+        s1.record()
+        barrier()
+        ts = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        stub_ms = float(ts.item()) / K
     if world > 1:  # the NCCL baseline on the same steps
         for i in range(3):
             step_nccl(i)
@@ -323,10 +336,11 @@ def run_ours(args):
         "stage_ms": stage_ms, "gpu_launches": (7 if world == 1 else 10) * K,  # router GEMM, top-k, scan, scatter, 2 GEMMs, combine (+ signal, owner, add)
     }
     if world > 1:
-        comm_ms = stage_ms["owner_combine"] + stage_ms["add_delta"]
+        comm_ms = ms / K - stub_ms  # exposed exchange = step with the fused combine - step with the exchange stubbed
         line["combine"] = {"kind": "peer stores (fp32) from the down-GEMM epilogue to the token owner + owner sum in slot "
                                    f"order + peer delivery of the sums ({args.wire})",
-                           "owner_combine_plus_add_ms": comm_ms, "share_of_step": comm_ms / (ms / K),
+                           "exposed_ms": comm_ms, "share_of_step": comm_ms / (ms / K),
+                           "stubbed_exchange_ms_per_step": stub_ms,
                            "nccl_allreduce_baseline_ms_per_step": nccl_ms}
 
     if rank == 0:
@@ -428,8 +442,8 @@ def main():
         real_stdout.flush()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
