@@ -95,134 +95,181 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
   for (int i = threadIdx.x; i < kvdim; i += blockDim.x) vdst[i] = __float2bfloat16_rn(vsrc[i]);
 }
 
-// Single-query attention for one (sequence, kv head) (run.cpp:565-607).  Memory-bound: every K and V row of
-// the cache is read once per kv head and serves the query heads of the group from registers.  The block's
-// 4 warps are laid out as HS head groups x (4/HS) position groups: with a long context (HS = 1) every warp
-// serves all KVM query heads and the positions [t_lo, pos] are dealt out in chunks of 32; with a short one the
-// heads are split over the warps instead, so that no warp idles.  Within a chunk one lane owns one position
-// for the scores (its K row in registers, the queries broadcast from shared memory) and the lanes own the head
-// dimension for the values; online softmax per head; the partial (max, sum, accumulator) of the position
-// groups are merged through shared memory, where the learned sink joins the denominator only
-// (run.cpp:588-591).  HD = head_dim (32 or 64), KVM = query heads per kv head.
-template <int HD, int KVM, int HS>
+// ---- single-query attention (run.cpp:565-607) -------------------------------------------------------------------
+// One "problem" is one (sequence, kv head): the KVM query heads of the group against the K/V rows [t_lo, pos]
+// of that head.  The op is bound by reading the cache (every K and V row once), so all per-position arithmetic
+// runs on the tensor cores with warp-level mma.sync m16n8k16 (the M = 128 tcgen05 shapes have no use for 8 query
+// rows): rows of the A operand = query heads (8 of 16 used), and
+//   scores  S[head, pos]  = Q[head, dim] . K[pos, dim]      (B operand = K rows as they lie in the cache)
+//   output  O[head, dim] += P[head, pos] . V[pos, dim]      (A = the probabilities, taken from the S accumulators
+//                                                            in registers; B = V rows, pairs of positions packed
+//                                                            with one byte-permute each)
+// Q and P are fp32 values: each is split into a bf16 head and a bf16 remainder and multiplied in two MMAs, so the
+// products carry ~16 mantissa bits and accumulate in fp32 (K and V are bf16 in the cache, exactly).  The order of
+// the contraction index is free, which is used to give every thread 16-byte contiguous loads: thread (g = lane/4,
+// c = lane%4) owns the dims [HD/4*c, HD/4*(c+1)) of K row g of each 8-position tile, and the dims
+// [HD/8*g, HD/8*(g+1)) of the four V rows {2c, 2c+1, 2c+8, 2c+9} of each 16-position step.
+// A block's 4 warps serve G problems with 4/G warps each (positions dealt out in chunks of 32); online softmax per
+// head; the partial (max, sum, accumulator) are merged through shared memory, where the learned sink joins the
+// denominator only (run.cpp:588-591).
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  // rows 8..15 of A (registers a1, a3) are zero: only query rows 0..7 are in use
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// (x, y) -> bf16 pair of the rounded values (hi) and of the remainders (lo); x in the low half
+__device__ __forceinline__ void split_pair(float x, float y, uint32_t &hi, uint32_t &lo) {
+  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+  const __nv_bfloat16 xl = __float2bfloat16_rn(x - __bfloat162float(xh)), yl = __float2bfloat16_rn(y - __bfloat162float(yh));
+  hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+  lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
+}
+
+template <int HD, int G>
 __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
                                                         const __nv_bfloat16 *__restrict__ v_cache,
                                                         const float *__restrict__ sinks, int pos, int t_lo, int nq,
-                                                        int nkv, int S, __nv_bfloat16 *__restrict__ out) {
-  constexpr int DPL = HD / 32;   // output dims per lane
-  constexpr int NW = 4;
-  constexpr int PS = NW / HS;    // position groups
-  constexpr int HPW = KVM / HS;  // query heads per warp
-  __shared__ __align__(16) float q_s[KVM * HD];
-  __shared__ float m_s[PS][KVM], l_s[PS][KVM], acc_s[PS][KVM][HD];
-  const int b = blockIdx.x, kvh = blockIdx.y;
+                                                        int nkv, int kvm, int S, int n_problems,
+                                                        __nv_bfloat16 *__restrict__ out) {
+  constexpr int PS = 4 / G;    // warps (position groups) per problem
+  constexpr int D4 = HD / 4;   // K dims per thread
+  constexpr int KS = HD / 16;  // k-steps of the score MMA
+  constexpr int DV = HD / 8;   // V dims per thread = n-tiles of the output MMA
+  __shared__ float m_s[4][8], l_s[4][8];
+  __shared__ float acc_s[4][8][HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hs = warp % HS, ps = warp / HS, h0 = hs * HPW;
+  const int g = lane >> 2, c = lane & 3;
+  const int grp = warp / PS, ps = warp % PS;
+  const int prob = blockIdx.x * G + grp;
+  const bool active = prob < n_problems;
+  const int b = active ? prob / nkv : 0, kvh = active ? prob % nkv : 0;
   const int kvdim = nkv * HD;
-  for (int i = threadIdx.x; i < KVM * HD; i += blockDim.x) q_s[i] = q[(size_t)b * nq * HD + (size_t)kvh * KVM * HD + i];
-  __syncthreads();
-  const float scale = 1.0f / sqrtf((float)HD);
-  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * HD;
-  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * HD;
 
-  float m[HPW], l[HPW], acc[HPW][DPL];
+  uint32_t qh[KS][2], ql[KS][2];
 #pragma unroll
-  for (int h = 0; h < HPW; ++h) {
-    m[h] = -FLT_MAX;
-    l[h] = 0.f;
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
+  for (int s = 0; s < KS; ++s) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (active && g < kvm) v = *reinterpret_cast<const float4 *>(q + ((size_t)b * nq + (size_t)kvh * kvm + g) * HD + D4 * c + 4 * s);
+    split_pair(v.x, v.y, qh[s][0], ql[s][0]);
+    split_pair(v.z, v.w, qh[s][1], ql[s][1]);
   }
-  for (int t0 = t_lo + 32 * ps; t0 <= pos; t0 += 32 * PS) {
-    const int t = t0 + lane;
-    const bool valid = t <= pos;
-    const int n_here = min(32, pos - t0 + 1);
-    float kf[HD];
-    if (valid) {
-      const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)t * kvdim);
+  const float scale = 1.0f / sqrtf((float)HD);
+  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * HD + D4 * c;
+  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * HD + DV * g;
+
+  float m_run = -FLT_MAX, l_part = 0.f;  // l_part: this thread's share of the denominator (its own positions)
+  float o[DV][4];
 #pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        const uint4 kv4 = kr[c];
-        const uint32_t w[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
+  for (int i = 0; i < DV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  if (active) {
+    for (int t0 = t_lo + 32 * ps; t0 <= pos; t0 += 32 * PS) {
+      // every load of the chunk is requested before the first use; rows past `pos` re-read row `pos` (masked below)
+      uint32_t kr[4][D4 / 2];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          kf[c * 8 + 2 * e] = __uint_as_float(w[e] << 16);
-          kf[c * 8 + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+      for (int j = 0; j < 4; ++j) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(kbase + (size_t)min(t0 + 8 * j + g, pos) * kvdim);
+#pragma unroll
+        for (int u = 0; u < D4 / 8; ++u) {
+          const uint4 x = src[u];
+          kr[j][4 * u] = x.x, kr[j][4 * u + 1] = x.y, kr[j][4 * u + 2] = x.z, kr[j][4 * u + 3] = x.w;
         }
       }
-    } else {
+      uint32_t vr[2][4][DV / 2];
 #pragma unroll
-      for (int i = 0; i < HD; ++i) kf[i] = 0.f;
-    }
-    // values: all rows of the chunk are requested before the first is used (the loads are independent; issued
-    // one by one behind their uses they would serialise on memory latency)
-    uint32_t vv[32];
+      for (int s = 0; s < 2; ++s)
 #pragma unroll
-    for (int tt = 0; tt < 32; ++tt) {
-      const uint16_t *vr = vbase + (size_t)(t0 + min(tt, n_here - 1)) * kvdim;
-      vv[tt] = (DPL == 2) ? *reinterpret_cast<const uint32_t *>(vr + 2 * lane) : (uint32_t)vr[lane];
-    }
-    float p[HPW];
+        for (int r = 0; r < 4; ++r) {
+          const int row = 16 * s + 2 * c + (r & 1) + 8 * (r >> 1);
+          const uint16_t *src = vbase + (size_t)min(t0 + row, pos) * kvdim;
+          if (DV == 8) {
+            const uint4 x = *reinterpret_cast<const uint4 *>(src);
+            vr[s][r][0] = x.x, vr[s][r][1] = x.y, vr[s][r][DV / 2 - 2] = x.z, vr[s][r][DV / 2 - 1] = x.w;
+          } else {
+            const uint2 x = *reinterpret_cast<const uint2 *>(src);
+            vr[s][r][0] = x.x, vr[s][r][1] = x.y;
+          }
+        }
+      // scores of head g at positions t0 + 8j + 2c + {0,1}
+      float p[4][2];
+      float cmax = -FLT_MAX;
 #pragma unroll
-    for (int h = 0; h < HPW; ++h) {
-      const float4 *q4 = reinterpret_cast<const float4 *>(q_s + (h0 + h) * HD);
-      float dot = 0.f;
+      for (int j = 0; j < 4; ++j) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < HD / 4; ++c) {
-        const float4 qv = q4[c];
-        dot = fmaf(qv.x, kf[4 * c], dot);
-        dot = fmaf(qv.y, kf[4 * c + 1], dot);
-        dot = fmaf(qv.z, kf[4 * c + 2], dot);
-        dot = fmaf(qv.w, kf[4 * c + 3], dot);
+        for (int s = 0; s < KS; ++s) {
+          mma_bf16_16816(acc, qh[s][0], qh[s][1], kr[j][2 * s], kr[j][2 * s + 1]);
+          mma_bf16_16816(acc, ql[s][0], ql[s][1], kr[j][2 * s], kr[j][2 * s + 1]);
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[j][e] = (t0 + 8 * j + 2 * c + e <= pos) ? acc[e] * scale : -FLT_MAX;
+          cmax = fmaxf(cmax, p[j][e]);
+        }
       }
-      const float sc = valid ? dot * scale : -FLT_MAX;
-      const float m_new = fmaxf(m[h], warp_max(sc));
-      const float corr = __expf(m[h] - m_new);
-      p[h] = valid ? __expf(sc - m_new) : 0.f;
-      l[h] = l[h] * corr + warp_sum(p[h]);
+      cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 1));
+      cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 2));
+      const float m_new = fmaxf(m_run, cmax);  // finite: every chunk holds at least position t0 <= pos
+      const float corr = __expf(m_run - m_new);
+      float psum = 0.f;
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
-      m[h] = m_new;
-    }
+      for (int j = 0; j < 4; ++j)
 #pragma unroll
-    for (int tt = 0; tt < 32; ++tt) {
-      if (tt < n_here) {
-        float v[DPL];
-        v[0] = __uint_as_float(vv[tt] << 16);
-        if (DPL == 2) v[DPL - 1] = __uint_as_float(vv[tt] & 0xffff0000u);
+        for (int e = 0; e < 2; ++e) {
+          p[j][e] = (t0 + 8 * j + 2 * c + e <= pos) ? __expf(p[j][e] - m_new) : 0.f;
+          psum += p[j][e];
+        }
+      l_part = l_part * corr + psum;
+      m_run = m_new;
 #pragma unroll
-        for (int h = 0; h < HPW; ++h) {
-          const float pt = __shfl_sync(0xffffffffu, p[h], tt);
+      for (int i = 0; i < DV; ++i) o[i][0] *= corr, o[i][1] *= corr;
 #pragma unroll
-          for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pt, v[d], acc[h][d]);
+      for (int s = 0; s < 2; ++s) {
+        uint32_t a0h, a0l, a2h, a2l;
+        split_pair(p[2 * s][0], p[2 * s][1], a0h, a0l);
+        split_pair(p[2 * s + 1][0], p[2 * s + 1][1], a2h, a2l);
+#pragma unroll
+        for (int i = 0; i < DV; ++i) {  // n-tile i, column g = dim DV*g + i
+          const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
+          const uint32_t b0 = __byte_perm(vr[s][0][i >> 1], vr[s][1][i >> 1], sel);
+          const uint32_t b1 = __byte_perm(vr[s][2][i >> 1], vr[s][3][i >> 1], sel);
+          mma_bf16_16816(o[i], a0h, a2h, b0, b1);
+          mma_bf16_16816(o[i], a0l, a2l, b0, b1);
         }
       }
     }
   }
+  l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
+  l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
+  if (c == 0) {
+    m_s[warp][g] = m_run;
+    l_s[warp][g] = l_part;
+  }
 #pragma unroll
-  for (int h = 0; h < HPW; ++h) {
-    if (lane == 0) {
-      m_s[ps][h0 + h] = m[h];
-      l_s[ps][h0 + h] = l[h];
-    }
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) acc_s[ps][h0 + h][DPL * lane + d] = acc[h][d];
+  for (int i = 0; i < DV; ++i) {  // accumulator columns 2c, 2c+1 of n-tile i = dims DV*2c + i, DV*(2c+1) + i
+    acc_s[warp][g][DV * (2 * c) + i] = o[i][0];
+    acc_s[warp][g][DV * (2 * c + 1) + i] = o[i][1];
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < KVM * HD; i += blockDim.x) {
-    const int h = i / HD, d = i - h * HD;
-    const float sink = sinks[kvh * KVM + h];
+  for (int idx = threadIdx.x; idx < G * kvm * HD; idx += blockDim.x) {
+    const int gr = idx / (kvm * HD), rem = idx - gr * (kvm * HD);
+    const int h = rem / HD, d = rem - h * HD;
+    const int pr = blockIdx.x * G + gr;
+    if (pr >= n_problems) break;
+    const int pb = pr / nkv, pk = pr % nkv;
+    const float sink = sinks[pk * kvm + h];
     float mx = sink;
 #pragma unroll
-    for (int w = 0; w < PS; ++w) mx = fmaxf(mx, m_s[w][h]);
+    for (int w = 0; w < PS; ++w) mx = fmaxf(mx, m_s[gr * PS + w][h]);
     float denom = __expf(sink - mx), num = 0.f;
 #pragma unroll
     for (int w = 0; w < PS; ++w) {
-      const float c = __expf(m_s[w][h] - mx);
-      denom += l_s[w][h] * c;
-      num += acc_s[w][h][d] * c;
+      const float cw = __expf(m_s[gr * PS + w][h] - mx);
+      denom += l_s[gr * PS + w][h] * cw;
+      num += acc_s[gr * PS + w][h][d] * cw;
     }
-    out[(size_t)b * nq * HD + (size_t)(kvh * KVM + h) * HD + d] = __float2bfloat16_rn(num / denom);
+    out[(size_t)pb * nq * HD + (size_t)(pk * kvm + h) * HD + d] = __float2bfloat16_rn(num / denom);
   }
 }
 
@@ -309,30 +356,25 @@ cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const fl
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
                              int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s) {
   const int kv_mul = nq / nkv;
-  const int n_chunks = (pos - t_lo) / 32 + 1;
-  int hs = n_chunks >= 4 ? 1 : (n_chunks >= 2 ? 2 : 4);  // short context: split the heads over the warps
-  if (hs > kv_mul) hs = kv_mul;
-  const dim3 grid(B, nkv);
-#define GPTOSS_ATT_CASE(HD, KVM, HS)                                                                                 \
-  if (hd == HD && kv_mul == KVM && hs == HS) {                                                                       \
-    attention_kernel<HD, KVM, HS><<<grid, 128, 0, s>>>(q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv, S, out);      \
-    return cudaGetLastError();                                                                                       \
+  if (kv_mul < 1 || kv_mul > 8 || kv_mul * nkv != nq) return cudaErrorInvalidValue;  // query rows of one MMA tile
+  const int n_chunks = (pos - t_lo) / 32 + 1, n_prob = B * nkv;
+  // one warp per problem while there are problems enough to fill the machine (or a single chunk each); otherwise
+  // the positions of a problem are split over 2 or 4 warps
+  const int g = (n_chunks == 1 || n_prob >= 4096) ? 4 : ((n_chunks <= 3 || n_prob >= 2048) ? 2 : 1);
+  const int grid = (n_prob + g - 1) / g;
+#define GPTOSS_ATT_CASE(HD, G)                                                                                             \
+  if (hd == HD && g == G) {                                                                                                \
+    attention_kernel<HD, G><<<grid, 128, 0, s>>>(q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv, kv_mul, S, n_prob, out);  \
+    return cudaGetLastError();                                                                                             \
   }
-#define GPTOSS_ATT_HD(HD)    \
-  GPTOSS_ATT_CASE(HD, 8, 1)  \
-  GPTOSS_ATT_CASE(HD, 8, 2)  \
-  GPTOSS_ATT_CASE(HD, 8, 4)  \
-  GPTOSS_ATT_CASE(HD, 4, 1)  \
-  GPTOSS_ATT_CASE(HD, 4, 2)  \
-  GPTOSS_ATT_CASE(HD, 4, 4)  \
-  GPTOSS_ATT_CASE(HD, 2, 1)  \
-  GPTOSS_ATT_CASE(HD, 2, 2)  \
-  GPTOSS_ATT_CASE(HD, 1, 1)
-  GPTOSS_ATT_HD(64)
-  GPTOSS_ATT_HD(32)
-#undef GPTOSS_ATT_HD
+  GPTOSS_ATT_CASE(64, 4)
+  GPTOSS_ATT_CASE(64, 2)
+  GPTOSS_ATT_CASE(64, 1)
+  GPTOSS_ATT_CASE(32, 4)
+  GPTOSS_ATT_CASE(32, 2)
+  GPTOSS_ATT_CASE(32, 1)
 #undef GPTOSS_ATT_CASE
-  return cudaErrorInvalidValue;  // head_dim must be 32 or 64, 1/2/4/8 query heads per kv head
+  return cudaErrorInvalidValue;  // head_dim must be 32 or 64
 }
 cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s) {
   argmax_kernel<<<B, 1024, 0, s>>>(logits, V, next);

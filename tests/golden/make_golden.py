@@ -1,4 +1,5 @@
-"""Generates tests/golden/moe_7m_golden.npz by running the REFERENCE's own CPU model.
+"""Generates tests/golden/moe_7m_golden.npz and tests/golden/attn_hd64_golden.npz by running the REFERENCE's own
+CPU model.
 
 Needs the reference sources (default /root/reference; override with GPTOSS_REFERENCE_DIR): the
 reference's run.cpp is compiled by oracle/Makefile into oracle/_ref/libref_cpu.so and its forward()
@@ -8,6 +9,11 @@ MoE block (run.cpp:622-704) is captured: block input t, router scores, top-k ids
 weights and the block output e_agg.  The greedy continuation (32 random prompt ids, 64 generated
 tokens) is stored too, together with, per position, the argmax token, the gap between the two largest
 logits and the logits at 64 fixed vocabulary ids (for the whole-model parity test).
+
+The second fixture covers the attention geometry of the 20b/120b checkpoints that the 7m one lacks (head_dim 64,
+8 query heads per kv head) on a small two-layer model, over 200 teacher-forced positions with a sliding window
+of 48: the windowed layer (layer 0, run.cpp:582) drops old positions, the other attends to all of them.  It
+stores, per position, the argmax, the top-2 gap and the logits at 64 fixed ids.
 
 Run from the repository root:   python tests/golden/make_golden.py
 """
@@ -73,5 +79,43 @@ def main():
     print("generated:", gen[:16], "...")
 
 
+ATTN_SEED = 20240611
+
+
+def attn_config():
+    """head_dim 64, 16 query heads over 2 kv heads, window 48; the other dims small so that the fixture stays cheap.
+    Four experts, all four selected: the expert choice cannot flip between the fp32 reference and a path that
+    rounds GEMM inputs to bf16 (a flip at one position would stay in the KV cache for the rest of the sequence),
+    so the comparison stays at rounding-noise level over all positions."""
+    return binfmt.Config(1024, 128, 4, 4, 128, 2, 64, 16, 2, 256, 4096, 150000.0, 32.0, 48, 7.0)
+
+
+def make_attention_fixture(n_pos=200):
+    ref = oracle_lib.reference()
+    cfg = attn_config()
+    with tempfile.TemporaryDirectory() as td:
+        path = Path(td) / "attn-hd64-synth.bin"
+        binfmt.write_synthetic(str(path), cfg, ATTN_SEED, sigma=0.05)
+        ids = synth.uniform_ids(ATTN_SEED, PROMPT_STREAM, n_pos, cfg.vocab_size)
+        probe_idx = synth.uniform_ids(ATTN_SEED, PROMPT_STREAM + 1, 64, cfg.vocab_size)
+        logits = np.empty(cfg.vocab_size, np.float32)
+        h = ref.open(path)
+        nxts, margins, probes, stds = [], [], [], []
+        for pos in range(n_pos):
+            nxt = ref.forward(h, int(ids[pos]), pos, logits)
+            top2 = np.partition(logits, -2)[-2:]
+            nxts.append(nxt), margins.append(float(top2[1] - top2[0])), probes.append(logits[probe_idx].copy())
+            stds.append(float(logits.std()))
+        ref.close(h)
+    out = Path(__file__).with_name("attn_hd64_golden.npz")
+    np.savez_compressed(out, seed=ATTN_SEED, sigma=0.05, ids=ids, next_token=np.array(nxts, np.int32),
+                        top2_margin=np.array(margins, np.float32), probe_idx=probe_idx,
+                        probe_logits=np.stack(probes), logit_std=np.array(stds, np.float32))
+    print(f"wrote {out} ({out.stat().st_size} bytes): {n_pos} positions, logit std {np.mean(stds):.4f}, "
+          f"median top-2 gap {np.median(margins):.4f}")
+
+
 if __name__ == "__main__":
-    main()
+    if "--attention-only" not in sys.argv:
+        main()
+    make_attention_fixture()

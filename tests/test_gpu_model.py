@@ -70,6 +70,37 @@ def test_free_running_greedy_decode_first_32_tokens(golden, checkpoint):
     m.close()
 
 
+def test_attention_hd64_gqa8_sliding_window_matches_reference_forward(tmp_path):
+    """head_dim 64 with 8 query heads per kv head (the 20b/120b attention geometry) over 200 positions and a
+    window of 48: layer 0 drops old positions (run.cpp:582), layer 1 attends to all; the context passes through
+    every split of the positions over warps.  Fixture from the reference's forward() (tests/golden/make_golden.py)."""
+    import sys
+    sys.path.insert(0, str(Path(__file__).parent / "golden"))
+    from make_golden import attn_config
+    from gptoss_b200 import model
+    g = np.load(Path(__file__).parent / "golden" / "attn_hd64_golden.npz")
+    cfg = attn_config()
+    ckpt = tmp_path / "attn-hd64-synth.bin"
+    binfmt.write_synthetic(str(ckpt), cfg, int(g["seed"]), sigma=float(g["sigma"]))
+    ids = g["ids"].astype(np.int32)
+    other = synth.uniform_ids(3, 4, len(ids), cfg.vocab_size).astype(np.int32)
+    m = model.Model(cfg, max_batch=3, max_seq=256)
+    m.load_bin(ckpt)
+    tol = 0.02 * float(g["logit_std"].mean())  # 2% of the logits' spread (bf16 GEMM inputs and KV cache vs fp32)
+    worst, safe_total = 0.0, 0
+    for pos in range(len(ids)):
+        nxt = m.step(np.array([ids[pos], other[pos], ids[pos]], np.int32), pos)
+        got = m.logits(0)[g["probe_idx"]]
+        worst = max(worst, float(np.abs(got - g["probe_logits"][pos]).max()))
+        assert np.array_equal(m.logits(2), m.logits(0))  # rows of a batch do not interact
+        if g["top2_margin"][pos] > 4 * tol:
+            safe_total += 1
+            assert nxt[0] == g["next_token"][pos] and nxt[2] == nxt[0], (pos, nxt, g["next_token"][pos])
+    assert worst <= tol, (worst, tol)
+    assert safe_total > 0.7 * len(ids)
+    m.close()
+
+
 def test_synthetic_fill_decodes_and_is_deterministic():
     from gptoss_b200 import model
     cfg = binfmt.config_7m()
