@@ -128,7 +128,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       ctrl->tbp[i] = a.tb_prefix[i];
       const int o = a.offsets[a.e_begin + i];
       ctrl->off[i] = o;
-      if (i < n_local) mx = max(mx, min(kMaxTileTokens, a.offsets[a.e_begin + i + 1] - o));
+      if (i < n_local) {  // rows of this expert's largest tile (see decode_tile)
+        const int rows = a.offsets[a.e_begin + i + 1] - o, nb = a.tb_prefix[i + 1] - a.tb_prefix[i];
+        if (nb > 0) mx = max(mx, min(kMaxTileTokens, (((rows + nb - 1) / nb) + 15) & ~15));
+      }
     }
     if (mx > 0) atomicMax(&ctrl->max_rows, mx);
   }

@@ -116,14 +116,16 @@ void rope_tables(const gptoss_model_config &c, int S, std::vector<float> &cs, st
 }
 
 // out[B, n_out] (fp32) = act[B, K] (bf16) . W[n_out, K]^T + bias — the down-GEMM kernel with one "expert"
-int dense(gptoss_model *m, const CUtensorMap &map_w, const CUtensorMap &map_act, int K, int n_out, const float *bias,
-          float *out) {
+enum { kDenseQkv = 0, kDenseOut = 1, kDenseVocab = 2 };  // which token-block split (dense_tbp) a dense GEMM uses
+
+int dense(gptoss_model *m, int which, const CUtensorMap &map_w, const CUtensorMap &map_act, int K, int n_out,
+          const float *bias, float *out) {
   GemmArgs a;
   memset(&a, 0, sizeof a);
   a.map_w = map_w;
   a.map_act = map_act;
   a.offsets = m->dense_off;
-  a.tb_prefix = m->dense_tbp;
+  a.tb_prefix = m->dense_tbp + 2 * which;
   a.e_begin = 0;
   a.n_local = 1;
   a.n_feat = n_out;
@@ -141,9 +143,31 @@ int dense(gptoss_model *m, const CUtensorMap &map_w, const CUtensorMap &map_act,
   return GPTOSS_OK;
 }
 
+// Number of token blocks for a dense GEMM of B rows and n_out features: work items = feature tiles x token blocks
+// go round-robin over the persistent CTAs, so the time is (rounds of items) x (time of one item).  An item costs
+// about its block's rows (at least 64: below that the weight tile's shared-memory reads bound the MMA) plus a
+// fixed part (pipeline fill, epilogue), here 32 rows' worth.  More, smaller blocks can fill the last round.
+int pick_token_blocks(int B, int n_out, int sm_count) {
+  const int nft = (n_out + kTileF - 1) / kTileF;
+  const int nb_min = (B + kMaxTileTokens - 1) / kMaxTileTokens;
+  int best = nb_min > 0 ? nb_min : 1;
+  long best_cost = -1;
+  for (int nb = best; nb <= 4 * best && nb <= 64; ++nb) {
+    const int blk = (((B + nb - 1) / nb) + 15) & ~15;
+    const long rounds = ((long)nft * nb + sm_count - 1) / sm_count;
+    const long cost = rounds * ((blk < 64 ? 64 : blk) + 32);
+    if (best_cost < 0 || cost < best_cost) best_cost = cost, best = nb;
+  }
+  return best;
+}
+
 int set_batch(gptoss_model *m, int B) {
   if (m->cur_B == B) return GPTOSS_OK;
-  const int off[2] = {0, B}, tbp[2] = {0, (B + kMaxTileTokens - 1) / kMaxTileTokens};
+  const gptoss_model_config &c = m->c;
+  const int qkvd = c.head_dim * (c.n_attn_heads + 2 * c.n_kv_heads);
+  const int off[2] = {0, B};
+  const int tbp[6] = {0, pick_token_blocks(B, qkvd, m->sm_count), 0, pick_token_blocks(B, c.hidden_dim, m->sm_count),
+                      0, pick_token_blocks(B, c.vocab_size, m->sm_count)};
   MK(cudaMemcpyAsync(m->dense_off, off, sizeof off, cudaMemcpyHostToDevice, m->stream));
   MK(cudaMemcpyAsync(m->dense_tbp, tbp, sizeof tbp, cudaMemcpyHostToDevice, m->stream));
   MK(cudaStreamSynchronize(m->stream));
@@ -214,7 +238,7 @@ int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batc
   A(dalloc(&m->iota, B));
   A(dalloc(&m->ones, B));
   A(dalloc(&m->dense_off, 2));
-  A(dalloc(&m->dense_tbp, 2));
+  A(dalloc(&m->dense_tbp, 6));
   A(dalloc(&m->status, kStatusWords));
   A(dalloc(&m->staging, kStagingElems));
   if (e == cudaSuccess) A(cudaMemset(m->status, 0, kStatusWords * sizeof(int)));
@@ -373,19 +397,19 @@ int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, i
   MK(launch_embed(m->tokens_dev, m->emb, B, (int)H, c.vocab_size, m->x, s));
   for (size_t l = 0; l < L; ++l) {
     MK(launch_residual_rmsnorm(m->x, nullptr, m->attn_norm + l * H, B, (int)H, m->t, s));
-    if ((rc = dense(m, m->map_qkv[l], m->map_t, (int)H, (int)qkvd, m->b_qkv + l * qkvd, m->qkv))) return rc;
+    if ((rc = dense(m, kDenseQkv, m->map_qkv[l], m->map_t, (int)H, (int)qkvd, m->b_qkv + l * qkvd, m->qkv))) return rc;
     __nv_bfloat16 *kc = m->k_cache + l * (size_t)m->max_batch * S * kvd, *vc = m->v_cache + l * (size_t)m->max_batch * S * kvd;
     MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, s));
     const bool windowed = c.sliding_window > 0 && (l % 2 == 0);  // run.cpp:582
     const int t_lo = windowed ? (pos - c.sliding_window + 1 > 0 ? pos - c.sliding_window + 1 : 0) : 0;
     MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, s));
-    if ((rc = dense(m, m->map_o[l], m->map_att, (int)qd, (int)H, m->b_o + l * H, m->proj))) return rc;
+    if ((rc = dense(m, kDenseOut, m->map_o[l], m->map_att, (int)qd, (int)H, m->b_o + l * H, m->proj))) return rc;
     MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
     if ((rc = gptoss_moe_forward(m->moe, (int)l, B, m->t, m->x, s))) return m->fail(rc, gptoss_last_error(m->moe));
   }
   if (next_tokens_host) {  // a step whose outputs are all overridden by prompt tokens needs no logits
     MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, (int)H, m->t, s));
-    if ((rc = dense(m, m->map_unemb, m->map_t, (int)H, c.vocab_size, nullptr, m->logits))) return rc;
+    if ((rc = dense(m, kDenseVocab, m->map_unemb, m->map_t, (int)H, c.vocab_size, nullptr, m->logits))) return rc;
     MK(launch_argmax(m->logits, B, c.vocab_size, m->next_dev, s));
     MK(cudaMemcpyAsync(next_tokens_host, m->next_dev, B * sizeof(int), cudaMemcpyDeviceToHost, s));
   }

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float *__restrict
 
 // qkv[b, :] = (q heads | k heads | v heads), bias already added (run.cpp:534-557).  Rotates q and k with the
 // cos/sin of position `pos` (half-split pairs: element i pairs with i + hd/2), writes q as fp32 and k, v as
-// bf16 into the caches at [b, pos, kv_head*hd + i].
+// bf16 into the caches at [b, kv_head, pos, i]: the rows that one (sequence, kv head) attends to are contiguous.
 __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__restrict__ qkv, const float *__restrict__ cos_t,
                                                              const float *__restrict__ sin_t, int pos, int nq, int nkv,
                                                              int hd, int S, float *__restrict__ q_out,
@@ -85,14 +85,16 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
       q_out[(size_t)b * qdim + h * hd + j] = o1;
       q_out[(size_t)b * qdim + h * hd + j + half] = o2;
     } else {
-      __nv_bfloat16 *dst = k_cache + ((size_t)b * S + pos) * kvdim + (h - nq) * hd;
+      __nv_bfloat16 *dst = k_cache + (((size_t)b * nkv + (h - nq)) * S + pos) * hd;
       dst[j] = __float2bfloat16_rn(o1);
       dst[j + half] = __float2bfloat16_rn(o2);
     }
   }
   const float *vsrc = row + qdim + kvdim;
-  __nv_bfloat16 *vdst = v_cache + ((size_t)b * S + pos) * kvdim;
-  for (int i = threadIdx.x; i < kvdim; i += blockDim.x) vdst[i] = __float2bfloat16_rn(vsrc[i]);
+  for (int i = threadIdx.x; i < kvdim; i += blockDim.x) {
+    const int h = i / hd, j = i - h * hd;
+    v_cache[(((size_t)b * nkv + h) * S + pos) * hd + j] = __float2bfloat16_rn(vsrc[i]);
+  }
 }
 
 // ---- single-query attention (run.cpp:565-607) -------------------------------------------------------------------
@@ -104,19 +106,21 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
 //   output  O[head, dim] += P[head, pos] . V[pos, dim]      (A = the probabilities, taken from the S accumulators
 //                                                            in registers; B = V rows, pairs of positions packed
 //                                                            with one byte-permute each)
-// Q and P are fp32 values: each is split into a bf16 head and a bf16 remainder and multiplied in two MMAs, so the
-// products carry ~16 mantissa bits and accumulate in fp32 (K and V are bf16 in the cache, exactly).  The order of
+// Q and P are fp32 values: each is split into a bf16 head (tile rows 0..7) and a bf16 remainder (rows 8..15, which 8
+// query heads leave free), and the two accumulator halves are added, so the products carry ~16 mantissa bits and
+// accumulate in fp32 at no extra MMA (K and V are bf16 in the cache, exactly).  The order of
 // the contraction index is free, which is used to give every thread 16-byte contiguous loads: thread (g = lane/4,
 // c = lane%4) owns the dims [HD/4*c, HD/4*(c+1)) of K row g of each 8-position tile, and the dims
 // [HD/8*g, HD/8*(g+1)) of the four V rows {2c, 2c+1, 2c+8, 2c+9} of each 16-position step.
 // A block's 4 warps serve G problems with 4/G warps each (positions dealt out in chunks of 32); online softmax per
 // head; the partial (max, sum, accumulator) are merged through shared memory, where the learned sink joins the
 // denominator only (run.cpp:588-591).
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-  // rows 8..15 of A (registers a1, a3) are zero: only query rows 0..7 are in use
+// a0/a2: rows 0..7 (k 0..7 / 8..15 of the step), a1/a3: rows 8..15; c[0..1]: rows 0..7, c[2..3]: rows 8..15
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 // (x, y) -> bf16 pair of the rounded values (hi) and of the remainders (lo); x in the low half
 __device__ __forceinline__ void split_pair(float x, float y, uint32_t &hi, uint32_t &lo) {
@@ -144,8 +148,6 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   const int prob = blockIdx.x * G + grp;
   const bool active = prob < n_problems;
   const int b = active ? prob / nkv : 0, kvh = active ? prob % nkv : 0;
-  const int kvdim = nkv * HD;
-
   uint32_t qh[KS][2], ql[KS][2];
 #pragma unroll
   for (int s = 0; s < KS; ++s) {
@@ -155,59 +157,69 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
     split_pair(v.z, v.w, qh[s][1], ql[s][1]);
   }
   const float scale = 1.0f / sqrtf((float)HD);
-  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + (size_t)b * S * kvdim + kvh * HD + D4 * c;
-  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + (size_t)b * S * kvdim + kvh * HD + DV * g;
+  // cache rows of this problem: [b, kvh, t, :], contiguous over t
+  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + ((size_t)b * nkv + kvh) * S * HD + D4 * c;
+  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + ((size_t)b * nkv + kvh) * S * HD + DV * g;
 
   float m_run = -FLT_MAX, l_part = 0.f;  // l_part: this thread's share of the denominator (its own positions)
   float o[DV][4];
 #pragma unroll
   for (int i = 0; i < DV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  if (active) {
-    for (int t0 = t_lo + 32 * ps; t0 <= pos; t0 += 32 * PS) {
-      // every load of the chunk is requested before the first use; rows past `pos` re-read row `pos` (masked below)
-      uint32_t kr[4][D4 / 2];
+  // The loads run one step ahead of their use: the K rows of the next chunk are requested as soon as the scores
+  // of this one have left the K registers, the V rows once the output MMAs have left the V registers, so that a
+  // warp always has a chunk's worth of rows in flight while it computes.  Rows past `pos` re-read row `pos` (their
+  // scores are masked).
+  uint32_t kr[4][D4 / 2], vr[2][4][DV / 2];
+  auto load_k = [&](int t0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(kbase + (size_t)min(t0 + 8 * j + g, pos) * kvdim);
+    for (int j = 0; j < 4; ++j) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(kbase + (size_t)min(t0 + 8 * j + g, pos) * HD);
 #pragma unroll
-        for (int u = 0; u < D4 / 8; ++u) {
-          const uint4 x = src[u];
-          kr[j][4 * u] = x.x, kr[j][4 * u + 1] = x.y, kr[j][4 * u + 2] = x.z, kr[j][4 * u + 3] = x.w;
+      for (int u = 0; u < D4 / 8; ++u) {
+        const uint4 x = src[u];
+        kr[j][4 * u] = x.x, kr[j][4 * u + 1] = x.y, kr[j][4 * u + 2] = x.z, kr[j][4 * u + 3] = x.w;
+      }
+    }
+  };
+  auto load_v = [&](int t0) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int row = 16 * s + 2 * c + (r & 1) + 8 * (r >> 1);
+        const uint16_t *src = vbase + (size_t)min(t0 + row, pos) * HD;
+        if (DV == 8) {
+          const uint4 x = *reinterpret_cast<const uint4 *>(src);
+          vr[s][r][0] = x.x, vr[s][r][1] = x.y, vr[s][r][DV / 2 - 2] = x.z, vr[s][r][DV / 2 - 1] = x.w;
+        } else {
+          const uint2 x = *reinterpret_cast<const uint2 *>(src);
+          vr[s][r][0] = x.x, vr[s][r][1] = x.y;
         }
       }
-      uint32_t vr[2][4][DV / 2];
-#pragma unroll
-      for (int s = 0; s < 2; ++s)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int row = 16 * s + 2 * c + (r & 1) + 8 * (r >> 1);
-          const uint16_t *src = vbase + (size_t)min(t0 + row, pos) * kvdim;
-          if (DV == 8) {
-            const uint4 x = *reinterpret_cast<const uint4 *>(src);
-            vr[s][r][0] = x.x, vr[s][r][1] = x.y, vr[s][r][DV / 2 - 2] = x.z, vr[s][r][DV / 2 - 1] = x.w;
-          } else {
-            const uint2 x = *reinterpret_cast<const uint2 *>(src);
-            vr[s][r][0] = x.x, vr[s][r][1] = x.y;
-          }
-        }
-      // scores of head g at positions t0 + 8j + 2c + {0,1}
+  };
+  const int t_first = t_lo + 32 * ps;
+  if (active && t_first <= pos) {
+    load_k(t_first);
+    load_v(t_first);
+    for (int t0 = t_first; t0 <= pos; t0 += 32 * PS) {
+      const int t_next = t0 + 32 * PS;
+      // scores of head g at positions t0 + 8j + 2c + {0,1}: rows 0..7 of the tile carry the bf16 heads of the
+      // queries, rows 8..15 their remainders, so that the sum of the two accumulator halves is the fp32-query product
       float p[4][2];
       float cmax = -FLT_MAX;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int s = 0; s < KS; ++s) {
-          mma_bf16_16816(acc, qh[s][0], qh[s][1], kr[j][2 * s], kr[j][2 * s + 1]);
-          mma_bf16_16816(acc, ql[s][0], ql[s][1], kr[j][2 * s], kr[j][2 * s + 1]);
-        }
+        for (int s = 0; s < KS; ++s) mma_bf16_16816(acc, qh[s][0], ql[s][0], qh[s][1], ql[s][1], kr[j][2 * s], kr[j][2 * s + 1]);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          p[j][e] = (t0 + 8 * j + 2 * c + e <= pos) ? acc[e] * scale : -FLT_MAX;
+          p[j][e] = (t0 + 8 * j + 2 * c + e <= pos) ? (acc[e] + acc[2 + e]) * scale : -FLT_MAX;
           cmax = fmaxf(cmax, p[j][e]);
         }
       }
+      if (t_next <= pos) load_k(t_next);
       cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 1));
       cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 2));
       const float m_new = fmaxf(m_run, cmax);  // finite: every chunk holds at least position t0 <= pos
@@ -223,9 +235,9 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
       l_part = l_part * corr + psum;
       m_run = m_new;
 #pragma unroll
-      for (int i = 0; i < DV; ++i) o[i][0] *= corr, o[i][1] *= corr;
+      for (int i = 0; i < DV; ++i) o[i][0] *= corr, o[i][1] *= corr, o[i][2] *= corr, o[i][3] *= corr;
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
+      for (int s = 0; s < 2; ++s) {  // probabilities: heads in rows 0..7, remainders in rows 8..15, as for the queries
         uint32_t a0h, a0l, a2h, a2l;
         split_pair(p[2 * s][0], p[2 * s][1], a0h, a0l);
         split_pair(p[2 * s + 1][0], p[2 * s + 1][1], a2h, a2l);
@@ -234,10 +246,10 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
           const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
           const uint32_t b0 = __byte_perm(vr[s][0][i >> 1], vr[s][1][i >> 1], sel);
           const uint32_t b1 = __byte_perm(vr[s][2][i >> 1], vr[s][3][i >> 1], sel);
-          mma_bf16_16816(o[i], a0h, a2h, b0, b1);
-          mma_bf16_16816(o[i], a0l, a2l, b0, b1);
+          mma_bf16_16816(o[i], a0h, a0l, a2h, a2l, b0, b1);
         }
       }
+      if (t_next <= pos) load_v(t_next);
     }
   }
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
@@ -248,8 +260,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   }
 #pragma unroll
   for (int i = 0; i < DV; ++i) {  // accumulator columns 2c, 2c+1 of n-tile i = dims DV*2c + i, DV*(2c+1) + i
-    acc_s[warp][g][DV * (2 * c) + i] = o[i][0];
-    acc_s[warp][g][DV * (2 * c + 1) + i] = o[i][1];
+    acc_s[warp][g][DV * (2 * c) + i] = o[i][0] + o[i][2];
+    acc_s[warp][g][DV * (2 * c + 1) + i] = o[i][1] + o[i][3];
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * kvm * HD; idx += blockDim.x) {
