@@ -38,7 +38,10 @@ EXPORTS = [
     "gptoss_comm_attach_local", "gptoss_comm_set_timeout_ms", "gptoss_moe_push_to_owners",
     "gptoss_moe_owner_combine", "gptoss_moe_add_delta", "gptoss_model_create", "gptoss_model_destroy",
     "gptoss_model_last_error", "gptoss_model_load_bin", "gptoss_model_load_mem", "gptoss_model_fill_synthetic", "gptoss_model_step",
-    "gptoss_model_read_logits",
+    "gptoss_model_read_logits", "gptoss_moe_slice_bounds", "gptoss_moe_gather_slice", "gptoss_moe_sliced_push",
+    "gptoss_moe_sliced_combine", "gptoss_moe_forward_sliced", "gptoss_model_create_ep", "gptoss_model_moe_ctx",
+    "gptoss_model_slice", "gptoss_model_step_begin", "gptoss_model_layer_attention", "gptoss_model_layer_moe_push",
+    "gptoss_model_layer_moe_combine", "gptoss_model_step_end",
 ]
 
 
@@ -129,6 +132,19 @@ def load() -> C.CDLL:
         "gptoss_model_fill_synthetic": ([vp, u64, f32], i32),
         "gptoss_model_step": ([vp, vp, i32, i32, vp], i32),
         "gptoss_model_read_logits": ([vp, i32, vp], i32),
+        "gptoss_moe_slice_bounds": ([ctxp, i32, C.POINTER(i32), C.POINTER(i32)], i32),
+        "gptoss_moe_gather_slice": ([ctxp, i32, vp, vp, vp, vp], i32),
+        "gptoss_moe_sliced_push": ([ctxp, i32, i32, vp], i32),
+        "gptoss_moe_sliced_combine": ([ctxp, vp, vp], i32),
+        "gptoss_moe_forward_sliced": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_model_create_ep": ([C.POINTER(ModelConfig), i32, i32, i32, i32, i32, C.POINTER(vp)], i32),
+        "gptoss_model_moe_ctx": ([vp], vp),
+        "gptoss_model_slice": ([vp, i32, C.POINTER(i32), C.POINTER(i32)], i32),
+        "gptoss_model_step_begin": ([vp, vp, i32, i32], i32),
+        "gptoss_model_layer_attention": ([vp, i32], i32),
+        "gptoss_model_layer_moe_push": ([vp, i32], i32),
+        "gptoss_model_layer_moe_combine": ([vp, i32], i32),
+        "gptoss_model_step_end": ([vp, vp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

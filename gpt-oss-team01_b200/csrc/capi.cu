@@ -48,6 +48,7 @@ struct gptoss_ctx {
   PeerTable peers{};
   bool attached = false;
   int comm_step = 0;
+  int gather_step = 0;  // token-sliced form: number of slice gathers so far (flag C carries it)
   int *status = nullptr;              // [kStatusWords]
   __nv_bfloat16 *t_stage = nullptr;   // [max_tokens,H]  device copies for the host-buffer entry point
   float *x_stage = nullptr;           // [max_tokens,H]
@@ -511,6 +512,63 @@ int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream) {
   CK(launch_add_delta(ctx->peers, ctx->wire == GPTOSS_WIRE_BF16, ctx->cur_T, ctx->d.H, ctx->comm_step, x_dev, ctx->status, ctx->sm_count,
                       static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
+}
+
+// ---- token-sliced form: every rank keeps only its slice of the residual stream ------------------------------
+int gptoss_moe_slice_bounds(const gptoss_ctx *ctx, int T, int *first, int *count) {
+  if (!ctx || T < 0) return GPTOSS_ERR_BAD_ARG;
+  const int slice = (T + ctx->world - 1) / ctx->world;
+  int b0 = ctx->rank * slice, n = T - b0;
+  n = n < 0 ? 0 : (n > slice ? slice : n);
+  if (n == 0) b0 = T;
+  if (first) *first = b0;
+  if (count) *count = n;
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const float *add_dev, const float *norm_w_dev,
+                            void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (!x_slice_dev || !norm_w_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice or norm-weight pointer");
+  if (T == 0) return GPTOSS_OK;
+  CK(cudaSetDevice(ctx->device));
+  const int step = ++ctx->gather_step;
+  CK(launch_slice_norm_gather(ctx->peers, T, ctx->d.H, x_slice_dev, add_dev, norm_w_dev, step, ctx->comm_counter,
+                              static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (T == 0) return GPTOSS_OK;
+  if (ctx->gather_step == 0) return ctx->fail(GPTOSS_ERR_STATE, "sliced push before any gather_slice");
+  CK(cudaSetDevice(ctx->device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CK(launch_wait_gathered(ctx->peers, ctx->gather_step, ctx->status, s));
+  if ((rc = gptoss_moe_route(ctx, layer, T, ctx->sym + ctx->sym_delta_off, stream))) return rc;
+  if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
+  return gptoss_moe_push_to_owners(ctx, layer, stream);
+}
+
+int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if (!x_slice_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  CK(launch_combine_owner_slice(ctx->peers, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, x_slice_dev, ctx->status,
+                                ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_forward_sliced(gptoss_ctx *ctx, int layer, int T, float *x_slice_dev, void *stream) {
+  int rc = gptoss_moe_sliced_push(ctx, layer, T, stream);
+  if (rc) return rc;
+  return gptoss_moe_sliced_combine(ctx, x_slice_dev, stream);
 }
 
 // ---- the per-layer operator --------------------------------------------------------------------------------

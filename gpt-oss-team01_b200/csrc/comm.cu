@@ -9,6 +9,11 @@
 // (the all-gather, again by peer stores) and raises flag B everywhere.  Each rank finally waits for flag B
 // of all owners and adds `delta` to its replicated residual stream.
 //
+// Token-sliced variant (each rank keeps only its own slice of the residual stream, e.g. behind data-parallel
+// attention): a rank normalises its slice and stores the bf16 rows into the gathered activation buffer of EVERY
+// rank (flag C), all ranks route the full batch and push to the owners as above, and the owner adds the slot-ordered
+// sum to its own residual slice: no delivery step, half the NVLink traffic of the replicated form.
+//
 // Flags carry the step number (monotonic), so nothing is ever reset.  All waits are bounded by wall time;
 // a wait that gives up records a time-out in the status words and the kernel carries on without waiting.
 #include "kernels.cuh"
@@ -139,6 +144,72 @@ __global__ void __launch_bounds__(256) add_delta_kernel(PeerTable pt, int T, int
   }
 }
 
+// Token-sliced form, producer side.  Residual update + RMSNorm of the rows of this rank's slice (one block per row,
+// the arithmetic of the single-GPU residual_rmsnorm kernel: fp32 squares per thread, warp sums, double across
+// warps), each bf16 row stored into the gathered activation buffer of every rank; the last block raises flag C.
+__global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, int T, int H, float *__restrict__ x_slice,
+                                                                const float *__restrict__ add, const float *__restrict__ w,
+                                                                int step, int *counter) {
+  __shared__ double part[8];
+  const int slice = (T + pt.world - 1) / pt.world;
+  const int b0 = pt.rank * slice, n_rows = max(0, min(T, b0 + slice) - b0);
+  const int i_row = blockIdx.x;
+  if (i_row < n_rows) {
+    float *xr = x_slice + (size_t)i_row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i];
+      if (add) {
+        v += add[(size_t)i_row * H + i];
+        xr[i] = v;
+      }
+      ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
+    const float inv = 1.0f / sqrtf((float)(tot / H + 1e-5));
+    const size_t row = (size_t)(b0 + i_row) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const __nv_bfloat16 v = __float2bfloat16_rn(w[i] * (inv * xr[i]));
+      for (int r = 0; r < pt.world; ++r) reinterpret_cast<__nv_bfloat16 *>(pt.delta[r])[row + i] = v;
+    }
+  }
+  signal_all_ranks(pt, 2, step, counter);
+}
+
+// Token-sliced form, consumer side: returns once every rank's slice of the gathered activations has arrived.
+__global__ void wait_gathered_kernel(PeerTable pt, int step, int *status) {
+  wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2300);
+}
+
+// Token-sliced form, owner side: x_slice[i,:] += ((s0+s1)+s2)+s3 for the rows of this rank's slice, slots in order.
+__global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, int T, int H, int k, int step,
+                                                                  float *__restrict__ x_slice, int *status) {
+  wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2400);
+  const int slice = (T + pt.world - 1) / pt.world;
+  const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
+  const int h4 = H >> 2;
+  const size_t total = (size_t)max(0, b1 - b0) * h4;
+  const float4 *y = reinterpret_cast<const float4 *>(pt.y[pt.rank]);
+  float4 *xp = reinterpret_cast<float4 *>(x_slice);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int b = b0 + (int)(i / h4), c = (int)(i % h4);
+    const size_t row4 = (size_t)b * k * h4 + c;
+    float4 a = y[row4];
+    for (int j = 1; j < k; ++j) {
+      const float4 v = y[row4 + (size_t)j * h4];
+      a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    }
+    float4 o = xp[i];
+    o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
+    xp[i] = o;
+  }
+}
+
 cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s) {
   signal_pushed_kernel<<<1, 32, 0, s>>>(pt, step);
   return cudaGetLastError();
@@ -168,6 +239,31 @@ cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, 
     add_delta_kernel<true><<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
   else
     add_delta_kernel<false><<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x_slice, const float *add, const float *w,
+                                     int step, int *counter, cudaStream_t s) {
+  const int slice = (T + pt.world - 1) / pt.world;
+  int rows = T - pt.rank * slice;
+  rows = rows < 0 ? 0 : (rows > slice ? slice : rows);
+  slice_norm_gather_kernel<<<rows > 0 ? rows : 1, 256, 0, s>>>(pt, T, H, x_slice, add, w, step, counter);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s) {
+  wait_gathered_kernel<<<1, 32, 0, s>>>(pt, step, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
+                                       int sm_count, cudaStream_t s) {
+  const int slice = (T + pt.world - 1) / pt.world;
+  const size_t total = (size_t)slice * (H >> 2);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > sm_count * 16) blocks = sm_count * 16;
+  if (blocks < 1) blocks = 1;
+  combine_owner_slice_kernel<<<blocks, 256, 0, s>>>(pt, T, H, k, step, x_slice, status);
   return cudaGetLastError();
 }
 

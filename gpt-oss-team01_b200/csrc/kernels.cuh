@@ -53,14 +53,22 @@ struct PeerTable {
   int rank, world;
   unsigned long long timeout_ns;  // limit of every wait on a peer flag
   float *y[kMaxRanks];      // every rank's y_pairs  [P,H] fp32 (index = own rank: local memory)
-  float *delta[kMaxRanks];  // every rank's delta    [T,H] fp32, or bf16 in the same storage (bf16 wire)
-  int *flags[kMaxRanks];    // every rank's flags    [2][kMaxRanks]: A = "rank r pushed", B = "owner r delivered"
+  float *delta[kMaxRanks];  // every rank's delta    [T,H] fp32, or bf16 in the same storage (bf16 wire); in the token-sliced
+                            //                       form the same storage holds the gathered activations [T,H] bf16
+  int *flags[kMaxRanks];    // every rank's flags    [3][kMaxRanks]: A = "rank r pushed", B = "owner r delivered",
+                            //                       C = "rank r stored its slice of the gathered activations"
 };
 cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s);
 cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
                                  int *counter, int sm_count, cudaStream_t s);
 cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, int step, float *x, int *status,
                              int sm_count, cudaStream_t s);
+
+cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x_slice, const float *add, const float *w,
+                                     int step, int *counter, cudaStream_t s);
+cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s);
+cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
+                                       int sm_count, cudaStream_t s);
 
 // router.cu
 struct RouterArgs {

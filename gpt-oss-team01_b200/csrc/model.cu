@@ -1,5 +1,11 @@
-// Whole-model decode step around the MoE block: the B200 counterpart of forward_gpu_20b_batched
-// (getp-csrc/src/model.cpp:6-151) and of the CPU forward() (run.cpp:501-717), for ONE GPU.
+// Whole-model decode step around the MoE block: the B200 counterpart of forward_gpu_20b_batched /
+// forward_gpu_120b_batched (getp-csrc/src/model.cpp:6-151, 153-489) and of the CPU forward() (run.cpp:501-717).
+//
+// One GPU holds the whole model, or `world` GPUs (one model object each) split the work: the sequences of the
+// batch are dealt out in contiguous slices (attention, dense GEMMs, KV cache and residual stream of a sequence live
+// on its rank only: data-parallel attention, no attention-side all-reduce) and the experts are sharded by rank;
+// per layer the ranks exchange the normalised activations (each stores its slice to all) and the expert outputs
+// (stored to the token's owner from the down-GEMM epilogue), both over peer memory.
 //
 // Per step (all sequences at the same position, prompt tokens force-fed by the caller — the reference's
 // lock-step decode): embedding -> per layer [RMSNorm -> QKV GEMM -> RoPE + KV store -> single-query attention
@@ -25,6 +31,9 @@ using namespace gptoss;
 struct gptoss_model {
   gptoss_model_config c;
   int device = 0, max_batch = 0, S = 0, sm_count = kSmCountFallback;
+  int rank = 0, world = 1;
+  int max_local = 0;                    // sequences this rank can hold: max_batch, or its slice of it
+  int step_B = 0, step_pos = 0, step_first = 0, step_n = 0;  // the step in progress: global batch, position, own slice
   gptoss_ctx *moe = nullptr;
   // weights
   __nv_bfloat16 *emb = nullptr, *unemb = nullptr, *w_qkv = nullptr, *w_o = nullptr;
@@ -138,7 +147,7 @@ int dense(gptoss_model *m, int which, const CUtensorMap &map_w, const CUtensorMa
   a.status = m->status;
   a.n_owners = 1;
   a.top_k = 1;
-  a.slice_tokens = m->max_batch;
+  a.slice_tokens = m->max_local;
   MK(launch_grouped_mlp2(a, m->sm_count, m->stream));
   return GPTOSS_OK;
 }
@@ -182,22 +191,31 @@ int set_batch(gptoss_model *m, int B) {
 extern "C" {
 
 int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batch, int max_seq, gptoss_model **out) {
+  return gptoss_model_create_ep(cfg, device, 0, 1, max_batch, max_seq, out);
+}
+
+int gptoss_model_create_ep(const gptoss_model_config *cfg, int device, int rank, int world, int max_batch, int max_seq,
+                           gptoss_model **out) {
   if (!cfg || !out) return GPTOSS_ERR_BAD_ARG;
   *out = nullptr;
   const gptoss_model_config &c = *cfg;
   if (c.vocab_size <= 0 || c.hidden_dim <= 0 || c.hidden_dim % 8 || c.n_layers <= 0 || (c.head_dim != 32 && c.head_dim != 64) ||
       c.n_attn_heads <= 0 || c.n_kv_heads <= 0 || c.n_attn_heads % c.n_kv_heads ||
       (c.n_attn_heads / c.n_kv_heads != 1 && c.n_attn_heads / c.n_kv_heads != 2 && c.n_attn_heads / c.n_kv_heads != 4 &&
-       c.n_attn_heads / c.n_kv_heads != 8) || max_batch <= 0 || max_seq <= 0 || max_seq > c.seq_len)
+       c.n_attn_heads / c.n_kv_heads != 8) || max_batch <= 0 || max_seq <= 0 || max_seq > c.seq_len || world <= 0 ||
+      rank < 0 || rank >= world)
     return GPTOSS_ERR_BAD_ARG;
   gptoss_model *m = new (std::nothrow) gptoss_model();
   if (!m) return GPTOSS_ERR_CUDA;
   m->c = c;
   m->device = device;
   m->max_batch = max_batch;
+  m->rank = rank;
+  m->world = world;
+  m->max_local = (max_batch + world - 1) / world;
   m->S = max_seq;
   gptoss_moe_dims d{c.hidden_dim, c.intermediate_dim, c.n_experts, c.experts_per_token, c.n_layers, c.swiglu_limit};
-  int rc = gptoss_ctx_create(&d, device, 0, 1, max_batch, GPTOSS_WIRE_F32, &m->moe);
+  int rc = gptoss_ctx_create(&d, device, rank, world, max_batch, GPTOSS_WIRE_F32, &m->moe);
   if (rc) {
     delete m;
     return rc;
@@ -205,7 +223,7 @@ int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batc
   cudaDeviceProp prop;
   cudaGetDeviceProperties(&prop, device);
   m->sm_count = prop.multiProcessorCount;
-  const size_t L = c.n_layers, H = c.hidden_dim, V = c.vocab_size, B = max_batch, S = max_seq;
+  const size_t L = c.n_layers, H = c.hidden_dim, V = c.vocab_size, B = m->max_local, S = max_seq;
   const size_t qd = (size_t)c.head_dim * c.n_attn_heads, kvd = (size_t)c.head_dim * c.n_kv_heads, qkvd = qd + 2 * kvd;
   cudaError_t e = cudaSuccess;
   auto A = [&](cudaError_t r) {
@@ -378,55 +396,131 @@ int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma) {
   return GPTOSS_OK;
 }
 
-// One lock-step decode step: tokens[B] at position `pos` -> greedy next tokens[B]
-// (forward_gpu_20b_batched, getp-csrc/src/model.cpp:6-151; CPU: forward + sample_argmax, run.cpp:501,739).
-int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host) {
+// ---- one lock-step decode step, in phases -------------------------------------------------------------------
+// gptoss_model_step runs them in order; they are separate entry points so that a host can interleave the ranks of
+// an expert-parallel group itself (several model objects driven by one thread, e.g. on one device in a test).
+//   step_begin         tokens of this rank's sequences -> embedding rows (the residual stream)
+//   layer_attention    RMSNorm -> QKV GEMM -> RoPE + KV store -> attention -> o-proj GEMM -> residual + RMSNorm
+//                      (expert-parallel: the normalised rows go to every rank's gathered activations)
+//   layer_moe_push     one GPU: the whole MoE block.  Expert-parallel: routing of the gathered batch, expert GEMMs of
+//                      this rank's experts, rows pushed to the tokens' owners
+//   layer_moe_combine  expert-parallel only: slot-ordered sum of the pushed rows into this rank's residual rows
+//   step_end           final RMSNorm -> classifier GEMM -> argmax -> next tokens of this rank's sequences
+int gptoss_model_slice(const gptoss_model *m, int B, int *first, int *count) {
   if (!m) return GPTOSS_ERR_BAD_ARG;
-  if (!tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
+  return gptoss_moe_slice_bounds(m->moe, B, first, count);
+}
+
+gptoss_ctx *gptoss_model_moe_ctx(gptoss_model *m) { return m ? m->moe : nullptr; }
+
+int gptoss_model_step_begin(gptoss_model *m, const int *tokens_host, int pos, int B) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
   if (B <= 0 || B > m->max_batch || pos < 0 || pos >= m->S) return m->fail(GPTOSS_ERR_BAD_ARG, "batch or position out of range");
   if (!m->weights_ready) return m->fail(GPTOSS_ERR_STATE, "model has no weights yet");
   MK(cudaSetDevice(m->device));
-  int rc = set_batch(m, B);
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(m->moe, B, &first, &n);
+  if (n > 0 && !tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
+  m->step_B = B, m->step_pos = pos, m->step_first = first, m->step_n = n;
+  if (n == 0) return GPTOSS_OK;
+  int rc = set_batch(m, n);
   if (rc) return rc;
+  MK(cudaMemcpyAsync(m->tokens_dev, tokens_host, n * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+  MK(launch_embed(m->tokens_dev, m->emb, n, m->c.hidden_dim, m->c.vocab_size, m->x, m->stream));
+  return GPTOSS_OK;
+}
+
+int gptoss_model_layer_attention(gptoss_model *m, int layer) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (layer < 0 || layer >= m->c.n_layers || m->step_B <= 0) return m->fail(GPTOSS_ERR_STATE, "no step in progress or bad layer");
+  MK(cudaSetDevice(m->device));
   const gptoss_model_config &c = m->c;
-  const size_t L = c.n_layers, H = c.hidden_dim, S = m->S;
-  const int nq = c.n_attn_heads, nkv = c.n_kv_heads, hd = c.head_dim;
+  const size_t l = layer, H = c.hidden_dim, S = m->S;
+  const int nq = c.n_attn_heads, nkv = c.n_kv_heads, hd = c.head_dim, B = m->step_n, pos = m->step_pos;
   const size_t qd = (size_t)hd * nq, kvd = (size_t)hd * nkv, qkvd = qd + 2 * kvd;
   cudaStream_t s = m->stream;
-  MK(cudaMemcpyAsync(m->tokens_dev, tokens_host, B * sizeof(int), cudaMemcpyHostToDevice, s));
-  MK(launch_embed(m->tokens_dev, m->emb, B, (int)H, c.vocab_size, m->x, s));
-  for (size_t l = 0; l < L; ++l) {
+  int rc;
+  if (B > 0) {
     MK(launch_residual_rmsnorm(m->x, nullptr, m->attn_norm + l * H, B, (int)H, m->t, s));
     if ((rc = dense(m, kDenseQkv, m->map_qkv[l], m->map_t, (int)H, (int)qkvd, m->b_qkv + l * qkvd, m->qkv))) return rc;
-    __nv_bfloat16 *kc = m->k_cache + l * (size_t)m->max_batch * S * kvd, *vc = m->v_cache + l * (size_t)m->max_batch * S * kvd;
+    __nv_bfloat16 *kc = m->k_cache + l * (size_t)m->max_local * S * kvd, *vc = m->v_cache + l * (size_t)m->max_local * S * kvd;
     MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, s));
     const bool windowed = c.sliding_window > 0 && (l % 2 == 0);  // run.cpp:582
     const int t_lo = windowed ? (pos - c.sliding_window + 1 > 0 ? pos - c.sliding_window + 1 : 0) : 0;
     MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, s));
     if ((rc = dense(m, kDenseOut, m->map_o[l], m->map_att, (int)qd, (int)H, m->b_o + l * H, m->proj))) return rc;
-    MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
-    if ((rc = gptoss_moe_forward(m->moe, (int)l, B, m->t, m->x, s))) return m->fail(rc, gptoss_last_error(m->moe));
   }
-  if (next_tokens_host) {  // a step whose outputs are all overridden by prompt tokens needs no logits
-    MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, (int)H, m->t, s));
-    if ((rc = dense(m, kDenseVocab, m->map_unemb, m->map_t, (int)H, c.vocab_size, nullptr, m->logits))) return rc;
+  if (m->world == 1) {
+    MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
+  } else if ((rc = gptoss_moe_gather_slice(m->moe, m->step_B, m->x, m->proj, m->mlp_norm + l * H, s))) {
+    return m->fail(rc, gptoss_last_error(m->moe));
+  }
+  return GPTOSS_OK;
+}
+
+int gptoss_model_layer_moe_push(gptoss_model *m, int layer) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (layer < 0 || layer >= m->c.n_layers || m->step_B <= 0) return m->fail(GPTOSS_ERR_STATE, "no step in progress or bad layer");
+  const int rc = m->world == 1 ? gptoss_moe_forward(m->moe, layer, m->step_B, m->t, m->x, m->stream)
+                               : gptoss_moe_sliced_push(m->moe, layer, m->step_B, m->stream);
+  return rc ? m->fail(rc, gptoss_last_error(m->moe)) : GPTOSS_OK;
+}
+
+int gptoss_model_layer_moe_combine(gptoss_model *m, int layer) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (layer < 0 || layer >= m->c.n_layers || m->step_B <= 0) return m->fail(GPTOSS_ERR_STATE, "no step in progress or bad layer");
+  if (m->world == 1) return GPTOSS_OK;
+  const int rc = gptoss_moe_sliced_combine(m->moe, m->x, m->stream);
+  return rc ? m->fail(rc, gptoss_last_error(m->moe)) : GPTOSS_OK;
+}
+
+int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (m->step_B <= 0) return m->fail(GPTOSS_ERR_STATE, "no step in progress");
+  MK(cudaSetDevice(m->device));
+  const gptoss_model_config &c = m->c;
+  const int B = m->step_n, H = c.hidden_dim;
+  cudaStream_t s = m->stream;
+  int rc;
+  if (next_tokens_host && B > 0) {  // a step whose outputs are all overridden by prompt tokens needs no logits
+    MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, H, m->t, s));
+    if ((rc = dense(m, kDenseVocab, m->map_unemb, m->map_t, H, c.vocab_size, nullptr, m->logits))) return rc;
     MK(launch_argmax(m->logits, B, c.vocab_size, m->next_dev, s));
     MK(cudaMemcpyAsync(next_tokens_host, m->next_dev, B * sizeof(int), cudaMemcpyDeviceToHost, s));
   }
   int st[kStatusWords];
   MK(cudaMemcpyAsync(st, m->status, sizeof st, cudaMemcpyDeviceToHost, s));
   MK(cudaStreamSynchronize(s));
+  m->step_B = 0;
   if (st[0] != 0) {
     cudaMemset(m->status, 0, sizeof st);
     return m->fail(GPTOSS_ERR_TIMEOUT, "device-side bounded wait gave up in a dense GEMM");
   }
-  return gptoss_ctx_status(m->moe);
+  rc = gptoss_ctx_status(m->moe);
+  return rc ? m->fail(rc, gptoss_last_error(m->moe)) : GPTOSS_OK;
+}
+
+// One lock-step decode step: tokens of this rank's sequences at position `pos` -> their greedy next tokens
+// (forward_gpu_20b_batched / forward_gpu_120b_batched, getp-csrc/src/model.cpp:6-151,153-489; CPU: forward +
+// sample_argmax, run.cpp:501,739).  B is the batch of the whole group.
+int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host) {
+  int rc = gptoss_model_step_begin(m, tokens_host, pos, B);
+  for (int l = 0; !rc && l < m->c.n_layers; ++l) {
+    if ((rc = gptoss_model_layer_attention(m, l))) break;
+    if ((rc = gptoss_model_layer_moe_push(m, l))) break;
+    rc = gptoss_model_layer_moe_combine(m, l);
+  }
+  if (rc) {
+    if (m) m->step_B = 0;
+    return rc;
+  }
+  return gptoss_model_step_end(m, next_tokens_host);
 }
 
 // Copies the logits of one sequence of the last step to the host (debug/parity tap).
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out) {
   if (!m || !host_out) return GPTOSS_ERR_BAD_ARG;
-  if (row < 0 || row >= m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "row out of range");
+  if (row < 0 || row >= m->max_local) return m->fail(GPTOSS_ERR_BAD_ARG, "row out of range");
   MK(cudaSetDevice(m->device));
   MK(cudaMemcpy(host_out, m->logits + (size_t)row * m->c.vocab_size, (size_t)m->c.vocab_size * sizeof(float),
                 cudaMemcpyDeviceToHost));

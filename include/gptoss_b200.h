@@ -137,6 +137,29 @@ int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream);
 int gptoss_moe_owner_combine(gptoss_ctx *ctx, void *stream);
 int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream);
 
+/* ---- token-sliced form of the expert-parallel block ------------------------------------------------
+ * For callers that keep only a slice of the residual stream on each GPU (data-parallel attention in front
+ * of the expert-parallel block): rank r owns tokens [r*ceil(T/world), ...).  It replaces, together,
+ * ring_all_reduce_tb2_quantize_fp8 + residual_rmsnorm (the all-reduce that re-creates the replicated
+ * activations, getp-csrc/src/parallelism.cpp:1195, layer_hip_batch.cpp:95) and the second half of
+ * ring_reduce_agg_quantize_fp8 (the all-gather of the reduced sums, parallelism.cpp:1605-1670): the owner
+ * keeps the sums, nothing is delivered back.  Results are bit-identical to the replicated form and to one GPU.
+ *   slice_bounds   : first token and token count of this rank's slice for a batch of T tokens;
+ *   gather_slice   : x_slice += add (if add != NULL); bf16(RMSNorm(x_slice) * norm_w) stored into the gathered
+ *                    activation buffer [T,H] of EVERY rank; raises this rank's "gathered" flag everywhere;
+ *   sliced_push    : waits for the "gathered" flags of all ranks, routes the T gathered tokens, gate/up GEMM +
+ *                    SwiGLU, down GEMM pushing to the owners, raises "pushed";
+ *   sliced_combine : waits for "pushed" of all ranks; x_slice += slot-ordered sum of this rank's tokens;
+ *   forward_sliced : sliced_push + sliced_combine.
+ * x_slice_dev, add_dev: fp32 [slice count, H] on the device; norm_w_dev: fp32 [H].  Every rank must make the
+ * same sequence of these calls; they must not be interleaved with the replicated form within one step. */
+int gptoss_moe_slice_bounds(const gptoss_ctx *ctx, int T, int *first, int *count);
+int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const float *add_dev, const float *norm_w_dev,
+                            void *stream);
+int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream);
+int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream);
+int gptoss_moe_forward_sliced(gptoss_ctx *ctx, int layer, int T, float *x_slice_dev, void *stream);
+
 /* ---- stages of the operator (same order as inside gptoss_moe_forward) ------------------------------
  * They work on the context's scratch so that a test can stop after any stage and read the taps. */
 /* router_gemm_v2 + topk_softmax_batched + moe_build_offsets_hip + moe_pack_inputs_hip
@@ -210,11 +233,27 @@ typedef struct {
 
 typedef struct gptoss_model gptoss_model;
 
-/* One GPU holding the whole model (weights bf16, KV cache bf16 [layer][sequence][position][kv_dim], scratch
- * for max_batch sequences of at most max_seq positions).  Replaces build_transformer + our_init for the
+/* One GPU holding the whole model (weights bf16, KV cache bf16 [layer][sequence][kv head][position][head_dim],
+ * scratch for max_batch sequences of at most max_seq positions).  Replaces build_transformer + our_init for the
  * single-GPU (20B-style, data-parallel replica) engine: run.cpp:283, getp-csrc/src/alloc.cpp:1035.
  * Limits: head_dim 32 or 64; 1, 2, 4 or 8 query heads per kv head. */
 int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batch, int max_seq, gptoss_model **out);
+/* Rank `rank` of a group of `world` GPUs that decode one batch together (the 120B-style engine,
+ * forward_gpu_120b_batched, getp-csrc/src/model.cpp:153-489; one model object per GPU, one calling thread or
+ * process each).  max_batch is the batch of the whole group.  The sequences are dealt out in contiguous slices
+ * (gptoss_model_slice): attention, dense GEMMs, KV cache and residual stream of a sequence live on its rank only, so
+ * the attention side needs no all-reduce (the reference's ring_all_reduce_tb2_quantize_fp8, parallelism.cpp:1195,
+ * has no counterpart); the experts are sharded by rank (n_experts % world == 0) and each layer exchanges the
+ * normalised activations and the expert outputs over peer memory (token-sliced form of the MoE block above).
+ * Every rank loads the same checkpoint (or the same synthetic seed) and keeps its share.  Before the first step
+ * the ranks' MoE contexts (gptoss_model_moe_ctx) must be attached to one another with gptoss_comm_export /
+ * gptoss_comm_attach (processes) or gptoss_comm_attach_local (one process).  A decode must keep the same batch
+ * size B on every step (a sequence stays on its rank).  Results are bit-identical to the single-GPU model. */
+int gptoss_model_create_ep(const gptoss_model_config *cfg, int device, int rank, int world, int max_batch, int max_seq,
+                           gptoss_model **out);
+gptoss_ctx *gptoss_model_moe_ctx(gptoss_model *m);
+/* First sequence and number of sequences of this rank for a batch of B (everything for a single-GPU model). */
+int gptoss_model_slice(const gptoss_model *m, int B, int *first, int *count);
 int gptoss_model_destroy(gptoss_model *m);
 const char *gptoss_model_last_error(const gptoss_model *m);
 /* load_checkpoint (run.cpp:235-281): reads a flat model.bin (header + fp32 tensors in the order of
@@ -233,6 +272,19 @@ int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma);
  * caller would discard anyway (every sequence still inside its prompt): the KV caches are updated, the
  * final norm, classifier and argmax are skipped.  Synchronous. */
 int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host);
+/* The phases of gptoss_model_step, which runs begin, then per layer attention / moe_push / moe_combine, then end.
+ * In a group, B is the batch of the group and tokens_host / next_tokens_host hold this rank's sequences only.
+ * Separate entry points so that one host thread can drive the ranks of a group in turn (each phase for every rank
+ * before the next phase: a rank's moe_push waits on the device for every rank's attention phase, its moe_combine
+ * for every rank's moe_push).  attention: RMSNorm, QKV GEMM, RoPE + KV store, attention, o-proj GEMM, residual +
+ * RMSNorm (group: stored into every rank's gathered activations).  moe_push: the MoE block (group: routing, expert
+ * GEMMs, rows pushed to their owners).  moe_combine: group only, the owner's slot-ordered sum into its residual
+ * rows.  end: final norm, classifier, argmax, synchronises and reports device-side errors. */
+int gptoss_model_step_begin(gptoss_model *m, const int *tokens_host, int pos, int B);
+int gptoss_model_layer_attention(gptoss_model *m, int layer);
+int gptoss_model_layer_moe_push(gptoss_model *m, int layer);
+int gptoss_model_layer_moe_combine(gptoss_model *m, int layer);
+int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host);
 /* Logits (fp32 [vocab]) of one sequence of the last step; debug/parity tap (PRINT_LOGITS, getp_run.cpp:236). */
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out);
 
