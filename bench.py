@@ -400,36 +400,67 @@ def run_ours(args):
 
 
 def run_decode(args):
-    """Whole-model batched greedy decode of the gpt-oss-20b architecture on ONE GPU (random-init weights generated
-    on the device): 1024 sequences of 128 random prompt ids force-fed one position per step, then 256 generated
-    tokens — BASELINE config 4 at N = 1.  Reported like the reference's getp mode: generated tokens / wall time of
-    the whole inference loop (getp-csrc/getp_eval.cpp:125-131)."""
+    """Whole-model batched greedy decode (random-init weights generated on the device), sequences of random prompt
+    ids force-fed one position per step, then greedy tokens.  decode20b: gpt-oss-20b architecture, 1024 x 128 prompt
+    ids, 256 generated (BASELINE config 4); decode120b: gpt-oss-120b architecture, 2048 x 256, 256 generated
+    (config 5; needs the experts spread over >= 4 GPUs).  With N > 1 (one process per GPU) the N GPUs decode the
+    batch together: sequences in slices, experts sharded, per-layer exchange over peer memory.  Reported like the
+    reference's getp mode: generated tokens / wall time of the whole inference loop (getp-csrc/getp_eval.cpp:125-131),
+    the slowest rank's time."""
     import torch
     from gptoss_b200 import binfmt, model
-    B, n_prompt, n_gen = args.decode_batch, args.decode_prompt, args.decode_gen
-    cfg = binfmt.config_20b(seq_len=1024)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    big = args.workload == "decode120b"
+    B = args.decode_batch or (2048 if big else 1024)
+    n_prompt = args.decode_prompt or (256 if big else 128)
+    n_gen = args.decode_gen or 256
+    cfg = binfmt.config_120b(seq_len=1024) if big else binfmt.config_20b(seq_len=1024)
     if args.decode_layers:
         cfg.n_layers = args.decode_layers
-    torch.cuda.set_device(0)
-    m = model.Model(cfg, device=0, max_batch=B, max_seq=n_prompt + n_gen)
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    m = model.Model(cfg, device=local_rank, max_batch=B, max_seq=n_prompt + n_gen, rank=rank, world=world)
     m.fill_synthetic(SEED, SIGMA)
-    prompts = synth.uniform_ids(SEED, 11, B * n_prompt, cfg.vocab_size).reshape(B, n_prompt)
-    m.generate(prompts[:, :2], 2)  # warm-up: 3 steps
-    with ClockSampler(0) as clocks:
+    if world > 1:
+        m.attach_peers()
+    first, n = m.slice(B)
+    prompts = synth.uniform_ids(SEED, 11, B * n_prompt, cfg.vocab_size).reshape(B, n_prompt)[first:first + n]
+    m.generate(prompts[:, :2], 2, batch=B)  # warm-up: 3 steps
+    if world > 1:
+        dist.barrier()
+    with ClockSampler(local_rank) as clocks:
         t0 = time.perf_counter()
-        out = m.generate(prompts, n_gen)
+        out = m.generate(prompts, n_gen, batch=B)
         dt = time.perf_counter() - t0
+    n_distinct = int(len(np.unique(out)))
+    if world > 1:
+        tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        dist.barrier()
     steps = n_prompt + n_gen - 1
-    line = {"metric": "batched decode tok/s, gpt-oss-20b arch (whole model, greedy, lock-step)", "value": B * n_gen / dt,
-            "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": 1e3 * dt / steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+    arch = "gpt-oss-120b" if big else "gpt-oss-20b"
+    line = {"metric": f"batched decode tok/s, {arch} arch (whole model, greedy, lock-step)", "value": B * n_gen / dt,
+            "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": 1e3 * dt / steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": f"gpt-oss-20b architecture, {cfg.n_layers} layers, batch {B} x {n_prompt} random prompt "
+            "config": {"workload": f"{arch} architecture, {cfg.n_layers} layers, batch {B} x {n_prompt} random prompt "
                                    f"ids, greedy decode {n_gen} tokens; tokens in/out over host memory every step",
+                       "parallelism": "one GPU" if world == 1 else
+                       f"{world} GPUs: sequences in {world} slices (data-parallel attention), {cfg.n_experts // world} "
+                       "experts per GPU, activations and expert rows exchanged over NVLink peer memory",
                        "positions_per_second": B * steps / dt, "seed": SEED},
-            "clocks": clocks.summary(), "distinct_tokens_generated": int(len(np.unique(out)))}
+            "clocks": clocks.summary(), "distinct_tokens_generated_rank0": n_distinct}
     m.close()
-    print_line(line)
+    if rank == 0:
+        print_line(line)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -448,11 +479,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
                     help="N > 1: format in which owners deliver the summed rows (rows travel to the owner in fp32)")
-    ap.add_argument("--workload", choices=["moe_layer", "decode20b"], default="moe_layer",
+    ap.add_argument("--workload", choices=["moe_layer", "decode20b", "decode120b"], default="moe_layer",
                     help="moe_layer: the MoE block (headline); decode20b: whole-model greedy decode on one GPU")
-    ap.add_argument("--decode-batch", type=int, default=1024)
-    ap.add_argument("--decode-prompt", type=int, default=128)
-    ap.add_argument("--decode-gen", type=int, default=256)
+    ap.add_argument("--decode-batch", type=int, default=0, help="0 = the config's batch (1024 / 2048)")
+    ap.add_argument("--decode-prompt", type=int, default=0, help="0 = the config's prompt length (128 / 256)")
+    ap.add_argument("--decode-gen", type=int, default=0, help="0 = 256")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count (0 = 24)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
@@ -460,7 +491,7 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "decode20b":
+    elif args.workload in ("decode20b", "decode120b"):
         run_decode(args)
     else:
         run_ours(args)

@@ -71,6 +71,14 @@ class Model:
         assert len(blob) == self.world * capi.IPC_HANDLE_BYTES
         self._check(self.lib.gptoss_comm_attach(self._ctx(), blob))
 
+    def attach_peers(self, group=None):
+        """One process per GPU: exchanges the IPC handles over torch.distributed and attaches all ranks."""
+        import torch.distributed as dist
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, self.comm_export(), group=group)
+        self.comm_attach(gathered)
+        dist.barrier(group=group)
+
     @staticmethod
     def attach_local(models):
         """Attaches the ranks of a group whose model objects live in this process (rank order)."""
@@ -124,17 +132,19 @@ class Model:
         self._check(self.lib.gptoss_model_read_logits(self._m, row, out.ctypes.data_as(C.c_void_p)))
         return out
 
-    def generate(self, prompts, n_generate, stop_on_eos=False):
+    def generate(self, prompts, n_generate, stop_on_eos=False, batch=None):
         """prompts: int32 [B, n_prompt] (same length).  Returns int32 [B, n_generate]: the greedy continuation,
         prompt tokens force-fed one position per step; a sequence that emits an end-of-sequence id keeps
-        running in lock-step (its later tokens are ignored by the caller) unless stop_on_eos trims them to -1."""
+        running in lock-step (its later tokens are ignored by the caller) unless stop_on_eos trims them to -1.
+        In a group, ``prompts`` holds this rank's sequences and ``batch`` is the batch of the whole group; every
+        rank must call generate with the same prompt length and n_generate."""
         prompts = np.ascontiguousarray(prompts, dtype=np.int32)
         B, n_prompt = prompts.shape
         out = np.full((B, n_generate), -1, np.int32)
         done = np.zeros(B, bool)
         tok = prompts[:, 0].copy()
         for pos in range(n_prompt + n_generate - 1):
-            nxt = self.step(tok, pos, need_next=pos + 1 >= n_prompt)
+            nxt = self.step(tok, pos, need_next=pos + 1 >= n_prompt, batch=batch)
             if pos + 1 < n_prompt:
                 tok = prompts[:, pos + 1].copy()
             else:

@@ -59,6 +59,64 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
+def _model_worker(rank, world, port, out_dir):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path[:0] = [str(root), str(root / "tests")]
+    import __graft_entry__ as entry
+    entry.load_package()
+    import torch.distributed as dist
+    from gptoss_b200 import binfmt, model, synth
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    cfg = binfmt.config_7m()
+    batch, n_pos = 11, 24
+    ids = synth.uniform_ids(5, 6, batch * n_pos, cfg.vocab_size).reshape(n_pos, batch).astype(np.int32)
+    m = model.Model(cfg, device=rank, max_batch=batch, max_seq=32, rank=rank, world=world)
+    m.fill_synthetic(77)
+    handles = [None] * world
+    dist.all_gather_object(handles, m.comm_export())
+    m.comm_attach(handles)
+    first, n = m.slice(batch)
+    single = None
+    if rank == 0:
+        single = model.Model(cfg, device=0, max_batch=batch, max_seq=32)
+        single.fill_synthetic(77)
+    dist.barrier()
+    ok = True
+    for pos in range(n_pos):
+        got = m.step(ids[pos, first:first + n], pos, batch=batch)
+        want = torch.from_numpy(single.step(ids[pos], pos)) if rank == 0 else torch.empty(batch, dtype=torch.int32)
+        dist.broadcast(want, src=0)
+        ok = ok and bool(np.array_equal(got, want.numpy()[first:first + n]))
+    dist.barrier()
+    m.close()
+    if single:
+        single.close()
+    (Path(out_dir) / f"rank{rank}.txt").write_text("ok" if ok else "mismatch")
+    dist.destroy_process_group()
+
+
+def test_group_decode_across_processes_matches_single_gpu(tmp_path):
+    """Whole-model decode by a group of real GPUs (one process each, sequences in slices, experts sharded): every
+    rank's greedy tokens equal the single-GPU model's for its sequences, 24 positions in a row."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2 if n < 4 else 4
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_model_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
 def test_fused_combine_across_processes_matches_single_gpu(tmp_path):
     n = torch.cuda.device_count()
     if n < 2:
