@@ -145,8 +145,8 @@ __global__ void __launch_bounds__(256) add_delta_kernel(PeerTable pt, int T, int
 }
 
 // Token-sliced form, producer side.  Residual update + RMSNorm of the rows of this rank's slice (one block per row,
-// the arithmetic of the single-GPU residual_rmsnorm kernel: fp32 squares per thread, warp sums, double across
-// warps), each bf16 row stored into the gathered activation buffer of every rank; the last block raises flag C.
+// the same row routine as the single-GPU kernel, hence the same bits), each bf16 row stored into the gathered
+// activation buffer of every rank; the last block raises flag C.
 __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, int T, int H, float *__restrict__ x_slice,
                                                                 const float *__restrict__ add, const float *__restrict__ w,
                                                                 int step, int *counter) {
@@ -155,28 +155,15 @@ __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, in
   const int b0 = pt.rank * slice, n_rows = max(0, min(T, b0 + slice) - b0);
   const int i_row = blockIdx.x;
   if (i_row < n_rows) {
-    float *xr = x_slice + (size_t)i_row * H;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      float v = xr[i];
-      if (add) {
-        v += add[(size_t)i_row * H + i];
-        xr[i] = v;
-      }
-      ss += v * v;
-    }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)ss;
-    __syncthreads();
-    double tot = 0.0;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
-    const float inv = 1.0f / sqrtf((float)(tot / H + 1e-5));
     const size_t row = (size_t)(b0 + i_row) * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      const __nv_bfloat16 v = __float2bfloat16_rn(w[i] * (inv * xr[i]));
-      for (int r = 0; r < pt.world; ++r) reinterpret_cast<__nv_bfloat16 *>(pt.delta[r])[row + i] = v;
-    }
+    residual_rmsnorm_row(
+        x_slice + (size_t)i_row * H, add ? add + (size_t)i_row * H : nullptr, w, H, part,
+        [&](int i, uint2 v) {
+          for (int r = 0; r < pt.world; ++r) reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(pt.delta[r]) + row)[i] = v;
+        },
+        [&](int i, __nv_bfloat16 v) {
+          for (int r = 0; r < pt.world; ++r) reinterpret_cast<__nv_bfloat16 *>(pt.delta[r])[row + i] = v;
+        });
   }
   signal_all_ranks(pt, 2, step, counter);
 }

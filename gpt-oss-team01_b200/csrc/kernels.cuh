@@ -148,4 +148,61 @@ cudaError_t launch_synth_mlp1(__nv_bfloat16 *dst, int I, int K, uint64_t seed, u
 cudaError_t launch_synth_normal_f32(float *dst, uint64_t n, uint64_t seed, uint64_t tensor_id,
                                     uint64_t start, float sigma, cudaStream_t s);
 
+// ---- residual + RMSNorm of one row, shared by the single-GPU kernel and the peer-storing one ---------------------
+//   if (add) x[:] += add[:]            (projection output incl. its bias)
+//   store(i, w[i] * (x[i] * rsqrt(mean(x^2) + 1e-5)))   for every i, 4 consecutive elements at a time if H % 4 == 0
+// Called by every thread of a 256-thread block (part: 8 doubles of shared memory).  The sum of squares is accumulated
+// in fp32 per thread, added across the warp by shuffles and across warps in double, in this fixed order, so every
+// caller gets the same bits for the same row.
+template <class Store4, class Store1>
+__device__ __forceinline__ void residual_rmsnorm_row(float *__restrict__ xr, const float *__restrict__ addr,
+                                                     const float *__restrict__ w, int H, double *part, Store4 store4,
+                                                     Store1 store1) {
+  float ss = 0.f;
+  const bool vec = (H & 3) == 0;
+  if (vec) {
+    float4 *x4 = reinterpret_cast<float4 *>(xr);
+    const float4 *a4 = reinterpret_cast<const float4 *>(addr);
+    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+      float4 v = x4[i];
+      if (addr) {
+        const float4 a = a4[i];
+        v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+        x4[i] = v;
+      }
+      ss += v.x * v.x;
+      ss += v.y * v.y;
+      ss += v.z * v.z;
+      ss += v.w * v.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i];
+      if (addr) {
+        v += addr[i];
+        xr[i] = v;
+      }
+      ss += v * v;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)ss;
+  __syncthreads();
+  double tot = 0.0;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
+  const float inv = 1.0f / sqrtf((float)(tot / H + 1e-5));
+  if (vec) {
+    const float4 *x4 = reinterpret_cast<const float4 *>(xr), *w4 = reinterpret_cast<const float4 *>(w);
+    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+      const float4 v = x4[i], g = w4[i];
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(g.x * (inv * v.x), g.y * (inv * v.y));
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(g.z * (inv * v.z), g.w * (inv * v.w));
+      store4(i, make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi)));
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) store1(i, __float2bfloat16_rn(w[i] * (inv * xr[i])));
+  }
+}
+
 }  // namespace gptoss

@@ -35,32 +35,17 @@ __global__ void __launch_bounds__(256) embed_kernel(const int *__restrict__ toke
   for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_f32(row[i]);
 }
 
-// Optional residual update followed by RMSNorm (run.cpp:304-317, 611-623):
-//   if (add) x[b,:] += add[b,:]            (projection output incl. its bias)
-//   out[b,:] = bf16( w[:] * (x[b,:] * rsqrt(mean(x^2) + 1e-5)) )
-// One block per row; the sum of squares is accumulated in fp32 per thread and reduced in double.
+// Optional residual update followed by RMSNorm (run.cpp:304-317, 611-623), one block per row:
+//   if (add) x[b,:] += add[b,:];   out[b,:] = bf16( w[:] * (x[b,:] * rsqrt(mean(x^2) + 1e-5)) )
 __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ add,
                                                                const float *__restrict__ w, int H,
                                                                __nv_bfloat16 *__restrict__ out) {
   __shared__ double part[8];
-  const int b = blockIdx.x;
-  float *xr = x + (size_t)b * H;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = xr[i];
-    if (add) {
-      v += add[(size_t)b * H + i];
-      xr[i] = v;
-    }
-    ss += v * v;
-  }
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = (double)ss;
-  __syncthreads();
-  double tot = 0.0;
-  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += part[i];
-  const float inv = 1.0f / sqrtf((float)(tot / H + 1e-5));
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)b * H + i] = __float2bfloat16_rn(w[i] * (inv * xr[i]));
+  const size_t row = (size_t)blockIdx.x * H;
+  __nv_bfloat16 *o = out + row;
+  residual_rmsnorm_row(
+      x + row, add ? add + row : nullptr, w, H, part, [&](int i, uint2 v) { reinterpret_cast<uint2 *>(o)[i] = v; },
+      [&](int i, __nv_bfloat16 v) { o[i] = v; });
 }
 
 // qkv[b, :] = (q heads | k heads | v heads), bias already added (run.cpp:534-557).  Rotates q and k with the
@@ -72,28 +57,35 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
                                                              __nv_bfloat16 *__restrict__ k_cache,
                                                              __nv_bfloat16 *__restrict__ v_cache) {
   const int b = blockIdx.x;
-  const int half = hd >> 1;
+  const int half = hd >> 1, hp = half >> 1;  // hp: pairs of adjacent rotation indices per head (hd is 32 or 64)
   const int qdim = nq * hd, kvdim = nkv * hd;
   const float *row = qkv + (size_t)b * (qdim + 2 * kvdim);
-  const float *cs = cos_t + (size_t)pos * half, *sn = sin_t + (size_t)pos * half;
-  for (int i = threadIdx.x; i < (nq + nkv) * half; i += blockDim.x) {
-    const int h = i / half, j = i - h * half;  // heads 0..nq-1 are q, nq.. are k
+  const float2 *cs = reinterpret_cast<const float2 *>(cos_t + (size_t)pos * half);
+  const float2 *sn = reinterpret_cast<const float2 *>(sin_t + (size_t)pos * half);
+  for (int i = threadIdx.x; i < (nq + nkv) * hp; i += blockDim.x) {
+    const int h = i / hp, j = 2 * (i - h * hp);  // heads 0..nq-1 are q, nq.. are k; elements j, j+1 and their partners
     const float *src = row + (size_t)h * hd;
-    const float x1 = src[j], x2 = src[j + half], c = cs[j], s = sn[j];
-    const float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
+    const float2 x1 = *reinterpret_cast<const float2 *>(src + j), x2 = *reinterpret_cast<const float2 *>(src + j + half);
+    const float2 c = cs[j >> 1], s = sn[j >> 1];
+    const float2 o1 = make_float2(x1.x * c.x - x2.x * s.x, x1.y * c.y - x2.y * s.y);
+    const float2 o2 = make_float2(x2.x * c.x + x1.x * s.x, x2.y * c.y + x1.y * s.y);
     if (h < nq) {
-      q_out[(size_t)b * qdim + h * hd + j] = o1;
-      q_out[(size_t)b * qdim + h * hd + j + half] = o2;
+      float *dst = q_out + (size_t)b * qdim + h * hd + j;
+      *reinterpret_cast<float2 *>(dst) = o1;
+      *reinterpret_cast<float2 *>(dst + half) = o2;
     } else {
-      __nv_bfloat16 *dst = k_cache + (((size_t)b * nkv + (h - nq)) * S + pos) * hd;
-      dst[j] = __float2bfloat16_rn(o1);
-      dst[j + half] = __float2bfloat16_rn(o2);
+      __nv_bfloat16 *dst = k_cache + (((size_t)b * nkv + (h - nq)) * S + pos) * hd + j;
+      *reinterpret_cast<__nv_bfloat162 *>(dst) = __floats2bfloat162_rn(o1.x, o1.y);
+      *reinterpret_cast<__nv_bfloat162 *>(dst + half) = __floats2bfloat162_rn(o2.x, o2.y);
     }
   }
   const float *vsrc = row + qdim + kvdim;
-  for (int i = threadIdx.x; i < kvdim; i += blockDim.x) {
-    const int h = i / hd, j = i - h * hd;
-    v_cache[(((size_t)b * nkv + h) * S + pos) * hd + j] = __float2bfloat16_rn(vsrc[i]);
+  for (int i = threadIdx.x; i < (kvdim >> 2); i += blockDim.x) {
+    const int h = (4 * i) / hd, j = 4 * i - h * hd;
+    const float4 v = reinterpret_cast<const float4 *>(vsrc)[i];
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(v_cache + (((size_t)b * nkv + h) * S + pos) * hd + j) =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
   }
 }
 
@@ -140,8 +132,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   constexpr int D4 = HD / 4;   // K dims per thread
   constexpr int KS = HD / 16;  // k-steps of the score MMA
   constexpr int DV = HD / 8;   // V dims per thread = n-tiles of the output MMA
-  __shared__ float m_s[4][8], l_s[4][8];
-  __shared__ float acc_s[4][8][HD];
+  __shared__ float m_s[4][8], l_s[4][8], f_s[4][8];
+  __shared__ __align__(16) float acc_s[4][8][HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int grp = warp / PS, ps = warp % PS;
@@ -254,6 +246,32 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   }
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
+  if (PS == 1) {
+    // one warp per problem: nothing to merge.  Thread (g, c) holds head g, dims [2*DV*c, 2*DV*(c+1)) (accumulator
+    // columns 2c and 2c+1 of n-tile i are dims DV*2c + i and DV*(2c+1) + i); the sink joins the denominator only
+    if (active && g < kvm) {
+      const float sink = sinks[kvh * kvm + g];
+      const float mx = fmaxf(sink, m_run);
+      const float cw = __expf(m_run - mx);
+      const float inv = cw / (__expf(sink - mx) + l_part * cw);
+      uint32_t pk[DV];
+#pragma unroll
+      for (int i = 0; i < DV; i += 2) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn((o[i][0] + o[i][2]) * inv, (o[i + 1][0] + o[i + 1][2]) * inv);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn((o[i][1] + o[i][3]) * inv, (o[i + 1][1] + o[i + 1][3]) * inv);
+        pk[i >> 1] = *reinterpret_cast<const uint32_t *>(&lo);
+        pk[(DV >> 1) + (i >> 1)] = *reinterpret_cast<const uint32_t *>(&hi);
+      }
+      uint32_t *dst = reinterpret_cast<uint32_t *>(out + (size_t)b * nq * HD + (size_t)(kvh * kvm + g) * HD + 2 * DV * c);
+      if (DV == 8) {
+        reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[DV - 4], pk[DV - 3], pk[DV - 2], pk[DV - 1]);
+      } else {
+        reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+    }
+    return;
+  }
   if (c == 0) {
     m_s[warp][g] = m_run;
     l_s[warp][g] = l_part;
@@ -264,24 +282,43 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
     acc_s[warp][g][DV * (2 * c + 1) + i] = o[i][1] + o[i][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * kvm * HD; idx += blockDim.x) {
-    const int gr = idx / (kvm * HD), rem = idx - gr * (kvm * HD);
-    const int h = rem / HD, d = rem - h * HD;
+  // merge of the position groups: per (problem, head) the common maximum and denominator (with the sink), folded into
+  // one factor per position group; then every thread scales and adds 4 dims of one head
+  if (threadIdx.x < G * 8) {
+    const int gr = threadIdx.x >> 3, h = threadIdx.x & 7;
     const int pr = blockIdx.x * G + gr;
-    if (pr >= n_problems) break;
-    const int pb = pr / nkv, pk = pr % nkv;
-    const float sink = sinks[pk * kvm + h];
-    float mx = sink;
+    if (pr < n_problems && h < kvm) {
+      const float sink = sinks[(pr % nkv) * kvm + h];
+      float mx = sink;
 #pragma unroll
-    for (int w = 0; w < PS; ++w) mx = fmaxf(mx, m_s[gr * PS + w][h]);
-    float denom = __expf(sink - mx), num = 0.f;
+      for (int w = 0; w < PS; ++w) mx = fmaxf(mx, m_s[gr * PS + w][h]);
+      float denom = __expf(sink - mx);
+      float cw[PS];
+#pragma unroll
+      for (int w = 0; w < PS; ++w) {
+        cw[w] = __expf(m_s[gr * PS + w][h] - mx);
+        denom += l_s[gr * PS + w][h] * cw[w];
+      }
+#pragma unroll
+      for (int w = 0; w < PS; ++w) f_s[gr * PS + w][h] = cw[w] / denom;
+    }
+  }
+  __syncthreads();
+  constexpr int HD4 = HD / 4;
+  for (int idx = threadIdx.x; idx < G * 8 * HD4; idx += blockDim.x) {
+    const int gr = idx / (8 * HD4), h = (idx / HD4) & 7, d4 = idx % HD4;
+    const int pr = blockIdx.x * G + gr;
+    if (pr >= n_problems || h >= kvm) continue;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int w = 0; w < PS; ++w) {
-      const float cw = __expf(m_s[gr * PS + w][h] - mx);
-      denom += l_s[gr * PS + w][h] * cw;
-      num += acc_s[gr * PS + w][h][d] * cw;
+      const float f = f_s[gr * PS + w][h];
+      const float4 v = *reinterpret_cast<const float4 *>(&acc_s[gr * PS + w][h][4 * d4]);
+      num.x = fmaf(v.x, f, num.x), num.y = fmaf(v.y, f, num.y), num.z = fmaf(v.z, f, num.z), num.w = fmaf(v.w, f, num.w);
     }
-    out[(size_t)pb * nq * HD + (size_t)(pk * kvm + h) * HD + d] = __float2bfloat16_rn(num / denom);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(num.x, num.y), hi = __floats2bfloat162_rn(num.z, num.w);
+    *reinterpret_cast<uint2 *>(out + (size_t)(pr / nkv) * nq * HD + (size_t)((pr % nkv) * kvm + h) * HD + 4 * d4) =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
   }
 }
 
@@ -370,9 +407,11 @@ cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const
   const int kv_mul = nq / nkv;
   if (kv_mul < 1 || kv_mul > 8 || kv_mul * nkv != nq) return cudaErrorInvalidValue;  // query rows of one MMA tile
   const int n_chunks = (pos - t_lo) / 32 + 1, n_prob = B * nkv;
-  // one warp per problem while there are problems enough to fill the machine (or a single chunk each); otherwise
-  // the positions of a problem are split over 2 or 4 warps
-  const int g = (n_chunks == 1 || n_prob >= 4096) ? 4 : ((n_chunks <= 3 || n_prob >= 2048) ? 2 : 1);
+  // Warps per problem by the context length alone (1 up to 512 positions: a warp streams its problem's rows front
+  // to back with the loads one chunk ahead, which beats sharing them out; 2 up to 2048; else 4): the split fixes the
+  // order of the softmax accumulation, so it must not depend on the batch, or a sequence would get different
+  // low-order bits in a large batch, a small one, or a slice of one on another GPU.
+  const int g = n_chunks <= 16 ? 4 : (n_chunks <= 64 ? 2 : 1);
   const int grid = (n_prob + g - 1) / g;
 #define GPTOSS_ATT_CASE(HD, G)                                                                                             \
   if (hd == HD && g == G) {                                                                                                \
