@@ -75,6 +75,8 @@ __device__ __forceinline__ void signal_all_ranks(const PeerTable &pt, int which,
 // Raised by the down-GEMM launch when it pushes to owners: a one-block kernel right after it on the same
 // stream (kernel completion orders the GEMM's peer stores before these flag stores).
 __global__ void signal_pushed_kernel(PeerTable pt, int step) {
+  pdl_wait();  // the down GEMM before this kernel must have completed (its peer stores included)
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     __threadfence_system();
     for (int r = 0; r < pt.world; ++r) st_release_sys(pt.flags[r] + pt.rank, step);
@@ -96,6 +98,7 @@ __device__ __forceinline__ float4 unpack_bf16x4(const uint2 &u) {
 template <bool BF16>
 __global__ void __launch_bounds__(256) combine_owner_kernel(PeerTable pt, int T, int H, int k, int step,
                                                             int *status, int *counter) {
+  pdl_wait();
   wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2100);
   const int slice = (T + pt.world - 1) / pt.world;
   const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
@@ -123,12 +126,14 @@ __global__ void __launch_bounds__(256) combine_owner_kernel(PeerTable pt, int T,
       }
     }
   }
+  pdl_launch_dependents();
   signal_all_ranks(pt, 1, step, counter);
 }
 
 // Every rank: x += delta once all owners have delivered their slices.
 template <bool BF16>
 __global__ void __launch_bounds__(256) add_delta_kernel(PeerTable pt, int T, int H, int step, float *x, int *status) {
+  pdl_wait();
   wait_all_ranks(pt.flags[pt.rank] + kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2200);
   const size_t total = (size_t)T * (H >> 2);
   float4 *xp = reinterpret_cast<float4 *>(x);
@@ -142,6 +147,7 @@ __global__ void __launch_bounds__(256) add_delta_kernel(PeerTable pt, int T, int
     o.w += v.w;
     xp[i] = o;
   }
+  pdl_launch_dependents();
 }
 
 // Token-sliced form, producer side.  Residual update + RMSNorm of the rows of this rank's slice (one block per row,
@@ -151,6 +157,7 @@ __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, in
                                                                 const float *__restrict__ add, const float *__restrict__ w,
                                                                 int step, int *counter) {
   __shared__ double part[8];
+  pdl_wait();
   const int slice = (T + pt.world - 1) / pt.world;
   const int b0 = pt.rank * slice, n_rows = max(0, min(T, b0 + slice) - b0);
   const int i_row = blockIdx.x;
@@ -165,17 +172,21 @@ __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, in
           for (int r = 0; r < pt.world; ++r) reinterpret_cast<__nv_bfloat16 *>(pt.delta[r])[row + i] = v;
         });
   }
+  pdl_launch_dependents();
   signal_all_ranks(pt, 2, step, counter);
 }
 
 // Token-sliced form, consumer side: returns once every rank's slice of the gathered activations has arrived.
 __global__ void wait_gathered_kernel(PeerTable pt, int step, int *status) {
+  pdl_wait();
+  pdl_launch_dependents();
   wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2300);
 }
 
 // Token-sliced form, owner side: x_slice[i,:] += ((s0+s1)+s2)+s3 for the rows of this rank's slice, slots in order.
 __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, int T, int H, int k, int step,
                                                                   float *__restrict__ x_slice, int *status) {
+  pdl_wait();
   wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2400);
   const int slice = (T + pt.world - 1) / pt.world;
   const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
@@ -195,11 +206,11 @@ __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, 
     o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
     xp[i] = o;
   }
+  pdl_launch_dependents();
 }
 
 cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s) {
-  signal_pushed_kernel<<<1, 32, 0, s>>>(pt, step);
-  return cudaGetLastError();
+  return launch_chain(signal_pushed_kernel, dim3(1), dim3(32), 0, s, pt, step);
 }
 
 cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
@@ -209,11 +220,8 @@ cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 16) blocks = sm_count * 16;
   if (blocks < 1) blocks = 1;
-  if (bf16_wire)
-    combine_owner_kernel<true><<<blocks, 256, 0, s>>>(pt, T, H, k, step, status, counter);
-  else
-    combine_owner_kernel<false><<<blocks, 256, 0, s>>>(pt, T, H, k, step, status, counter);
-  return cudaGetLastError();
+  return launch_chain(bf16_wire ? combine_owner_kernel<true> : combine_owner_kernel<false>, dim3(blocks), dim3(256), 0, s, pt,
+                      T, H, k, step, status, counter);
 }
 
 cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, int step, float *x, int *status,
@@ -222,11 +230,8 @@ cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, 
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 16) blocks = sm_count * 16;
   if (blocks < 1) blocks = 1;
-  if (bf16_wire)
-    add_delta_kernel<true><<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
-  else
-    add_delta_kernel<false><<<blocks, 256, 0, s>>>(pt, T, H, step, x, status);
-  return cudaGetLastError();
+  return launch_chain(bf16_wire ? add_delta_kernel<true> : add_delta_kernel<false>, dim3(blocks), dim3(256), 0, s, pt, T, H,
+                      step, x, status);
 }
 
 cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x_slice, const float *add, const float *w,
@@ -234,13 +239,12 @@ cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x
   const int slice = (T + pt.world - 1) / pt.world;
   int rows = T - pt.rank * slice;
   rows = rows < 0 ? 0 : (rows > slice ? slice : rows);
-  slice_norm_gather_kernel<<<rows > 0 ? rows : 1, 256, 0, s>>>(pt, T, H, x_slice, add, w, step, counter);
-  return cudaGetLastError();
+  return launch_chain(slice_norm_gather_kernel, dim3(rows > 0 ? rows : 1), dim3(256), 0, s, pt, T, H, x_slice, add, w, step,
+                      counter);
 }
 
 cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s) {
-  wait_gathered_kernel<<<1, 32, 0, s>>>(pt, step, status);
-  return cudaGetLastError();
+  return launch_chain(wait_gathered_kernel, dim3(1), dim3(32), 0, s, pt, step, status);
 }
 
 cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
@@ -250,8 +254,7 @@ cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k,
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 16) blocks = sm_count * 16;
   if (blocks < 1) blocks = 1;
-  combine_owner_slice_kernel<<<blocks, 256, 0, s>>>(pt, T, H, k, step, x_slice, status);
-  return cudaGetLastError();
+  return launch_chain(combine_owner_slice_kernel, dim3(blocks), dim3(256), 0, s, pt, T, H, k, step, x_slice, status);
 }
 
 }  // namespace gptoss

@@ -29,10 +29,12 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as
 __global__ void __launch_bounds__(256) embed_kernel(const int *__restrict__ tokens, const __nv_bfloat16 *__restrict__ table,
                                                     int H, int vocab, float *__restrict__ x) {
   const int b = blockIdx.x;
+  pdl_wait();
   int tok = tokens[b];
   tok = min(max(tok, 0), vocab - 1);
   const uint16_t *row = reinterpret_cast<const uint16_t *>(table) + (size_t)tok * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) x[(size_t)b * H + i] = bf16_bits_to_f32(row[i]);
+  pdl_launch_dependents();  // at the end: the next kernel's blocks should not take room from this one's
 }
 
 // Optional residual update followed by RMSNorm (run.cpp:304-317, 611-623), one block per row:
@@ -41,11 +43,13 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(float *__restrict
                                                                const float *__restrict__ w, int H,
                                                                __nv_bfloat16 *__restrict__ out) {
   __shared__ double part[8];
+  pdl_wait();
   const size_t row = (size_t)blockIdx.x * H;
   __nv_bfloat16 *o = out + row;
   residual_rmsnorm_row(
       x + row, add ? add + row : nullptr, w, H, part, [&](int i, uint2 v) { reinterpret_cast<uint2 *>(o)[i] = v; },
       [&](int i, __nv_bfloat16 v) { o[i] = v; });
+  pdl_launch_dependents();
 }
 
 // qkv[b, :] = (q heads | k heads | v heads), bias already added (run.cpp:534-557).  Rotates q and k with the
@@ -56,6 +60,7 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
                                                              int hd, int S, float *__restrict__ q_out,
                                                              __nv_bfloat16 *__restrict__ k_cache,
                                                              __nv_bfloat16 *__restrict__ v_cache) {
+  pdl_wait();
   const int b = blockIdx.x;
   const int half = hd >> 1, hp = half >> 1;  // hp: pairs of adjacent rotation indices per head (hd is 32 or 64)
   const int qdim = nq * hd, kvdim = nkv * hd;
@@ -87,6 +92,7 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
     *reinterpret_cast<uint2 *>(v_cache + (((size_t)b * nkv + h) * S + pos) * hd + j) =
         make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
   }
+  pdl_launch_dependents();
 }
 
 // ---- single-query attention (run.cpp:565-607) -------------------------------------------------------------------
@@ -140,6 +146,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   const int prob = blockIdx.x * G + grp;
   const bool active = prob < n_problems;
   const int b = active ? prob / nkv : 0, kvh = active ? prob % nkv : 0;
+  pdl_wait();  // q and this position's K/V rows come from the kernel before
   uint32_t qh[KS][2], ql[KS][2];
 #pragma unroll
   for (int s = 0; s < KS; ++s) {
@@ -246,6 +253,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   }
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
+  pdl_launch_dependents();  // after the main loop: the next kernel's blocks should not take room from this one's
   if (PS == 1) {
     // one warp per problem: nothing to merge.  Thread (g, c) holds head g, dims [2*DV*c, 2*DV*(c+1)) (accumulator
     // columns 2c and 2c+1 of n-tile i are dims DV*2c + i and DV*(2c+1) + i); the sink joins the denominator only
@@ -327,6 +335,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
   __shared__ float bv[32];
   __shared__ int bi[32];
   const int b = blockIdx.x;
+  pdl_wait();
   const float *row = logits + (size_t)b * V;
   float best = -FLT_MAX;
   int idx = 0x7fffffff;
@@ -388,19 +397,17 @@ __global__ void iota_ones_kernel(int *__restrict__ iota, float *__restrict__ one
 }  // namespace
 
 cudaError_t launch_embed(const int *tokens, const __nv_bfloat16 *table, int B, int H, int vocab, float *x, cudaStream_t s) {
-  embed_kernel<<<B, 256, 0, s>>>(tokens, table, H, vocab, x);
-  return cudaGetLastError();
+  return launch_chain(embed_kernel, dim3(B), dim3(256), 0, s, tokens, table, H, vocab, x);
 }
 cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, int B, int H, __nv_bfloat16 *out,
                                     cudaStream_t s) {
-  residual_rmsnorm_kernel<<<B, 256, 0, s>>>(x, add, w, H, out);
-  return cudaGetLastError();
+  return launch_chain(residual_rmsnorm_kernel, dim3(B), dim3(256), 0, s, x, add, w, H, out);
 }
 cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
                                   int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
                                   cudaStream_t s) {
-  qkv_rope_store_kernel<<<B, 256, 0, s>>>(qkv, cos_t, sin_t, pos, nq, nkv, hd, S, q_out, k_cache, v_cache);
-  return cudaGetLastError();
+  return launch_chain(qkv_rope_store_kernel, dim3(B), dim3(256), 0, s, qkv, cos_t, sin_t, pos, nq, nkv, hd, S, q_out, k_cache,
+                      v_cache);
 }
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
                              int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s) {
@@ -415,8 +422,8 @@ cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const
   const int grid = (n_prob + g - 1) / g;
 #define GPTOSS_ATT_CASE(HD, G)                                                                                             \
   if (hd == HD && g == G) {                                                                                                \
-    attention_kernel<HD, G><<<grid, 128, 0, s>>>(q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv, kv_mul, S, n_prob, out);  \
-    return cudaGetLastError();                                                                                             \
+    return launch_chain(attention_kernel<HD, G>, dim3(grid), dim3(128), 0, s, q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv,   \
+                        kv_mul, S, n_prob, out);                                                                           \
   }
   GPTOSS_ATT_CASE(64, 4)
   GPTOSS_ATT_CASE(64, 2)
@@ -428,8 +435,7 @@ cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const
   return cudaErrorInvalidValue;  // head_dim must be 32 or 64
 }
 cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s) {
-  argmax_kernel<<<B, 1024, 0, s>>>(logits, V, next);
-  return cudaGetLastError();
+  return launch_chain(argmax_kernel, dim3(B), dim3(1024), 0, s, logits, V, next);
 }
 cudaError_t launch_iota_ones(int *iota, float *ones, int n, cudaStream_t s) {
   iota_ones_kernel<<<(n + 255) / 256, 256, 0, s>>>(iota, ones, n);
