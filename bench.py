@@ -247,20 +247,32 @@ def run_ours(args):
         ms = float(tms.item())
     value = T * K / (ms * 1e-3)
 
-    nccl_ms = stub_ms = None
-    if world > 1:  # the same kernels with the exchange stubbed: per-rank partial only (no push, no delivery, no add)
-        for i in range(3):
-            blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for i in range(K):
-            blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
-        s1.record()
-        barrier()
-        ts = torch.tensor([s0.elapsed_time(s1)], device="cuda")
-        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
-        stub_ms = float(ts.item()) / K
+    nccl_ms = stub_ms = stub_free_ms = None
+    if world > 1:
+        # The same kernels with the exchange stubbed: every rank computes the partial of its own experts (no push,
+        # no delivery, no add).  Timed twice: with a device-side rendezvous of the ranks after every step (what the
+        # expert-parallel step costs without moving any data: the ranks still wait for the most loaded one every
+        # step) and free-running (each rank at its own pace; the gap between the two is load imbalance, not exchange).
+        def timed_stub(sync):
+            for i in range(3):
+                blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
+                if sync:
+                    blk.rendezvous()
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for i in range(K):
+                blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
+                if sync:
+                    blk.rendezvous()
+            s1.record()
+            barrier()
+            ts = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+            return float(ts.item()) / K
+        stub_ms = timed_stub(True)
+        stub_free_ms = timed_stub(False)
+        blk.status()
     if world > 1:  # the NCCL baseline on the same steps
         for i in range(3):
             step_nccl(i)
@@ -333,7 +345,7 @@ def run_ours(args):
         "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
                            "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
                            "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
-        "stage_ms": stage_ms, "gpu_launches": (7 if world == 1 else 10) * K,  # router GEMM, top-k, scan, scatter, 2 GEMMs, combine (+ signal, owner, add)
+        "stage_ms": stage_ms, "gpu_launches": (7 if world == 1 else 8) * K,  # router GEMM, top-k, scan, scatter, 2 GEMMs, combine (N > 1: owner combine + add instead)
     }
     if world > 1:
         comm_ms = ms / K - stub_ms  # exposed exchange = step with the fused combine - step with the exchange stubbed
@@ -341,6 +353,7 @@ def run_ours(args):
                                    f"order + peer delivery of the sums ({args.wire})",
                            "exposed_ms": comm_ms, "share_of_step": comm_ms / (ms / K),
                            "stubbed_exchange_ms_per_step": stub_ms,
+                           "stubbed_exchange_without_rendezvous_ms_per_step": stub_free_ms,
                            "nccl_allreduce_baseline_ms_per_step": nccl_ms}
 
     if rank == 0:

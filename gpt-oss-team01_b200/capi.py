@@ -41,7 +41,7 @@ EXPORTS = [
     "gptoss_model_read_logits", "gptoss_moe_slice_bounds", "gptoss_moe_gather_slice", "gptoss_moe_sliced_push",
     "gptoss_moe_sliced_combine", "gptoss_moe_forward_sliced", "gptoss_model_create_ep", "gptoss_model_moe_ctx",
     "gptoss_model_slice", "gptoss_model_step_begin", "gptoss_model_layer_attention", "gptoss_model_layer_moe_push",
-    "gptoss_model_layer_moe_combine", "gptoss_model_step_end",
+    "gptoss_model_layer_moe_combine", "gptoss_model_step_end", "gptoss_comm_rendezvous",
 ]
 
 
@@ -145,6 +145,7 @@ def load() -> C.CDLL:
         "gptoss_model_layer_moe_push": ([vp, i32], i32),
         "gptoss_model_layer_moe_combine": ([vp, i32], i32),
         "gptoss_model_step_end": ([vp, vp], i32),
+        "gptoss_comm_rendezvous": ([ctxp, vp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -487,9 +487,13 @@ int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) {
   GemmArgs a = gemm_args(ctx, ctx->layers[layer], false);
   a.n_owners = ctx->world;
   a.slice_tokens = (ctx->cur_T + ctx->world - 1) / ctx->world;
-  for (int r = 0; r < ctx->world; ++r) a.y_owner[r] = ctx->peers.y[r];
+  for (int r = 0; r < ctx->world; ++r) {
+    a.y_owner[r] = ctx->peers.y[r];
+    a.signal_flags[r] = ctx->peers.flags[r] + ctx->rank;  // flag A of this rank on rank r
+  }
+  a.signal_step = step;
+  a.signal_counter = ctx->comm_counter;
   CK(launch_grouped_mlp2(a, ctx->sm_count, s));
-  CK(launch_signal_pushed(ctx->peers, step, s));
   return GPTOSS_OK;
 }
 
@@ -537,6 +541,14 @@ int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const fl
   const int step = ++ctx->gather_step;
   CK(launch_slice_norm_gather(ctx->peers, T, ctx->d.H, x_slice_dev, add_dev, norm_w_dev, step, ctx->comm_counter,
                               static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_comm_rendezvous(gptoss_ctx *ctx, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  CK(cudaSetDevice(ctx->device));
+  CK(launch_rendezvous(ctx->peers, ++ctx->gather_step, ctx->status, static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }
 

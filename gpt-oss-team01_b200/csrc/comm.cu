@@ -14,6 +14,7 @@
 // rank (flag C), all ranks route the full batch and push to the owners as above, and the owner adds the slot-ordered
 // sum to its own residual slice: no delivery step, half the NVLink traffic of the replicated form.
 //
+// A rank's "pushed" flag is raised by its down GEMM itself: the last CTA to finish stores it on every rank.
 // Flags carry the step number (monotonic), so nothing is ever reset.  All waits are bounded by wall time;
 // a wait that gives up records a time-out in the status words and the kernel carries on without waiting.
 #include "kernels.cuh"
@@ -27,15 +28,6 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ int ld_acquire_sys(const int *p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(int *p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 // Threads 0..world-1 of the block each wait until flags[r] >= step; then the block synchronises.
 __device__ __forceinline__ void wait_all_ranks(const int *flags, int world, int step, unsigned long long limit_ns,
                                                int *status, int site) {
@@ -56,32 +48,24 @@ __device__ __forceinline__ void wait_all_ranks(const int *flags, int world, int 
   __syncthreads();
 }
 
-// Last block of the grid (all blocks fence + count) raises flag `which` (0 = A, 1 = B) on every rank.
+// The last block of the grid to get here raises flag `which` (0 = A, 1 = B, 2 = C) of this rank on every rank.  The
+// block's stores are ordered before its count by the barrier plus ONE thread's system-scope fence (the fence is
+// cumulative over what the barrier made visible to that thread); a fence by every thread would make each of them
+// wait out the round trip of the block's peer stores.
 __device__ __forceinline__ void signal_all_ranks(const PeerTable &pt, int which, int step, int *counter) {
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int *>(counter), 1u);
     if (prev == gridDim.x * gridDim.y - 1) {
       *counter = 0;
       __threadfence_system();
-      for (int r = 0; r < pt.world; ++r) st_release_sys(pt.flags[r] + which * kMaxRanks + pt.rank, step);
+      for (int r = 0; r < pt.world; ++r) st_relaxed_sys(pt.flags[r] + which * kMaxRanks + pt.rank, step);
     }
   }
 }
 
 }  // namespace
-
-// Raised by the down-GEMM launch when it pushes to owners: a one-block kernel right after it on the same
-// stream (kernel completion orders the GEMM's peer stores before these flag stores).
-__global__ void signal_pushed_kernel(PeerTable pt, int step) {
-  pdl_wait();  // the down GEMM before this kernel must have completed (its peer stores included)
-  pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    for (int r = 0; r < pt.world; ++r) st_release_sys(pt.flags[r] + pt.rank, step);
-  }
-}
 
 __device__ __forceinline__ uint2 pack_bf16x4(const float4 &v) {
   const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
@@ -183,6 +167,18 @@ __global__ void wait_gathered_kernel(PeerTable pt, int step, int *status) {
   wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2300);
 }
 
+// Device-side rendezvous of the ranks (no data): raises this rank's flag C everywhere, then waits for everyone's.
+__global__ void rendezvous_kernel(PeerTable pt, int step, int *status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < pt.world; ++r) st_relaxed_sys(pt.flags[r] + 2 * kMaxRanks + pt.rank, step);
+  }
+  __syncthreads();
+  wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2500);
+}
+
 // Token-sliced form, owner side: x_slice[i,:] += ((s0+s1)+s2)+s3 for the rows of this rank's slice, slots in order.
 __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, int T, int H, int k, int step,
                                                                   float *__restrict__ x_slice, int *status) {
@@ -209,16 +205,12 @@ __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, 
   pdl_launch_dependents();
 }
 
-cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s) {
-  return launch_chain(signal_pushed_kernel, dim3(1), dim3(32), 0, s, pt, step);
-}
-
 cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
                                  int *counter, int sm_count, cudaStream_t s) {
   const int slice = (T + pt.world - 1) / pt.world;
   const size_t total = (size_t)slice * (H >> 3);
   int blocks = (int)((total + 255) / 256);
-  if (blocks > sm_count * 16) blocks = sm_count * 16;
+  if (blocks > sm_count * 4) blocks = sm_count * 4;  // few, long-lived blocks: each ends with a system-scope fence
   if (blocks < 1) blocks = 1;
   return launch_chain(bf16_wire ? combine_owner_kernel<true> : combine_owner_kernel<false>, dim3(blocks), dim3(256), 0, s, pt,
                       T, H, k, step, status, counter);
@@ -245,6 +237,10 @@ cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x
 
 cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s) {
   return launch_chain(wait_gathered_kernel, dim3(1), dim3(32), 0, s, pt, step, status);
+}
+
+cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaStream_t s) {
+  return launch_chain(rendezvous_kernel, dim3(1), dim3(32), 0, s, pt, step, status);
 }
 
 cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,

@@ -51,4 +51,16 @@ struct Dims {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Flags that another GPU (or this one) polls: acquire load, and a relaxed system-scope store that is meant to follow
+// ONE __threadfence_system() covering every flag of a batch (fence once, then store the flags back to back: a
+// release store per flag would pay the round trip to each peer in turn).
+__device__ __forceinline__ int ld_acquire_sys(const int *p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 }  // namespace gptoss

@@ -327,6 +327,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if constexpr (NA == 1) {
+    // pushing to owners: every row this CTA stored (possibly into a peer's memory) is ordered before the count by
+    // the barrier above plus this thread's system-scope fence; the last CTA to finish raises this rank's "pushed"
+    // flag on every rank
+    if (a.signal_step > 0 && threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int *>(a.signal_counter), 1u);
+      if (prev == gridDim.x - 1) {
+        *a.signal_counter = 0;
+        __threadfence_system();
+        for (int r = 0; r < a.n_owners; ++r) st_relaxed_sys(a.signal_flags[r], a.signal_step);
+      }
+    }
+  }
 }
 
 template <int NA>

@@ -58,7 +58,6 @@ struct PeerTable {
   int *flags[kMaxRanks];    // every rank's flags    [3][kMaxRanks]: A = "rank r pushed", B = "owner r delivered",
                             //                       C = "rank r stored its slice of the gathered activations"
 };
-cudaError_t launch_signal_pushed(const PeerTable &pt, int step, cudaStream_t s);
 cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
                                  int *counter, int sm_count, cudaStream_t s);
 cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, int step, float *x, int *status,
@@ -67,6 +66,7 @@ cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, 
 cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x_slice, const float *add, const float *w,
                                      int step, int *counter, cudaStream_t s);
 cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s);
+cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaStream_t s);
 cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
                                        int sm_count, cudaStream_t s);
 
@@ -106,6 +106,9 @@ struct GemmArgs {
   float *y_owner[kMaxRanks];  // mlp2 with n_owners > 1: y_pairs of the rank that owns the token slice
   int n_owners;            // 1 = store locally; > 1 = push each row to its owner
   int slice_tokens;        // tokens per owner slice
+  int *signal_flags[kMaxRanks];  // mlp2 pushing to owners: this rank's "pushed" flag on every rank, raised to
+  int signal_step;               // signal_step by the last CTA to finish (0 = no signalling)
+  int *signal_counter;           // CTAs finished so far (left at 0)
   int top_k;
   const int *sorted;       // mlp2: [P]
   const float *topk_w;     // mlp2: [P] by pair id

@@ -11,9 +11,15 @@
 // cut into batches, each batch decodes in lock-step from position 0, prompt tokens are force-fed one per
 // step, the first generated token lands at index 0 of the request's output row, a sequence stops at the
 // end-of-sequence ids 199999 / 200002, and each output row is terminated by -1 after generated_len + 1 ids.
-// Batches are spread over the visible GPUs as data-parallel replicas, one host thread and one model per GPU
-// (DP_20B, getp-csrc/include/config.hpp:16-19).  Batch size: environment GPTOSS_BATCH (default 1024).
+// Batches are spread over the GPUs (GPTOSS_GPUS, default 1) as data-parallel replicas, one host thread and one
+// model per GPU (DP_20B, getp-csrc/include/config.hpp:16-19).  With GPTOSS_EP=1 the GPUs instead decode every
+// batch together, like the reference's 120B engine (forward_gpu_120b_batched, getp-csrc/src/model.cpp:153-489; one
+// host thread per GPU meeting at a pthread barrier, getp-csrc/getp_run.cpp): the experts are sharded over the GPUs,
+// the sequences of a batch are dealt out in slices, and the ranks exchange activations over peer memory on the
+// device.  Batch size: environment GPTOSS_BATCH (default 1024; with GPTOSS_EP the batch of the whole group).
 #include "getp_eval.cpp"
+
+#include <pthread.h>
 
 #include <algorithm>
 #include <atomic>
@@ -32,6 +38,7 @@ namespace {
 std::vector<gptoss_model *> g_models;  // one per GPU
 int g_batch = 1024;
 int g_max_seq = 0;
+bool g_group = false;  // GPTOSS_EP: the models are the ranks of one group
 
 void die(const char *what, gptoss_model *m) {
   fprintf(stderr, "gptoss_b200: %s: %s\n", what, m ? gptoss_model_last_error(m) : "");
@@ -45,10 +52,35 @@ gptoss_model_config to_config(const Config &c) {
   return g;
 }
 
-// One batch of requests [first, first + n) on one model, in lock-step.  Returns the token count the
-// reference reports (generated_len + 1 per request).
-long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg, Requests *reqs, int first, int n) {
+// What the ranks of a group agree on after every step: how many sequences are still running anywhere.
+struct GroupSync {
+  pthread_barrier_t bar;
+  std::vector<int> active;  // per rank
+  explicit GroupSync(int ranks) : active(ranks, 0) { pthread_barrier_init(&bar, nullptr, ranks); }
+  ~GroupSync() { pthread_barrier_destroy(&bar); }
+  int total_active(int rank, int mine) {
+    active[rank] = mine;
+    pthread_barrier_wait(&bar);
+    int t = 0;
+    for (int a : active) t += a;
+    pthread_barrier_wait(&bar);  // nobody overwrites its entry before everyone has read it
+    return t;
+  }
+};
+
+// One batch of requests [first, first + n) in lock-step.  Returns the token count the reference reports
+// (generated_len + 1 per request).  A single model decodes the whole batch; a rank of a group (sync != nullptr) its
+// slice of it, and keeps stepping, for the other ranks' sake, until no sequence of the batch is running anywhere.
+long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg, Requests *reqs, int first, int n,
+                    GroupSync *sync = nullptr, int rank = 0) {
   const int max_seq_len = reqs->max_seq_len;
+  const int batch = n;  // the batch of the whole group
+  if (sync) {
+    int s_first = 0, s_n = 0;
+    gptoss_model_slice(model, batch, &s_first, &s_n);
+    first += s_first;
+    n = s_n;
+  }
   std::vector<std::vector<int>> prompt(n);
   for (int i = 0; i < n; ++i) {
     const char *text = get_str_req_ptr(reqs, first + i);
@@ -65,10 +97,11 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
   std::vector<char> active(n, 1);
   int n_active = n;
   for (int i = 0; i < n; ++i) cur[i] = prompt[i][0];
-  for (int pos = 0; pos < max_seq_len - 1 && n_active > 0; ++pos) {
+  int running = sync ? sync->total_active(rank, n_active) : n_active;
+  for (int pos = 0; pos < max_seq_len - 1 && running > 0; ++pos) {
     bool need_next = false;  // does any running sequence take the model's token this step?
     for (int i = 0; i < n && !need_next; ++i) need_next = active[i] && pos_of[i] >= (int)prompt[i].size() - 1;
-    if (gptoss_model_step(model, cur.data(), pos, n, need_next ? next.data() : nullptr)) die("decode step failed", model);
+    if (gptoss_model_step(model, cur.data(), pos, batch, need_next ? next.data() : nullptr)) die("decode step failed", model);
     for (int i = 0; i < n; ++i) {
       if (!active[i]) continue;
       int tok = next[i];
@@ -84,6 +117,7 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
       cur[i] = tok;
       ++pos_of[i];
     }
+    running = sync ? sync->total_active(rank, n_active) : n_active;
   }
   long long count = 0;
   for (int i = 0; i < n; ++i) {
@@ -101,16 +135,25 @@ void warm_up(Transformer *transformer, Tokenizer *tokenizer) {
   if (const char *b = getenv("GPTOSS_BATCH")) g_batch = std::max(1, atoi(b));
   int n_gpus = 1;
   if (const char *g = getenv("GPTOSS_GPUS")) n_gpus = std::max(1, atoi(g));
+  if (const char *e = getenv("GPTOSS_EP")) g_group = atoi(e) != 0 && n_gpus > 1;
   const Config &c = transformer->config;
   g_max_seq = c.seq_len;
   if (const char *s = getenv("GPTOSS_MAX_SEQ")) g_max_seq = std::min(c.seq_len, std::max(2, atoi(s)));
   const gptoss_model_config gc = to_config(c);
   for (int g = 0; g < n_gpus; ++g) {
     gptoss_model *m = nullptr;
-    if (gptoss_model_create(&gc, g, g_batch, g_max_seq, &m)) die("cannot create the model (GPU count, memory, dimensions)", nullptr);
+    const int rc = g_group ? gptoss_model_create_ep(&gc, g, g, n_gpus, g_batch, g_max_seq, &m)
+                           : gptoss_model_create(&gc, g, g_batch, g_max_seq, &m);
+    if (rc) die("cannot create the model (GPU count, memory, dimensions, experts not divisible by the GPUs)", nullptr);
     // the reference keeps the whole file mapped: header first, then the tensors (run.cpp:274-280)
     if (gptoss_model_load_mem(m, transformer->data, (uint64_t)transformer->file_size)) die("cannot load the checkpoint", m);
     g_models.push_back(m);
+  }
+  if (g_group) {  // every rank maps every rank's exchange buffers
+    std::vector<gptoss_ctx *> ctxs;
+    for (gptoss_model *m : g_models) ctxs.push_back(gptoss_model_moe_ctx(m));
+    for (gptoss_model *m : g_models)
+      if (gptoss_comm_attach_local(gptoss_model_moe_ctx(m), ctxs.data())) die("cannot attach the GPUs to one another", m);
   }
 }
 
@@ -126,6 +169,18 @@ long long inference(Transformer *transformer, Tokenizer *tokenizer, Sampler *sam
   std::atomic<int> next_batch{0};
   std::atomic<long long> total{0};
   std::vector<std::thread> workers;
+  if (g_group) {  // one thread per rank; every batch is decoded by all of them together
+    GroupSync sync((int)g_models.size());
+    for (int r = 0; r < (int)g_models.size(); ++r)
+      workers.emplace_back([&, r] {
+        for (int b = 0; b < n_batches; ++b) {
+          const int first = b * g_batch, n = std::min(g_batch, requests->num_reqs - first);
+          total += run_batch(g_models[r], tokenizer, cfg, requests, first, n, &sync, r);
+        }
+      });
+    for (auto &w : workers) w.join();
+    return total;
+  }
   for (gptoss_model *model : g_models)
     workers.emplace_back([&, model] {
       for (int b = next_batch++; b < n_batches; b = next_batch++) {

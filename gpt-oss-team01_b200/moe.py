@@ -129,6 +129,10 @@ class MoEBlock:
         for b in blocks:
             b._check(b.lib.gptoss_comm_attach_local(b._ctx, arr))
 
+    def rendezvous(self, stream=None):
+        """Device-side meeting point of the ranks on the stream (no data)."""
+        self._check(self.lib.gptoss_comm_rendezvous(self._ctx, _stream(stream)))
+
     def set_peer_timeout_ms(self, ms):
         self._check(self.lib.gptoss_comm_set_timeout_ms(self._ctx, ms))
 

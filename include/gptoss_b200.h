@@ -154,6 +154,11 @@ int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream);
  * x_slice_dev, add_dev: fp32 [slice count, H] on the device; norm_w_dev: fp32 [H].  Every rank must make the
  * same sequence of these calls; they must not be interleaved with the replicated form within one step. */
 int gptoss_moe_slice_bounds(const gptoss_ctx *ctx, int T, int *first, int *count);
+/* Device-side rendezvous of the ranks on `stream`, no data: kernels queued after it start only once every rank
+ * has reached its own call (bounded wait; a rank that never arrives shows as GPTOSS_ERR_TIMEOUT in gptoss_ctx_status).
+ * Every rank must call it the same number of times; it shares its counter with gather_slice.  Measurement aid: a
+ * step of per-rank work followed by a rendezvous costs what the expert-parallel step costs without its data exchange. */
+int gptoss_comm_rendezvous(gptoss_ctx *ctx, void *stream);
 int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const float *add_dev, const float *norm_w_dev,
                             void *stream);
 int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream);

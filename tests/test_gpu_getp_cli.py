@@ -65,3 +65,30 @@ def test_getp_mode_writes_the_tokens_of_the_stepwise_decode(tmp_path):
             want.append(outs[i][:gen_len + 1])
     m.close()
     assert got == want
+
+
+@pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")
+def test_getp_mode_group_of_gpus_writes_the_same_tokens(tmp_path):
+    """GPTOSS_EP=1: the GPUs decode every batch together (experts sharded, sequences in slices, one host thread per
+    GPU); the written ids must equal those of the single-GPU run of the same command."""
+    n_gpus = torch.cuda.device_count()
+    if n_gpus < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2 if n_gpus < 4 else 4
+    cfg = binfmt.config_7m()
+    ckpt, tok, inp = (tmp_path / n for n in ("m.bin", "tokenizer.bin", "in.txt"))
+    binfmt.write_synthetic(str(ckpt), cfg, 4242)
+    binfmt.write_synthetic_tokenizer(str(tok), cfg.vocab_size)
+    prompts = ["hello world", "a", "The quick brown fox", "B200", "mixture of experts", "peer memory", "x y z"]
+    inp.write_text(f"{len(prompts)}\n" + "\n".join(prompts) + "\n")
+    steps = 40
+    outs = []
+    for env in ({"GPTOSS_GPUS": "1"}, {"GPTOSS_GPUS": str(world), "GPTOSS_EP": "1"}):
+        out = tmp_path / f"out{len(outs)}.txt"
+        r = subprocess.run([str(EXE), str(ckpt), "-z", str(tok), "-m", "getp", "-i", str(inp), "-o", str(out), "-n", str(steps)],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
+                           env={"GPTOSS_BATCH": "5", "GPTOSS_MAX_SEQ": str(steps), "PATH": "/usr/bin:/bin",
+                                "NCCL_NVLS_ENABLE": "0", **env})
+        assert r.returncode == 0, r.stdout[-2000:]
+        outs.append(out.read_text())
+    assert outs[0] == outs[1] and len(outs[0].splitlines()) == len(prompts)
