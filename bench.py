@@ -58,36 +58,51 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs.  nvidia-smi needs up to a
+    second before its first line on a box with many GPUs, so the sampler may be started ahead of the region
+    (``start()``, e.g. before the warm-up steps); only the lines read between ``with`` entry and exit count, plus the
+    last one before and the first one after when the region is shorter than the sampling period."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.all_rows, self.rows, self.proc = index, [], [], None
+        self.t_in = self.t_out = None
+
+    def start(self):
+        if self.proc is None:
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits", "-lms", "20"],
+                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._read, daemon=True)
+                self.thread.start()
+            except OSError:
+                self.proc = None
+        return self
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "20"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        self.start()
+        self.t_in = time.monotonic()
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.all_rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *a):
+        self.t_out = time.monotonic()
         if self.proc:
             time.sleep(0.15)
             self.proc.terminate()
             self.thread.join(timeout=2)
+        inside = [r for t, r in self.all_rows if self.t_in <= t <= self.t_out]
+        before = [r for t, r in self.all_rows if t < self.t_in][-1:]
+        after = [r for t, r in self.all_rows if t > self.t_out][:1]
+        self.rows = inside if len(inside) >= 3 else before + inside + after
 
     def summary(self):
         sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
@@ -227,12 +242,13 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    clocks = ClockSampler(local_rank).start()
     for i in range(W):
         step(i)
     barrier()
     blk.status()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    with clocks:
         barrier()
         ev0.record()
         for i in range(K):
@@ -437,7 +453,7 @@ def run_decode(args):
         import torch.distributed as dist
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    m = model.Model(cfg, device=local_rank, max_batch=B, max_seq=n_prompt + n_gen, rank=rank, world=world)
+    m = model.Model(cfg, device=local_rank, max_batch=B, max_seq=args.decode_first_pos + n_prompt + n_gen, rank=rank, world=world)
     m.fill_synthetic(SEED, SIGMA)
     if world > 1:
         m.attach_peers()
@@ -448,7 +464,7 @@ def run_decode(args):
         dist.barrier()
     with ClockSampler(local_rank) as clocks:
         t0 = time.perf_counter()
-        out = m.generate(prompts, n_gen, batch=B)
+        out = m.generate(prompts, n_gen, batch=B, first_pos=args.decode_first_pos)
         dt = time.perf_counter() - t0
     n_distinct = int(len(np.unique(out)))
     if world > 1:
@@ -498,6 +514,8 @@ def main():
     ap.add_argument("--decode-prompt", type=int, default=0, help="0 = the config's prompt length (128 / 256)")
     ap.add_argument("--decode-gen", type=int, default=0, help="0 = 256")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count (0 = 24)")
+    ap.add_argument("--decode-first-pos", type=int, default=0,
+                    help="profiling runs: start the timed decode at this position (cache rows before it are zeros)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
                     help="distinct layers of weights the steps rotate over (1 keeps a profiling run small)")

@@ -132,19 +132,20 @@ class Model:
         self._check(self.lib.gptoss_model_read_logits(self._m, row, out.ctypes.data_as(C.c_void_p)))
         return out
 
-    def generate(self, prompts, n_generate, stop_on_eos=False, batch=None):
+    def generate(self, prompts, n_generate, stop_on_eos=False, batch=None, first_pos=0):
         """prompts: int32 [B, n_prompt] (same length).  Returns int32 [B, n_generate]: the greedy continuation,
         prompt tokens force-fed one position per step; a sequence that emits an end-of-sequence id keeps
         running in lock-step (its later tokens are ignored by the caller) unless stop_on_eos trims them to -1.
         In a group, ``prompts`` holds this rank's sequences and ``batch`` is the batch of the whole group; every
-        rank must call generate with the same prompt length and n_generate."""
+        rank must call generate with the same prompt length and n_generate.  ``first_pos`` shifts the positions (the
+        cache rows before it keep whatever they held: for timing a step at a long context without decoding up to it)."""
         prompts = np.ascontiguousarray(prompts, dtype=np.int32)
         B, n_prompt = prompts.shape
         out = np.full((B, n_generate), -1, np.int32)
         done = np.zeros(B, bool)
         tok = prompts[:, 0].copy()
         for pos in range(n_prompt + n_generate - 1):
-            nxt = self.step(tok, pos, need_next=pos + 1 >= n_prompt, batch=batch)
+            nxt = self.step(tok, first_pos + pos, need_next=pos + 1 >= n_prompt, batch=batch)
             if pos + 1 < n_prompt:
                 tok = prompts[:, pos + 1].copy()
             else:
