@@ -34,6 +34,15 @@ def _ptr(t):
     raise TypeError(type(t))
 
 
+def slice_bounds(rank: int, world: int, n_tokens: int):
+    """(first token, token count) of the slice rank ``rank`` owns in a batch of ``n_tokens``: contiguous slices of
+    ceil(n_tokens / world) tokens, the last ones shorter or empty (same rule as gptoss_moe_slice_bounds)."""
+    per = (n_tokens + world - 1) // world
+    first = rank * per
+    count = max(0, min(per, n_tokens - first))
+    return (first if count else n_tokens), count
+
+
 def _stream(stream):
     if stream is None:
         stream = torch.cuda.current_stream()
