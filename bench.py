@@ -222,6 +222,8 @@ def run_ours(args):
                        wire={"f32": 0, "bf16": 1}[args.wire])
     for layer in range(N_WEIGHT_SETS):
         blk.fill_layer_synthetic(layer, SEED, SIGMA)
+        if args.zipf > 0:  # skewed routing (BASELINE config 3): router_bias[e] += -s * ln(e + 1), hottest expert first
+            blk.set_router_bias(layer, synth.zipf_router_bias(SEED, layer, E, args.zipf))
     t_dev = moe.synth_normal_bf16(T * H, SEED, synth.tensor_id(synth.TID_ACTIVATION), 1.0).view(T, H)
     x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
     partial = torch.empty_like(x) if world > 1 else None
@@ -357,7 +359,9 @@ def run_ours(args):
         "metric": "batched decode tok/s, gpt-oss-20b MoE FFN block (one layer call per step)",
         "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
-        "data": "synthetic", "config": workload_config(world, T), "roofline": roof,
+        "data": "synthetic", "config": dict(workload_config(world, T), **({"router_skew": f"Zipf s={args.zipf} over expert id "
+                                                                              "(router_bias[e] -= s*ln(e+1))"} if args.zipf > 0 else {})),
+        "roofline": roof,
         "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
                            "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
                            "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
@@ -517,6 +521,8 @@ def main():
     ap.add_argument("--decode-first-pos", type=int, default=0,
                     help="profiling runs: start the timed decode at this position (cache rows before it are zeros)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--zipf", type=float, default=0.0,
+                    help="skew the routing: router_bias[e] -= s*ln(e+1) (1.2 = BASELINE config 3); 0 = uniform")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
                     help="distinct layers of weights the steps rotate over (1 keeps a profiling run small)")
     args = ap.parse_args()

@@ -71,6 +71,29 @@ class MoeLayerOps {
                          void *stream) {
     check(gptoss_moe_build_offsets(ctx_, cur_batch_size, topk_i, expert_offsets, sorted_pair_ids, stream));
   }
+  // ---- peers (one MoeLayerOps per GPU thread of the same process, rank order) -----------------------------------
+  // replaces the hipDeviceEnablePeerAccess setup of the reference's ring (getp-csrc/src/parallelism.cpp)
+  static void attach_local(MoeLayerOps *const *ranks, int world) {
+    gptoss_ctx *ctxs[16] = {};
+    for (int r = 0; r < world && r < 16; ++r) ctxs[r] = ranks[r]->ctx_;
+    for (int r = 0; r < world; ++r) ranks[r]->check(gptoss_comm_attach_local(ranks[r]->ctx_, ctxs));
+  }
+  // ring_reduce_agg_quantize_fp8 + add_vector_batched, fused with moe_mlp2_forward_hip + moe_scatter_aggregate_ep_hip:
+  // the three stages behind forward() once peers are attached
+  void moe_mlp2_push_to_owners(int layer, void *stream) { check(gptoss_moe_push_to_owners(ctx_, layer, stream)); }
+  void owner_combine(void *stream) { check(gptoss_moe_owner_combine(ctx_, stream)); }
+  void add_delivered(float *x, void *stream) { check(gptoss_moe_add_delta(ctx_, x, stream)); }
+  // token-sliced form: residual_rmsnorm (layer_hip_batch.cpp:95) of this rank's rows + the all-gather that replaces
+  // ring_all_reduce_tb2_quantize_fp8 (parallelism.cpp:1195); then the block on the gathered rows, sums kept by the owner
+  void residual_rmsnorm_gather(float *x_slice, const float *add, const float *norm_w, int cur_batch_size, void *stream) {
+    check(gptoss_moe_gather_slice(ctx_, cur_batch_size, x_slice, add, norm_w, stream));
+  }
+  void forward_sliced(int layer, float *x_slice, int cur_batch_size, void *stream) {
+    check(gptoss_moe_forward_sliced(ctx_, layer, cur_batch_size, x_slice, stream));
+  }
+  void slice_bounds(int cur_batch_size, int *first, int *count) const {
+    gptoss_moe_slice_bounds(ctx_, cur_batch_size, first, count);
+  }
   // synchronises and reports a device-side time-out, if any
   void check_device() { check(gptoss_ctx_status(ctx_)); }
   gptoss_ctx *raw() { return ctx_; }
