@@ -46,7 +46,7 @@ FLOP_PER_TOKEN = 2 * H * E + 2 * K_TOP * H * (2 * I) + 2 * K_TOP * I * H  # 199,
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM kernel at this workload,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_MLP1_BYTES = 1_124_969_080  # profiles/moe_block_cfg2_T1024.md (dram read 1.101467 GB + write 23.50 MB)
+NCU_TRAFFIC_MLP1_BYTES = 1_105_950_368  # dram read 1,102,148,000 + write 3,802,368 per launch (profiles/moe_block_cfg2_T1024.md)
 
 
 def measured_peaks():
@@ -171,7 +171,7 @@ def run_reference(args):
         return
     # torchrun pins OMP_NUM_THREADS to 1; the reference arm uses every host core (set before libgomp loads)
     os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
-    T = TOKENS_PER_GPU * args.gpus
+    T = (args.tokens_per_gpu or TOKENS_PER_GPU) * args.gpus
     tok_s, info, times = cpu_arm(T, target_seconds=6.0, repeats=max(1, args.steps), warmup=min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": "batched decode tok/s, gpt-oss-20b MoE FFN block (one layer call per step)",
@@ -212,7 +212,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    T = TOKENS_PER_GPU * world
+    T = (args.tokens_per_gpu or TOKENS_PER_GPU) * world
     K, W = args.steps, max(args.warmup, 3)
 
     global N_WEIGHT_SETS
@@ -521,6 +521,9 @@ def main():
     ap.add_argument("--decode-first-pos", type=int, default=0,
                     help="profiling runs: start the timed decode at this position (cache rows before it are zeros)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--tokens-per-gpu", type=int, default=0,
+                    help="tokens per step and GPU (0 = 1024, the headline workload; 8192 on one GPU = BASELINE config 3's "
+                         "shape, where the block is tensor-bound)")
     ap.add_argument("--zipf", type=float, default=0.0,
                     help="skew the routing: router_bias[e] -= s*ln(e+1) (1.2 = BASELINE config 3); 0 = uniform")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,

@@ -21,6 +21,8 @@
 //
 // Every mbarrier wait is bounded: when a wait gives up the CTA raises an abort flag, records a
 // time-out in the status words, drains its outstanding copies, frees its TMEM and returns.
+#include <cstdlib>
+
 #include "kernels.cuh"
 #include "tcgen05.cuh"
 
@@ -38,14 +40,20 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 8;
 constexpr int kRingBytes = 216 * 1024;
 
-template <int NA>
+// NA = weight tiles per ring stage (both multiply the same token rows); GLU = the two tiles are the gate and up
+// halves of the same 128 features (SwiGLU epilogue, bf16 out), otherwise they are two adjacent 128-feature tiles
+// of the down projection (fp32 rows by pair id).  Two tiles per stage double the MMA work and the weight bytes
+// in flight per byte of token rows staged.
+template <int NA, bool GLU>
 struct TileCfg {
   static constexpr int kAStageBytes = NA * kATileBytes;
-  static constexpr int kAccBuffers = (NA == 2) ? 1 : 2;   // gate+up fill all 512 TMEM columns at 256 tokens
-  static constexpr int kMetaTokens = (NA == 2) ? 1 : kMaxTileTokens;  // pair/weight staging only for mlp2
+  static constexpr int kAccBuffers = (NA == 2) ? 1 : 2;   // two tiles fill all 512 TMEM columns at 256 tokens
+  static constexpr int kMetaTokens = GLU ? 1 : kMaxTileTokens;  // pair/weight staging only for the down projection
+  static constexpr int kTileFeat = (NA == 2 && !GLU) ? 2 * kTileF : kTileF;  // output features per tile
+  static constexpr int kSlabs = GLU ? 2 : 1;                // weight slabs per expert in the tensor map
 };
 
-template <int NA>
+template <int NA, bool GLU>
 struct Ctrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -56,8 +64,8 @@ struct Ctrl {
   int max_rows;
   int tbp[kMaxExperts + 1];
   int off[kMaxExperts + 1];
-  float *dst_s[2][TileCfg<NA>::kMetaTokens];  // mlp2: destination row of each token column (local or peer)
-  float w_s[2][TileCfg<NA>::kMetaTokens];     // mlp2: gate weight of each token column
+  float *dst_s[2][TileCfg<NA, GLU>::kMetaTokens];  // mlp2: destination row of each token column (local or peer)
+  float w_s[2][TileCfg<NA, GLU>::kMetaTokens];     // mlp2: gate weight of each token column
 };
 
 struct Tile {
@@ -67,7 +75,7 @@ struct Tile {
   int n_valid;  // rows in the tile
 };
 
-template <class C>
+template <int TILE_FEAT, class C>
 __device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, int nft, int &cur, Tile &t) {
   while (cur < n_local && idx >= c->tbp[cur + 1] * nft) ++cur;
   if (cur >= n_local) return false;
@@ -78,7 +86,7 @@ __device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, in
   const int rows = c->off[cur + 1] - c->off[cur];
   const int blk = (((rows + nb - 1) / nb) + 15) & ~15;
   t.e = cur;
-  t.f0 = ft * kTileF;
+  t.f0 = ft * TILE_FEAT;
   t.row0 = c->off[cur] + tb * blk;
   t.n_valid = min(blk, rows - tb * blk);
   return true;
@@ -92,10 +100,10 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
 }
 
-template <int NA>
+template <int NA, bool GLU>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmArgs a) {
-  using Cfg = TileCfg<NA>;
-  using CtrlT = Ctrl<NA>;
+  using Cfg = TileCfg<NA, GLU>;
+  using CtrlT = Ctrl<NA, GLU>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t ring = smem_u32(smem_raw);
   CtrlT *ctrl = reinterpret_cast<CtrlT *>(smem_raw + kRingBytes);
@@ -159,7 +167,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       // Head start: the weights do not depend on the kernel before this one, so the weight tiles of the first
       // ring fill are requested before waiting for it; its outputs (the activation rows) are loaded after.
       int pre = 0;
-      if ((int)blockIdx.x < total_tiles && decode_tile(blockIdx.x, ctrl, n_local, nft, cur, t)) {
+      if ((int)blockIdx.x < total_tiles && decode_tile<Cfg::kTileFeat>(blockIdx.x, ctrl, n_local, nft, cur, t)) {
         const int n_chunks = (max(16, (t.n_valid + 15) & ~15) + kTokChunk - 1) / kTokChunk;
         pre = min(n_stages, a.k_blocks);
         for (int kb = 0; kb < pre; ++kb) {
@@ -167,8 +175,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           const uint32_t sa = ring + kb * stage_bytes;
           armed |= 1u << kb;
           mbar_expect_tx(bar, Cfg::kAStageBytes + n_chunks * kBChunkBytes);
-          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA, pol_w);
-          if (NA == 2) tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1, pol_w);
+          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * Cfg::kSlabs, pol_w);
+          if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
+            tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF,
+                             GLU ? t.e * Cfg::kSlabs + 1 : t.e * Cfg::kSlabs, pol_w);
         }
         pdl_wait();
         pdl_launch_dependents();
@@ -184,7 +194,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         pdl_launch_dependents();
       }
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-        if (!decode_tile(idx, ctrl, n_local, nft, cur, t)) break;
+        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const int n_chunks = (n_mma + kTokChunk - 1) / kTokChunk;
         const uint32_t tx = Cfg::kAStageBytes + n_chunks * kBChunkBytes;
@@ -195,8 +205,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           armed |= 1u << stage;
           last_par = (last_par & ~(1u << stage)) | (phase << stage);
           mbar_expect_tx(bar, tx);
-          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA, pol_w);
-          if (NA == 2) tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, t.f0, t.e * NA + 1, pol_w);
+          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * Cfg::kSlabs, pol_w);
+          if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
+            tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF,
+                             GLU ? t.e * Cfg::kSlabs + 1 : t.e * Cfg::kSlabs, pol_w);
           const uint32_t sb = sa + Cfg::kAStageBytes;
           for (int c = 0; c < n_chunks; ++c)
             tma_load_2d(sb + c * kBChunkBytes, &a.map_act, bar, kb * kBlockK, t.row0 + c * kTokChunk);
@@ -221,7 +233,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       uint32_t phase = 0, acc_phase = 0;
       Tile t;
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-        if (!decode_tile(idx, ctrl, n_local, nft, cur, t)) break;
+        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const uint32_t idesc = umma_idesc(n_mma);
         mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1u, &ctrl->abort, a.status, 0x200 | acc);
@@ -263,10 +275,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     Tile t;
     const uint64_t pol_keep = l2_policy_evict_last();  // the outputs are read again by the next kernel
     for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-      if (!decode_tile(idx, ctrl, n_local, nft, cur, t)) break;
+      if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
       const int f = t.f0 + q * 32 + lane;
       const bool f_ok = f < a.n_feat;
-      if constexpr (NA == 1) {
+      if constexpr (!GLU) {
+        // one staging buffer per accumulator buffer: with a single one, every epilogue thread must have left the
+        // previous tile before its slots are overwritten
+        if (Cfg::kAccBuffers == 1) epilogue_bar_sync();
         for (int n = et; n < t.n_valid; n += kEpilogueThreads) {
           const int pair = a.sorted[t.row0 + n];
           float *base = a.y_pairs;
@@ -277,7 +292,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         epilogue_bar_sync();
       }
       const float bias0 = (f_ok && a.bias_a) ? a.bias_a[(size_t)t.e * a.n_feat + f] : 0.f;  // a null bias means none
-      const float bias1 = (NA == 2 && f_ok) ? a.bias_b[(size_t)t.e * a.n_feat + f] : 0.f;
+      const bool f1_ok = NA == 2 && !GLU && f + kTileF < a.n_feat;  // second tile of the down projection: feature f + 128
+      const float bias1 = (GLU && f_ok)            ? a.bias_b[(size_t)t.e * a.n_feat + f]
+                          : (f1_ok && a.bias_a) ? a.bias_a[(size_t)t.e * a.n_feat + f + kTileF]
+                                                : 0.f;
       mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
       tc_fence_after();
       const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kMaxTileTokens);
@@ -289,7 +307,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         if (NA == 2) tmem_ld16(tbase + kMaxTileTokens + c0, r1);
         tmem_ld_wait();
         float v[16];
-        if constexpr (NA == 2) {
+        if constexpr (GLU) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             v[j] = swiglu(__uint_as_float(r0[j]) + bias0, __uint_as_float(r1[j]) + bias1, a.limit);
@@ -310,6 +328,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (f_ok && c0 + j < t.n_valid) st_f32_hint(pr[j] + f, v[j], pol_keep);
+          if constexpr (NA == 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f1_ok && c0 + j < t.n_valid)
+                st_f32_hint(pr[j] + f + kTileF, (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j], pol_keep);
+          }
         }
       }
       tc_fence_before();
@@ -327,7 +351,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if constexpr (NA == 1) {
+  if constexpr (!GLU) {
     // pushing to owners: every row this CTA stored (possibly into a peer's memory) is ordered before the count by
     // the barrier above plus this thread's system-scope fence; the last CTA to finish raises this rank's "pushed"
     // flag on every rank
@@ -343,14 +367,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   }
 }
 
-template <int NA>
+template <int NA, bool GLU>
 cudaError_t launch_grouped(const GemmArgs &a, int sm_count, cudaStream_t s) {
-  const size_t smem = (size_t)kRingBytes + sizeof(Ctrl<NA>);
-  static_assert(kRingBytes + sizeof(Ctrl<NA>) <= 232448, "exceeds the 227 KiB dynamic shared memory of an SM");
+  const size_t smem = (size_t)kRingBytes + sizeof(Ctrl<NA, GLU>);
+  static_assert(kRingBytes + sizeof(Ctrl<NA, GLU>) <= 232448, "exceeds the 227 KiB dynamic shared memory of an SM");
   static_assert(kRingBytes >= 2 * (2 * kATileBytes + kMaxTileTokens * kBlockK * 2), "ring must hold two full stages");
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return launch_chain(grouped_gemm_kernel<NA>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
+  return launch_chain(grouped_gemm_kernel<NA, GLU>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -374,10 +398,23 @@ cudaError_t get_encode_fn(EncodeTiledFn *fn) {
 }  // namespace
 
 cudaError_t launch_grouped_mlp1(const GemmArgs &a, int sm_count, cudaStream_t s) {
-  return launch_grouped<2>(a, sm_count, s);
+  return launch_grouped<2, true>(a, sm_count, s);
 }
+// Down projection / dense GEMM: two adjacent 128-feature tiles per ring stage (one pass over the token rows feeds
+// 256 output features) unless there are at most 128 features, or GPTOSS_MLP2_SINGLE=1 asks for the one-tile kernel
+// (A/B measurements).  The feature-tile count of the arguments is recomputed for the tile width used.
 cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s) {
-  return launch_grouped<1>(a, sm_count, s);
+  static const bool single = [] {
+    const char *e = getenv("GPTOSS_MLP2_SINGLE");
+    return e && e[0] == '1';
+  }();
+  GemmArgs b = a;
+  if (single || a.n_feat <= kTileF) {
+    b.n_feat_tiles = (a.n_feat + kTileF - 1) / kTileF;
+    return launch_grouped<1, false>(b, sm_count, s);
+  }
+  b.n_feat_tiles = (a.n_feat + 2 * kTileF - 1) / (2 * kTileF);
+  return launch_grouped<2, false>(b, sm_count, s);
 }
 
 cudaError_t encode_weight_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs) {

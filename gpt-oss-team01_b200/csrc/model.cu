@@ -157,7 +157,7 @@ int dense(gptoss_model *m, int which, const CUtensorMap &map_w, const CUtensorMa
 // about its block's rows (at least 64: below that the weight tile's shared-memory reads bound the MMA) plus a
 // fixed part (pipeline fill, epilogue), here 32 rows' worth.  More, smaller blocks can fill the last round.
 int pick_token_blocks(int B, int n_out, int sm_count) {
-  const int nft = (n_out + kTileF - 1) / kTileF;
+  const int nft = n_out <= kTileF ? 1 : (n_out + 2 * kTileF - 1) / (2 * kTileF);  // the dense GEMM works on 256-feature tiles
   const int nb_min = (B + kMaxTileTokens - 1) / kMaxTileTokens;
   int best = nb_min > 0 ? nb_min : 1;
   long best_cost = -1;
