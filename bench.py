@@ -60,8 +60,8 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs.  nvidia-smi needs up to a
     second before its first line on a box with many GPUs, so the sampler may be started ahead of the region
-    (``start()``, e.g. before the warm-up steps); only the lines read between ``with`` entry and exit count, plus the
-    last one before and the first one after when the region is shorter than the sampling period."""
+    (``start()``, e.g. before the warm-up steps); only the lines read between ``with`` entry and exit count (the last
+    one before and the first one after stand in when the region was shorter than one sampling period)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -102,7 +102,7 @@ class ClockSampler:
         inside = [r for t, r in self.all_rows if self.t_in <= t <= self.t_out]
         before = [r for t, r in self.all_rows if t < self.t_in][-1:]
         after = [r for t, r in self.all_rows if t > self.t_out][:1]
-        self.rows = inside if len(inside) >= 3 else before + inside + after
+        self.rows = inside if inside else before + after  # idle samples around the region only if it held none
 
     def summary(self):
         sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
