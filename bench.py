@@ -348,7 +348,7 @@ def run_ours(args):
         roof = {"bound": "tensor", "achieved": mlp1_flops / mlp1_s / 1e12, "peak": tf_burst, "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof["traffic"] = NCU_TRAFFIC_MLP1_BYTES if world == 1 else None  # captured at the N=1 workload only
-    roof.update({"kernel": "grouped_gemm_kernel<2> (gate/up GEMM + SwiGLU)", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)",
+    roof.update({"kernel": "grouped_gemm_kernel<2,true> (gate/up GEMM + SwiGLU)", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)",
                  "algorithmic_bytes_per_launch": mlp1_bytes, "algorithmic_flops_per_launch": mlp1_flops,
                  "avg_launch_ms": stage_ms["mlp1_swiglu"], "tensor_frac_of_burst": mlp1_flops / mlp1_s / 1e12 / tf_burst})
     block_bytes = n_local * 3 * H * I * 2 + n_local * (2 * I + H) * 2 + (H * E + E) * 2 + T * H * 2 + T * H * 8

@@ -11,13 +11,15 @@
 //
 // One persistent CTA per SM, 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one elected thread) and
 // TMEM owner, warps 2-9 = epilogue (two warps per TMEM lane quadrant, alternating 16-column chunks).
-// Tiles are (expert, token block of <= 256 rows, 128-feature tile), enumerated from the device-built
-// token-block prefix, so no row count ever travels to the host.
+// Tiles are (expert, token block of <= 256 rows, feature tile), enumerated from the device-built
+// token-block prefix, so no row count ever travels to the host.  A ring stage carries two weight tiles that
+// multiply the same token rows: the gate and up rows of 128 features (mlp1), or two adjacent 128-feature tiles
+// (mlp2 and the dense GEMMs; a one-tile variant remains for outputs of at most 128 features).
 //
 // The block is bound by streaming weights, so what matters is the number of weight bytes in flight per SM:
 // a ring stage holds the weight tile(s) of one k-block plus the activation rows of the largest token block
 // of this launch (read from the expert offsets, rounded to 32 rows), and the ring takes as many stages as
-// fit into shared memory (decode: 4 x 52 KiB for mlp1, 6 x 36 KiB for mlp2).
+// fit into shared memory (decode: 4 x 52 KiB).
 //
 // Every mbarrier wait is bounded: when a wait gives up the CTA raises an abort flag, records a
 // time-out in the status words, drains its outstanding copies, frees its TMEM and returns.
