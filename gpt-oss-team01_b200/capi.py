@@ -24,7 +24,7 @@ OK, ERR_BAD_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_STATE = range(6)
 WIRE_F32, WIRE_BF16 = 0, 1
 IPC_HANDLE_BYTES = 64
 (TAP_SCORES, TAP_TOPK_W, TAP_TOPK_I, TAP_OFFSETS, TAP_SORTED, TAP_X_PACKED, TAP_GATE_UP,
- TAP_Y_PAIRS) = range(8)
+ TAP_Y_PAIRS, TAP_GATHERED) = range(9)
 
 # every symbol include/gptoss_b200.h declares
 EXPORTS = [
@@ -41,7 +41,7 @@ EXPORTS = [
     "gptoss_model_read_logits", "gptoss_moe_slice_bounds", "gptoss_moe_gather_slice", "gptoss_moe_sliced_push",
     "gptoss_moe_sliced_combine", "gptoss_moe_forward_sliced", "gptoss_model_create_ep", "gptoss_model_moe_ctx",
     "gptoss_model_slice", "gptoss_model_step_begin", "gptoss_model_layer_attention", "gptoss_model_layer_moe_push",
-    "gptoss_model_layer_moe_combine", "gptoss_model_step_end", "gptoss_comm_rendezvous",
+    "gptoss_model_layer_moe_combine", "gptoss_model_step_end", "gptoss_comm_rendezvous", "gptoss_moe_gather_rows", "gptoss_moe_forward_host_sliced",
 ]
 
 
@@ -146,6 +146,8 @@ def load() -> C.CDLL:
         "gptoss_model_layer_moe_combine": ([vp, i32], i32),
         "gptoss_model_step_end": ([vp, vp], i32),
         "gptoss_comm_rendezvous": ([ctxp, vp], i32),
+        "gptoss_moe_gather_rows": ([ctxp, i32, vp, vp], i32),
+        "gptoss_moe_forward_host_sliced": ([ctxp, i32, i32, vp, vp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -535,11 +535,29 @@ int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const fl
   int rc = check_attached(ctx);
   if (rc) return rc;
   if ((rc = check_T(ctx, T))) return rc;
-  if (!x_slice_dev || !norm_w_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice or norm-weight pointer");
   if (T == 0) return GPTOSS_OK;
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(ctx, T, &first, &n);  // a rank without tokens still takes part (it raises its flag)
+  if ((n > 0 && !x_slice_dev) || !norm_w_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice or norm-weight pointer");
   CK(cudaSetDevice(ctx->device));
   const int step = ++ctx->gather_step;
   CK(launch_slice_norm_gather(ctx->peers, T, ctx->d.H, x_slice_dev, add_dev, norm_w_dev, step, ctx->comm_counter,
+                              static_cast<cudaStream_t>(stream)));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_gather_rows(gptoss_ctx *ctx, int T, const void *t_slice_dev_bf16, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (T == 0) return GPTOSS_OK;
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(ctx, T, &first, &n);
+  if (n > 0 && !t_slice_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
+  if (n > 0 && (reinterpret_cast<uintptr_t>(t_slice_dev_bf16) & 15)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "slice must be 16-byte aligned");
+  CK(cudaSetDevice(ctx->device));
+  const int step = ++ctx->gather_step;
+  CK(launch_slice_copy_gather(ctx->peers, T, ctx->d.H, t_slice_dev_bf16, step, ctx->comm_counter, ctx->sm_count,
                               static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }
@@ -569,7 +587,9 @@ int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream) {
 int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream) {
   int rc = check_attached(ctx);
   if (rc) return rc;
-  if (!x_slice_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(ctx, ctx->cur_T, &first, &n);
+  if (n > 0 && !x_slice_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
   CK(cudaSetDevice(ctx->device));
   if (ctx->cur_T == 0) return GPTOSS_OK;
   CK(launch_combine_owner_slice(ctx->peers, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, x_slice_dev, ctx->status,
@@ -652,6 +672,42 @@ int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t
   CK(cudaMemcpyAsync(ctx->status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_main));
   CK(cudaStreamSynchronize(ctx->s_main));
   if (ctx->status_host[0] != 0) return gptoss_ctx_status(ctx);  // formats the message and clears the word
+  return GPTOSS_OK;
+}
+
+// Token-sliced form through host buffers: this rank's rows of t and x only (the host -> device traffic of a step is
+// then the batch once over all GPUs instead of once per GPU); the rows of the other ranks arrive over NVLink.
+int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (T == 0) return GPTOSS_OK;
+  int first = 0, n_rows = 0;
+  gptoss_moe_slice_bounds(ctx, T, &first, &n_rows);
+  if (n_rows > 0 && (!t_host_slice || !x_host_slice)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
+  CK(cudaSetDevice(ctx->device));
+  if (!ctx->s_main) {
+    CK(cudaStreamCreateWithFlags(&ctx->s_main, cudaStreamNonBlocking));
+    CK(cudaStreamCreateWithFlags(&ctx->s_copy, cudaStreamNonBlocking));
+    CK(cudaEventCreateWithFlags(&ctx->ev_x, cudaEventDisableTiming));
+    CK(cudaEventCreateWithFlags(&ctx->ev_t, cudaEventDisableTiming));
+    CK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), kStatusWords * sizeof(int), cudaHostAllocDefault));
+  }
+  const size_t n = (size_t)n_rows * ctx->d.H;
+  if (n) CK(cudaMemcpyAsync(ctx->t_stage, t_host_slice, n * sizeof(uint16_t), cudaMemcpyHostToDevice, ctx->s_main));
+  CK(cudaEventRecord(ctx->ev_t, ctx->s_main));
+  CK(cudaStreamWaitEvent(ctx->s_copy, ctx->ev_t, 0));  // the residual rows follow the activations on the copy engine
+  if (n) CK(cudaMemcpyAsync(ctx->x_stage, x_host_slice, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
+  CK(cudaEventRecord(ctx->ev_x, ctx->s_copy));
+  if ((rc = gptoss_moe_gather_rows(ctx, T, ctx->t_stage, ctx->s_main))) return rc;
+  if ((rc = gptoss_moe_sliced_push(ctx, layer, T, ctx->s_main))) return rc;
+  CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
+  if ((rc = gptoss_moe_sliced_combine(ctx, ctx->x_stage, ctx->s_main))) return rc;
+  if (n) CK(cudaMemcpyAsync(x_host_slice, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_main));
+  CK(cudaMemcpyAsync(ctx->status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_main));
+  CK(cudaStreamSynchronize(ctx->s_main));
+  if (ctx->status_host[0] != 0) return gptoss_ctx_status(ctx);
   return GPTOSS_OK;
 }
 
@@ -775,6 +831,7 @@ int gptoss_read_tap(gptoss_ctx *ctx, int tap, void *host_dst, uint64_t bytes) {
     case GPTOSS_TAP_X_PACKED: src = ctx->x_packed; cap = P * H * 2; break;
     case GPTOSS_TAP_GATE_UP: src = ctx->gate_up; cap = P * I * 2; break;
     case GPTOSS_TAP_Y_PAIRS: src = ctx->y_pairs; cap = P * H * 4; break;
+    case GPTOSS_TAP_GATHERED: src = ctx->sym + ctx->sym_delta_off; cap = T * H * 2; break;
     default: return ctx->fail(GPTOSS_ERR_BAD_ARG, "unknown tap");
   }
   if (bytes > cap) return ctx->fail(GPTOSS_ERR_BAD_ARG, "tap read larger than the buffer");

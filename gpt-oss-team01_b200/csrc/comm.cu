@@ -160,6 +160,22 @@ __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, in
   signal_all_ranks(pt, 2, step, counter);
 }
 
+// Token-sliced form, producer side, for rows that are already normalised: copies this rank's bf16 rows into the
+// gathered activation buffer of every rank (16 bytes per thread and peer); the last block raises flag C.
+__global__ void __launch_bounds__(256) slice_copy_gather_kernel(PeerTable pt, int T, int H, const uint4 *__restrict__ t_slice,
+                                                                int step, int *counter) {
+  pdl_wait();
+  const int slice = (T + pt.world - 1) / pt.world;
+  const int b0 = pt.rank * slice, n_rows = max(0, min(T, b0 + slice) - b0);
+  const size_t total = (size_t)n_rows * H / 8, first = (size_t)b0 * H / 8;  // H % 8 == 0
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = t_slice[i];
+    for (int r = 0; r < pt.world; ++r) reinterpret_cast<uint4 *>(pt.delta[r])[first + i] = v;
+  }
+  pdl_launch_dependents();
+  signal_all_ranks(pt, 2, step, counter);
+}
+
 // Token-sliced form, consumer side: returns once every rank's slice of the gathered activations has arrived.
 __global__ void wait_gathered_kernel(PeerTable pt, int step, int *status) {
   pdl_wait();
@@ -232,6 +248,17 @@ cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x
   int rows = T - pt.rank * slice;
   rows = rows < 0 ? 0 : (rows > slice ? slice : rows);
   return launch_chain(slice_norm_gather_kernel, dim3(rows > 0 ? rows : 1), dim3(256), 0, s, pt, T, H, x_slice, add, w, step,
+                      counter);
+}
+
+cudaError_t launch_slice_copy_gather(const PeerTable &pt, int T, int H, const void *t_slice, int step, int *counter,
+                                     int sm_count, cudaStream_t s) {
+  const int slice = (T + pt.world - 1) / pt.world;
+  const size_t total = (size_t)slice * H / 8;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > sm_count * 4) blocks = sm_count * 4;
+  if (blocks < 1) blocks = 1;
+  return launch_chain(slice_copy_gather_kernel, dim3(blocks), dim3(256), 0, s, pt, T, H, static_cast<const uint4 *>(t_slice), step,
                       counter);
 }
 

@@ -65,6 +65,8 @@ cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, 
 
 cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x_slice, const float *add, const float *w,
                                      int step, int *counter, cudaStream_t s);
+cudaError_t launch_slice_copy_gather(const PeerTable &pt, int T, int H, const void *t_slice, int step, int *counter,
+                                     int sm_count, cudaStream_t s);
 cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s);
 cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaStream_t s);
 cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,

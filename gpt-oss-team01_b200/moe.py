@@ -175,6 +175,35 @@ class MoEBlock:
         T = t_bits.shape[0]
         self._check(self.lib.gptoss_moe_forward_host(self._ctx, layer, T, _ptr(t_bits), _ptr(x)))
 
+    # -- token-sliced form: every rank holds only its rows of the residual stream ---------------------------------
+    def slice(self, n_tokens):
+        """(first token, token count) of this rank's slice of a batch of n_tokens."""
+        return slice_bounds(self.rank, self.world, n_tokens)
+
+    def gather_slice(self, n_tokens, x_slice, norm_w, add=None, stream=None):
+        """x_slice (+)= add; bf16(RMSNorm(x_slice) * norm_w) stored into every rank's gathered activations."""
+        self._check(self.lib.gptoss_moe_gather_slice(self._ctx, n_tokens, _ptr(x_slice), _ptr(add) if add is not None else None,
+                                                     _ptr(norm_w), _stream(stream)))
+
+    def gather_rows(self, n_tokens, t_slice, stream=None):
+        """this rank's (already normalised) bf16 rows copied into every rank's gathered activations."""
+        self._check(self.lib.gptoss_moe_gather_rows(self._ctx, n_tokens, _ptr(t_slice) if t_slice is not None else None,
+                                                    _stream(stream)))
+
+    def sliced_push(self, layer, n_tokens, stream=None):
+        self._check(self.lib.gptoss_moe_sliced_push(self._ctx, layer, n_tokens, _stream(stream)))
+
+    def sliced_combine(self, x_slice, stream=None):
+        self._check(self.lib.gptoss_moe_sliced_combine(self._ctx, _ptr(x_slice), _stream(stream)))
+
+    def forward_sliced(self, layer, n_tokens, x_slice, stream=None):
+        self._check(self.lib.gptoss_moe_forward_sliced(self._ctx, layer, n_tokens, _ptr(x_slice), _stream(stream)))
+
+    def forward_host_sliced(self, layer, n_tokens, t_bits_slice, x_slice):
+        """Host buffers holding THIS RANK'S rows of a batch of n_tokens: t_bits_slice uint16 [n,H], x_slice fp32 [n,H]
+        in/out.  Synchronous; every rank calls it."""
+        self._check(self.lib.gptoss_moe_forward_host_sliced(self._ctx, layer, n_tokens, _ptr(t_bits_slice), _ptr(x_slice)))
+
     # -- stages (reference launcher names in the docstrings) --------------------------------------------------
     def route(self, layer, t, stream=None):
         """router_gemm_v2 + topk_softmax_batched + moe_build_offsets_hip + moe_pack_inputs_hip"""
@@ -219,6 +248,7 @@ class MoEBlock:
         "topk_i": (capi.TAP_TOPK_I, np.int32), "offsets": (capi.TAP_OFFSETS, np.int32),
         "sorted": (capi.TAP_SORTED, np.int32), "x_packed": (capi.TAP_X_PACKED, np.uint16),
         "gate_up": (capi.TAP_GATE_UP, np.uint16), "y_pairs": (capi.TAP_Y_PAIRS, np.float32),
+        "gathered": (capi.TAP_GATHERED, np.uint16),
     }
 
     def tap(self, name, T):
@@ -226,7 +256,7 @@ class MoEBlock:
         H, I, E, k = self.H, self.I, self.E, self.k
         shape = {"scores": (T, E), "topk_w": (T, k), "topk_i": (T, k), "offsets": (E + 1,),
                  "sorted": (T * k,), "x_packed": (T * k, H), "gate_up": (T * k, I),
-                 "y_pairs": (T * k, H)}[name]
+                 "y_pairs": (T * k, H), "gathered": (T, H)}[name]
         out = np.empty(shape, dt)
         self._check(self.lib.gptoss_read_tap(self._ctx, tap, _ptr(out), out.nbytes))
         return out

@@ -161,9 +161,17 @@ int gptoss_moe_slice_bounds(const gptoss_ctx *ctx, int T, int *first, int *count
 int gptoss_comm_rendezvous(gptoss_ctx *ctx, void *stream);
 int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const float *add_dev, const float *norm_w_dev,
                             void *stream);
+/* gather_rows: like gather_slice for rows that are already normalised: copies this rank's bf16 rows
+ * [slice count, H] (device, 16-byte aligned) into the gathered activations of every rank and raises "gathered". */
+int gptoss_moe_gather_rows(gptoss_ctx *ctx, int T, const void *t_slice_dev_bf16, void *stream);
 int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream);
 int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream);
 int gptoss_moe_forward_sliced(gptoss_ctx *ctx, int layer, int T, float *x_slice_dev, void *stream);
+/* The token-sliced block through HOST buffers (pinned memory recommended): t_host_slice bf16 [slice count, H] and
+ * x_host_slice fp32 [slice count, H] hold THIS RANK'S rows of a batch of T tokens; on return x_host_slice holds
+ * x + MoE(t) for them.  Per step each GPU moves only its slice over PCIe (the batch crosses the host link once in
+ * total, not once per GPU); the other ranks' activations arrive over NVLink.  Synchronous; every rank must call it. */
+int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice);
 
 /* ---- stages of the operator (same order as inside gptoss_moe_forward) ------------------------------
  * They work on the context's scratch so that a test can stop after any stage and read the taps. */
@@ -217,6 +225,7 @@ const char *gptoss_noalloc_last_error(void);
 #define GPTOSS_TAP_X_PACKED 5  /* bf16 [T*k,H] gathered inputs (rows of this rank's experts only)  */
 #define GPTOSS_TAP_GATE_UP 6   /* bf16 [T*k,I] SwiGLU output, rows in sorted order                 */
 #define GPTOSS_TAP_Y_PAIRS 7   /* fp32 [T*k,H] gate_weight * expert output, rows by PAIR id        */
+#define GPTOSS_TAP_GATHERED 8  /* bf16 [T,H]   token-sliced form: the activations gathered from all ranks */
 /* Copies `bytes` from the start of the tap to host memory after synchronising the device. */
 int gptoss_read_tap(gptoss_ctx *ctx, int tap, void *host_dst, uint64_t bytes);
 

@@ -51,6 +51,23 @@ def _worker(rank, world, port, out_dir):
             want = torch.empty_like(got)
         dist.broadcast(want, src=0)
         ok = ok and bool(torch.equal(got, want))
+    # the token-sliced form through host buffers: every rank moves only its rows over PCIe
+    first, n = blk.slice(T)
+    for step in range(3):
+        t = synth.activations(400 + step, T, H)
+        x0 = synth.normal(500 + step, synth.tensor_id(synth.TID_RESIDUAL), (T, H), 1.0)
+        t_bits = torch.from_numpy(synth.f32_to_bf16_bits(t).view(np.int16).reshape(T, H))
+        t_slice = t_bits[first:first + n].contiguous().pin_memory()
+        x_slice = torch.from_numpy(x0[first:first + n].copy()).pin_memory()
+        blk.forward_host_sliced(0, T, t_slice, x_slice)
+        if rank == 0:
+            want = torch.from_numpy(x0.copy()).cuda()
+            single.forward(0, t_bits.cuda().view(torch.bfloat16), want)
+            want = want.cpu()
+        else:
+            want = torch.empty((T, H), dtype=torch.float32)
+        dist.broadcast(want, src=0)
+        ok = ok and bool(torch.equal(x_slice, want[first:first + n]))
     dist.barrier()
     blk.close()
     if single:
