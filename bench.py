@@ -67,12 +67,13 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, enabled: bool = True):
         self.index, self.all_rows, self.rows, self.proc = index, [], [], None
         self.t_in = self.t_out = None
+        self.enabled = enabled  # only the rank that prints the line samples
 
     def start(self):
-        if self.proc is None:
+        if self.proc is None and self.enabled:
             try:
                 self.proc = subprocess.Popen(
                     ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
@@ -210,6 +211,7 @@ def run_ours(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
     torch.cuda.set_device(local_rank)
+    clocks = ClockSampler(local_rank, enabled=rank == 0).start()  # nvidia-smi needs a second or more before its first line on an 8-GPU box
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     T = (args.tokens_per_gpu or TOKENS_PER_GPU) * world
@@ -244,7 +246,6 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    clocks = ClockSampler(local_rank).start()
     for i in range(W):
         step(i)
     barrier()
