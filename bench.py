@@ -338,7 +338,16 @@ def run_ours(args):
 
     hbm_peak, tf_burst, tf_sust, peak_kind = measured_peaks()
     n_local = E // world
-    pairs_local = T * K_TOP // world  # expected rows of this rank's experts under uniform routing
+    # rows of this rank's experts in the routing of the last step (T*k/world under uniform routing); the rank with the
+    # most rows decides an expert-parallel step
+    off = blk.tap("offsets", T)
+    rows_here = int(off[(rank + 1) * n_local] - off[rank * n_local])
+    rows_max = rows_here
+    if world > 1:
+        rm = torch.tensor([rows_here], device="cuda")
+        dist.all_reduce(rm, op=dist.ReduceOp.MAX)
+        rows_max = int(rm.item())
+    pairs_local = rows_here
     mlp1_bytes = n_local * (2 * I * H * 2 + 2 * I * 4) + pairs_local * H * 2 + pairs_local * I * 2
     mlp1_flops = 2 * pairs_local * H * 2 * I
     mlp1_s = stage_ms["mlp1_swiglu"] * 1e-3
@@ -355,6 +364,8 @@ def run_ours(args):
     block_bytes = n_local * 3 * H * I * 2 + n_local * (2 * I + H) * 2 + (H * E + E) * 2 + T * H * 2 + T * H * 8
     block_flops = FLOP_PER_TOKEN * T / world
     block_roof_s = max(block_bytes / (hbm_peak * 1e9), block_flops / (tf_sust * 1e12))
+    busiest_flops = 2.0 * rows_max * 3 * H * I + 2.0 * T * H * E
+    busiest_roof_s = max(block_bytes / (hbm_peak * 1e9), busiest_flops / (tf_sust * 1e12))
 
     line = {
         "metric": "batched decode tok/s, gpt-oss-20b MoE FFN block (one layer call per step)",
@@ -365,6 +376,8 @@ def run_ours(args):
         "roofline": roof,
         "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
                            "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
+                           "busiest_rank_rows": rows_max, "rows_per_rank_if_even": T * K_TOP // world,
+                           "roof_ms_busiest_rank": busiest_roof_s * 1e3, "frac_busiest_rank": busiest_roof_s * 1e3 / (ms / K),
                            "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
         "stage_ms": stage_ms, "gpu_launches": (7 if world == 1 else 8) * K,  # router GEMM, top-k, scan, scatter, 2 GEMMs, combine (N > 1: owner combine + add instead)
     }
