@@ -46,7 +46,7 @@ FLOP_PER_TOKEN = 2 * H * E + 2 * K_TOP * H * (2 * I) + 2 * K_TOP * I * H  # 199,
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM kernel at this workload,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_MLP1_BYTES = 1_105_950_368  # dram read 1,102,148,000 + write 3,802,368 per launch (profiles/moe_block_cfg2_T1024.md)
+NCU_TRAFFIC_MLP1_BYTES = 1_105_950_368  # dram read 1,102,148,000 + write 3,802,368 per launch (ncu capture of this workload, summarised under profiles/)
 
 
 def measured_peaks():

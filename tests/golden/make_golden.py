@@ -1,7 +1,7 @@
 """Generates tests/golden/moe_7m_golden.npz and tests/golden/attn_hd64_golden.npz by running the REFERENCE's own
 CPU model.
 
-Needs the reference sources (default /root/reference; override with GPTOSS_REFERENCE_DIR): the
+Needs the reference sources (directory named by the environment variable GPTOSS_REFERENCE_DIR): the
 reference's run.cpp is compiled by oracle/Makefile into oracle/_ref/libref_cpu.so and its forward()
 (run.cpp:501) is executed on a seeded random-init checkpoint with the gpt-oss-7m dimensions
 (export_model_bin/gpt-oss-7m/config.json).  After each position the state left by the last layer's
