@@ -42,6 +42,7 @@ EXPORTS = [
     "gptoss_moe_sliced_combine", "gptoss_moe_forward_sliced", "gptoss_model_create_ep", "gptoss_model_moe_ctx",
     "gptoss_model_slice", "gptoss_model_step_begin", "gptoss_model_layer_attention", "gptoss_model_layer_moe_push",
     "gptoss_model_layer_moe_combine", "gptoss_model_step_end", "gptoss_comm_rendezvous", "gptoss_moe_gather_rows", "gptoss_moe_forward_host_sliced",
+    "gptoss_moe_route_local", "gptoss_moe_route_finish", "gptoss_moe_sliced_route",
 ]
 
 
@@ -148,6 +149,9 @@ def load() -> C.CDLL:
         "gptoss_comm_rendezvous": ([ctxp, vp], i32),
         "gptoss_moe_gather_rows": ([ctxp, i32, vp, vp], i32),
         "gptoss_moe_forward_host_sliced": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_moe_route_local": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_moe_route_finish": ([ctxp, i32, vp, vp], i32),
+        "gptoss_moe_sliced_route": ([ctxp, i32, i32, vp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -40,15 +40,20 @@ struct gptoss_ctx {
   __nv_bfloat16 *gate_up = nullptr;   // [P,I]
   float *y_pairs = nullptr;           // [P,H]   (inside `sym`)
   // symmetric buffer: same layout on every rank, exported to the peers over CUDA IPC
-  //   [flags: 2*kMaxRanks ints, padded to 1 KiB][delta: T*H fp32][y_pairs: P*H fp32]
+  //   [flags: 4*kMaxRanks ints, padded to 1 KiB][delta: T*H fp32][y_pairs: P*H fp32][topk_w: P fp32][topk_i: P i32]
+  //   [blk_hist: n_route_blocks*E i32]
   uint8_t *sym = nullptr;
-  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0;
+  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0, sym_tw_off = 0, sym_ti_off = 0, sym_hist_off = 0;
+  RouteShare share_self{};            // where routing rows go: this rank alone ...
+  RouteShare share{};                 // ... or every rank of the group (filled when peers are attached)
+  int route_step = 0;                 // number of shared routings so far (flag D carries it)
   int *comm_counter = nullptr;        // last-block counter of the owner combine
   void *peer_base[kMaxRanks] = {};    // opened IPC mappings (nullptr for the own rank / not attached)
   PeerTable peers{};
   bool attached = false;
   int comm_step = 0;
   int gather_step = 0;  // token-sliced form: number of slice gathers so far (flag C carries it)
+  int pending_gather = 0;  // gather step the next route_finish has to wait for (0 = none)
   int *status = nullptr;              // [kStatusWords]
   __nv_bfloat16 *t_stage = nullptr;   // [max_tokens,H]  device copies for the host-buffer entry point
   float *x_stage = nullptr;           // [max_tokens,H]
@@ -209,9 +214,6 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
     if (e == cudaSuccess) e = r;
   };
   A(dev_alloc(&ctx->rb.scores, T * E));
-  A(dev_alloc(&ctx->rb.topk_w, P));
-  A(dev_alloc(&ctx->rb.topk_i, P));
-  A(dev_alloc(&ctx->rb.blk_hist, nblk * E));
   A(dev_alloc(&ctx->rb.blk_base, nblk * E));
   A(dev_alloc(&ctx->rb.offsets, E + 1));
   A(dev_alloc(&ctx->rb.sorted, P));
@@ -220,12 +222,25 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->gate_up, P * I));
   ctx->sym_delta_off = 1024;
   ctx->sym_y_off = ctx->sym_delta_off + ((T * H * sizeof(float) + 1023) & ~(size_t)1023);
-  ctx->sym_bytes = ctx->sym_y_off + P * H * sizeof(float);
+  auto up = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+  ctx->sym_tw_off = up(ctx->sym_y_off + P * H * sizeof(float));
+  ctx->sym_ti_off = up(ctx->sym_tw_off + P * sizeof(float));
+  ctx->sym_hist_off = up(ctx->sym_ti_off + P * sizeof(int));
+  ctx->sym_bytes = up(ctx->sym_hist_off + nblk * E * sizeof(int));
   A(cudaMalloc(reinterpret_cast<void **>(&ctx->sym), ctx->sym_bytes));
   if (e == cudaSuccess) A(cudaMemset(ctx->sym, 0, 1024));
-  if (e == cudaSuccess) ctx->y_pairs = reinterpret_cast<float *>(ctx->sym + ctx->sym_y_off);
-  A(dev_alloc(&ctx->comm_counter, 1));
-  if (e == cudaSuccess) A(cudaMemset(ctx->comm_counter, 0, sizeof(int)));
+  if (e == cudaSuccess) {
+    ctx->y_pairs = reinterpret_cast<float *>(ctx->sym + ctx->sym_y_off);
+    ctx->rb.topk_w = reinterpret_cast<float *>(ctx->sym + ctx->sym_tw_off);
+    ctx->rb.topk_i = reinterpret_cast<int *>(ctx->sym + ctx->sym_ti_off);
+    ctx->rb.blk_hist = reinterpret_cast<int *>(ctx->sym + ctx->sym_hist_off);
+    ctx->share_self.n = 1;
+    ctx->share_self.topk_w[0] = ctx->rb.topk_w;
+    ctx->share_self.topk_i[0] = ctx->rb.topk_i;
+    ctx->share_self.blk_hist[0] = ctx->rb.blk_hist;
+  }
+  A(dev_alloc(&ctx->comm_counter, 2));  // [0] exchange kernels, [1] shared routing
+  if (e == cudaSuccess) A(cudaMemset(ctx->comm_counter, 0, 2 * sizeof(int)));
   A(dev_alloc(&ctx->status, kStatusWords));
   A(dev_alloc(&ctx->t_stage, T * H));
   A(dev_alloc(&ctx->x_stage, T * H));
@@ -250,9 +265,6 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaDeviceSynchronize();
   for (auto &w : ctx->layers) free_layer(w);
   cudaFree(ctx->rb.scores);
-  cudaFree(ctx->rb.topk_w);
-  cudaFree(ctx->rb.topk_i);
-  cudaFree(ctx->rb.blk_hist);
   cudaFree(ctx->rb.blk_base);
   cudaFree(ctx->rb.offsets);
   cudaFree(ctx->rb.sorted);
@@ -402,6 +414,48 @@ int gptoss_download_layer(gptoss_ctx *ctx, int layer, float *router_w, float *ro
 }
 
 // ---- stages ---------------------------------------------------------------------------------------------
+static int check_attached(gptoss_ctx *ctx);
+
+// Router GEMM + top-k + softmax + block histograms for rows [first, first + n) of a batch of T tokens (rows = their
+// bf16 activations, 16-byte aligned), results stored to every rank of `sh`.
+static int route_rows(gptoss_ctx *ctx, int layer, int T, const void *rows, int first, int n, const RouteShare &sh,
+                      cudaStream_t s) {
+  const LayerWeights &w = ctx->layers[layer];
+  const int k_blocks = (ctx->d.H + kBlockK - 1) / kBlockK;
+  if (n > 0) {
+    if (reinterpret_cast<uintptr_t>(rows) & 15u) return ctx->fail(GPTOSS_ERR_BAD_ARG, "activations must be 16-byte aligned");
+    if (ctx->map_t_base != rows || ctx->map_t_rows != n) {
+      CK(encode_map_2d(&ctx->map_t, rows, ctx->d.H, n, 128));
+      ctx->map_t_base = rows;
+      ctx->map_t_rows = n;
+    }
+    RouterArgs ra;
+    memset(&ra, 0, sizeof ra);
+    ra.map_t = ctx->map_t;
+    ra.map_wr = w.map_wr;
+    ra.partials = ctx->router_partials;
+    ra.T = n;
+    ra.split_T = T;  // split K as a rank that routes the whole batch would: same bits whoever routes a token
+    ra.E = ctx->d.E;
+    ra.n_cols = (ctx->d.E + 15) & ~15;
+    ra.k_blocks = k_blocks;
+    ra.status = ctx->status;
+    CK(launch_router_gemm(ra, kRouterMaxSplits, s));
+  }
+  CK(launch_router_topk(ctx->router_partials, router_splits_for(T, k_blocks, kRouterMaxSplits), w.router_b, n, first, ctx->d,
+                        ctx->rb, sh, s));
+  return GPTOSS_OK;
+}
+
+// Counting sort of the whole batch from the routing rows present in this rank's buffers + gather of the token rows
+// of this rank's experts.
+static int route_group(gptoss_ctx *ctx, int T, const void *t_full, cudaStream_t s) {
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, s));
+  CK(launch_scatter_gather(static_cast<const __nv_bfloat16 *>(t_full), ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base,
+                           ctx->rb.sorted, ctx->x_packed, s));
+  return GPTOSS_OK;
+}
+
 int gptoss_moe_route(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream) {
   int rc = check_layer(ctx, layer, true);
   if (rc) return rc;
@@ -411,31 +465,38 @@ int gptoss_moe_route(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, 
   ctx->cur_T = T;
   if (T == 0) return GPTOSS_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const LayerWeights &w = ctx->layers[layer];
-  const __nv_bfloat16 *t = static_cast<const __nv_bfloat16 *>(t_dev_bf16);
-  if (reinterpret_cast<uintptr_t>(t_dev_bf16) & 15u)
-    return ctx->fail(GPTOSS_ERR_BAD_ARG, "activations must be 16-byte aligned");
-  if (ctx->map_t_base != t_dev_bf16 || ctx->map_t_rows != T) {
-    CK(encode_map_2d(&ctx->map_t, t_dev_bf16, ctx->d.H, T, 128));
-    ctx->map_t_base = t_dev_bf16;
-    ctx->map_t_rows = T;
-  }
-  RouterArgs ra;
-  memset(&ra, 0, sizeof ra);
-  ra.map_t = ctx->map_t;
-  ra.map_wr = w.map_wr;
-  ra.partials = ctx->router_partials;
-  ra.T = T;
-  ra.E = ctx->d.E;
-  ra.n_cols = (ctx->d.E + 15) & ~15;
-  ra.k_blocks = (ctx->d.H + kBlockK - 1) / kBlockK;
-  ra.status = ctx->status;
-  CK(launch_router_gemm(ra, kRouterMaxSplits, s));
-  CK(launch_router_topk(ctx->router_partials, router_splits_for(T, ra.k_blocks, kRouterMaxSplits), w.router_b, T,
-                        ctx->d, ctx->rb, s));
-  CK(launch_expert_scan(ctx->rb, T, ctx->d, s));
-  CK(launch_scatter_gather(t, ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base, ctx->rb.sorted, ctx->x_packed, s));
-  return GPTOSS_OK;
+  if ((rc = route_rows(ctx, layer, T, t_dev_bf16, 0, T, ctx->share_self, s))) return rc;
+  return route_group(ctx, T, t_dev_bf16, s);
+}
+
+// Shared routing: this rank routes only its token slice and stores the rows to every rank (flag D); route_finish
+// waits for every rank's rows (and, in the token-sliced form, for the gathered activations) and groups the batch.
+int gptoss_moe_route_local(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  CK(cudaSetDevice(ctx->device));
+  ctx->cur_T = T;
+  if (T == 0) return GPTOSS_OK;
+  const uint8_t *t = static_cast<const uint8_t *>(t_dev_bf16 ? t_dev_bf16 : ctx->sym + ctx->sym_delta_off);
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(ctx, T, &first, &n);
+  ctx->share.step = ++ctx->route_step;
+  return route_rows(ctx, layer, T, t + (size_t)first * ctx->d.H * 2, first, n, ctx->share, static_cast<cudaStream_t>(stream));
+}
+
+int gptoss_moe_route_finish(gptoss_ctx *ctx, int T, const void *t_dev_bf16, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (T != ctx->cur_T || ctx->route_step == 0) return ctx->fail(GPTOSS_ERR_STATE, "route_finish without a matching route_local");
+  CK(cudaSetDevice(ctx->device));
+  if (T == 0) return GPTOSS_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CK(launch_wait_flags(ctx->peers, ctx->pending_gather, ctx->route_step, ctx->status, s));
+  ctx->pending_gather = 0;
+  return route_group(ctx, T, t_dev_bf16 ? t_dev_bf16 : ctx->sym + ctx->sym_delta_off, s);
 }
 
 int gptoss_moe_mlp1_swiglu(gptoss_ctx *ctx, int layer, void *stream) {
@@ -486,7 +547,7 @@ int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) {
   const int step = ++ctx->comm_step;
   GemmArgs a = gemm_args(ctx, ctx->layers[layer], false);
   a.n_owners = ctx->world;
-  a.slice_tokens = (ctx->cur_T + ctx->world - 1) / ctx->world;
+  a.slice_tokens = slice_rows(ctx->cur_T, ctx->world);
   for (int r = 0; r < ctx->world; ++r) {
     a.y_owner[r] = ctx->peers.y[r];
     a.signal_flags[r] = ctx->peers.flags[r] + ctx->rank;  // flag A of this rank on rank r
@@ -521,7 +582,7 @@ int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream) {
 // ---- token-sliced form: every rank keeps only its slice of the residual stream ------------------------------
 int gptoss_moe_slice_bounds(const gptoss_ctx *ctx, int T, int *first, int *count) {
   if (!ctx || T < 0) return GPTOSS_ERR_BAD_ARG;
-  const int slice = (T + ctx->world - 1) / ctx->world;
+  const int slice = slice_rows(T, ctx->world);
   int b0 = ctx->rank * slice, n = T - b0;
   n = n < 0 ? 0 : (n > slice ? slice : n);
   if (n == 0) b0 = T;
@@ -540,7 +601,7 @@ int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const fl
   gptoss_moe_slice_bounds(ctx, T, &first, &n);  // a rank without tokens still takes part (it raises its flag)
   if ((n > 0 && !x_slice_dev) || !norm_w_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice or norm-weight pointer");
   CK(cudaSetDevice(ctx->device));
-  const int step = ++ctx->gather_step;
+  const int step = ctx->pending_gather = ++ctx->gather_step;
   CK(launch_slice_norm_gather(ctx->peers, T, ctx->d.H, x_slice_dev, add_dev, norm_w_dev, step, ctx->comm_counter,
                               static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
@@ -556,7 +617,7 @@ int gptoss_moe_gather_rows(gptoss_ctx *ctx, int T, const void *t_slice_dev_bf16,
   if (n > 0 && !t_slice_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
   if (n > 0 && (reinterpret_cast<uintptr_t>(t_slice_dev_bf16) & 15)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "slice must be 16-byte aligned");
   CK(cudaSetDevice(ctx->device));
-  const int step = ++ctx->gather_step;
+  const int step = ctx->pending_gather = ++ctx->gather_step;
   CK(launch_slice_copy_gather(ctx->peers, T, ctx->d.H, t_slice_dev_bf16, step, ctx->comm_counter, ctx->sm_count,
                               static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
@@ -570,16 +631,15 @@ int gptoss_comm_rendezvous(gptoss_ctx *ctx, void *stream) {
   return GPTOSS_OK;
 }
 
+int gptoss_moe_sliced_route(gptoss_ctx *ctx, int layer, int T, void *stream) {
+  if (ctx && ctx->gather_step == 0) return ctx->fail(GPTOSS_ERR_STATE, "sliced route before any gather");
+  return gptoss_moe_route_local(ctx, layer, T, nullptr, stream);  // this rank's rows of its own gathered buffer
+}
+
 int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream) {
-  int rc = check_attached(ctx);
+  int rc = gptoss_moe_route_finish(ctx, T, nullptr, stream);
   if (rc) return rc;
-  if ((rc = check_T(ctx, T))) return rc;
   if (T == 0) return GPTOSS_OK;
-  if (ctx->gather_step == 0) return ctx->fail(GPTOSS_ERR_STATE, "sliced push before any gather_slice");
-  CK(cudaSetDevice(ctx->device));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  CK(launch_wait_gathered(ctx->peers, ctx->gather_step, ctx->status, s));
-  if ((rc = gptoss_moe_route(ctx, layer, T, ctx->sym + ctx->sym_delta_off, stream))) return rc;
   if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
   return gptoss_moe_push_to_owners(ctx, layer, stream);
 }
@@ -598,8 +658,9 @@ int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream)
 }
 
 int gptoss_moe_forward_sliced(gptoss_ctx *ctx, int layer, int T, float *x_slice_dev, void *stream) {
-  int rc = gptoss_moe_sliced_push(ctx, layer, T, stream);
+  int rc = gptoss_moe_sliced_route(ctx, layer, T, stream);
   if (rc) return rc;
+  if ((rc = gptoss_moe_sliced_push(ctx, layer, T, stream))) return rc;
   return gptoss_moe_sliced_combine(ctx, x_slice_dev, stream);
 }
 
@@ -621,8 +682,10 @@ int gptoss_moe_forward(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16
   // expert-parallel with peer memory: push rows to their owners from the down-GEMM epilogue, owners
   // combine their token slice and deliver it to every rank, every rank adds it to its residual
   int rc;
-  if ((rc = gptoss_moe_route(ctx, layer, T, t_dev_bf16, stream))) return rc;
+  if (!t_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null activation pointer");
+  if ((rc = gptoss_moe_route_local(ctx, layer, T, t_dev_bf16, stream))) return rc;  // each rank routes its token slice
   if (T == 0) return GPTOSS_OK;
+  if ((rc = gptoss_moe_route_finish(ctx, T, t_dev_bf16, stream))) return rc;
   if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
   if ((rc = gptoss_moe_push_to_owners(ctx, layer, stream))) return rc;
   if ((rc = gptoss_moe_owner_combine(ctx, stream))) return rc;
@@ -701,6 +764,7 @@ int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint
   if (n) CK(cudaMemcpyAsync(ctx->x_stage, x_host_slice, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
   CK(cudaEventRecord(ctx->ev_x, ctx->s_copy));
   if ((rc = gptoss_moe_gather_rows(ctx, T, ctx->t_stage, ctx->s_main))) return rc;
+  if ((rc = gptoss_moe_sliced_route(ctx, layer, T, ctx->s_main))) return rc;
   if ((rc = gptoss_moe_sliced_push(ctx, layer, T, ctx->s_main))) return rc;
   CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
   if ((rc = gptoss_moe_sliced_combine(ctx, ctx->x_stage, ctx->s_main))) return rc;
@@ -712,6 +776,17 @@ int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint
 }
 
 // ---- peer memory ----------------------------------------------------------------------------------------------
+// rank r's routing buffers and this rank's "routed" flag on rank r, inside r's symmetric buffer at `base`
+static void set_share(gptoss_ctx *ctx, int r, uint8_t *base) {
+  RouteShare &sh = ctx->share;
+  sh.n = ctx->world;
+  sh.counter = ctx->comm_counter + 1;
+  sh.topk_w[r] = reinterpret_cast<float *>(base + ctx->sym_tw_off);
+  sh.topk_i[r] = reinterpret_cast<int *>(base + ctx->sym_ti_off);
+  sh.blk_hist[r] = reinterpret_cast<int *>(base + ctx->sym_hist_off);
+  sh.flags[r] = reinterpret_cast<int *>(base) + 3 * kMaxRanks + ctx->rank;
+}
+
 int gptoss_comm_export(gptoss_ctx *ctx, void *handle_out) {
   if (!ctx) return GPTOSS_ERR_BAD_ARG;
   if (!handle_out) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null handle buffer");
@@ -744,6 +819,7 @@ int gptoss_comm_attach(gptoss_ctx *ctx, const void *handles) {
     ctx->peers.flags[r] = reinterpret_cast<int *>(base);
     ctx->peers.delta[r] = reinterpret_cast<float *>(base + ctx->sym_delta_off);
     ctx->peers.y[r] = reinterpret_cast<float *>(base + ctx->sym_y_off);
+    set_share(ctx, r, base);
   }
   ctx->attached = true;
   return GPTOSS_OK;
@@ -769,6 +845,7 @@ int gptoss_comm_attach_local(gptoss_ctx *ctx, gptoss_ctx *const *all) {
     ctx->peers.flags[r] = reinterpret_cast<int *>(p->sym);
     ctx->peers.delta[r] = reinterpret_cast<float *>(p->sym + p->sym_delta_off);
     ctx->peers.y[r] = reinterpret_cast<float *>(p->sym + p->sym_y_off);
+    set_share(ctx, r, p->sym);
   }
   ctx->attached = true;
   return GPTOSS_OK;

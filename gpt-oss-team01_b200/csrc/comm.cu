@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) combine_owner_kernel(PeerTable pt, int T,
                                                             int *status, int *counter) {
   pdl_wait();
   wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2100);
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
   const int h8 = H >> 3;  // 8 elements per thread: two float4 loads per slot, one 16-byte (bf16) or two (fp32) stores per rank
   const size_t total = (size_t)max(0, b1 - b0) * h8;
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, in
                                                                 int step, int *counter) {
   __shared__ double part[8];
   pdl_wait();
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const int b0 = pt.rank * slice, n_rows = max(0, min(T, b0 + slice) - b0);
   const int i_row = blockIdx.x;
   if (i_row < n_rows) {
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(256) slice_norm_gather_kernel(PeerTable pt, in
 __global__ void __launch_bounds__(256) slice_copy_gather_kernel(PeerTable pt, int T, int H, const uint4 *__restrict__ t_slice,
                                                                 int step, int *counter) {
   pdl_wait();
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const int b0 = pt.rank * slice, n_rows = max(0, min(T, b0 + slice) - b0);
   const size_t total = (size_t)n_rows * H / 8, first = (size_t)b0 * H / 8;  // H % 8 == 0
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -176,11 +176,13 @@ __global__ void __launch_bounds__(256) slice_copy_gather_kernel(PeerTable pt, in
   signal_all_ranks(pt, 2, step, counter);
 }
 
-// Token-sliced form, consumer side: returns once every rank's slice of the gathered activations has arrived.
-__global__ void wait_gathered_kernel(PeerTable pt, int step, int *status) {
+// Returns once every rank has raised flag C to gather_step (its slice of the gathered activations has arrived) and
+// flag D to route_step (the routing of its token slice has arrived); a step of 0 skips that flag.
+__global__ void wait_flags_kernel(PeerTable pt, int gather_step, int route_step, int *status) {
   pdl_wait();
   pdl_launch_dependents();
-  wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2300);
+  if (gather_step > 0) wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, gather_step, pt.timeout_ns, status, 0x2300);
+  if (route_step > 0) wait_all_ranks(pt.flags[pt.rank] + 3 * kMaxRanks, pt.world, route_step, pt.timeout_ns, status, 0x2600);
 }
 
 // Device-side rendezvous of the ranks (no data): raises this rank's flag C everywhere, then waits for everyone's.
@@ -200,7 +202,7 @@ __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, 
                                                                   float *__restrict__ x_slice, int *status) {
   pdl_wait();
   wait_all_ranks(pt.flags[pt.rank], pt.world, step, pt.timeout_ns, status, 0x2400);
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const int b0 = pt.rank * slice, b1 = min(T, b0 + slice);
   const int h4 = H >> 2;
   const size_t total = (size_t)max(0, b1 - b0) * h4;
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, 
 
 cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
                                  int *counter, int sm_count, cudaStream_t s) {
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const size_t total = (size_t)slice * (H >> 3);
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 4) blocks = sm_count * 4;  // few, long-lived blocks: each ends with a system-scope fence
@@ -244,7 +246,7 @@ cudaError_t launch_add_delta(const PeerTable &pt, bool bf16_wire, int T, int H, 
 
 cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x_slice, const float *add, const float *w,
                                      int step, int *counter, cudaStream_t s) {
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   int rows = T - pt.rank * slice;
   rows = rows < 0 ? 0 : (rows > slice ? slice : rows);
   return launch_chain(slice_norm_gather_kernel, dim3(rows > 0 ? rows : 1), dim3(256), 0, s, pt, T, H, x_slice, add, w, step,
@@ -253,7 +255,7 @@ cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x
 
 cudaError_t launch_slice_copy_gather(const PeerTable &pt, int T, int H, const void *t_slice, int step, int *counter,
                                      int sm_count, cudaStream_t s) {
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const size_t total = (size_t)slice * H / 8;
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 4) blocks = sm_count * 4;
@@ -262,8 +264,8 @@ cudaError_t launch_slice_copy_gather(const PeerTable &pt, int T, int H, const vo
                       counter);
 }
 
-cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s) {
-  return launch_chain(wait_gathered_kernel, dim3(1), dim3(32), 0, s, pt, step, status);
+cudaError_t launch_wait_flags(const PeerTable &pt, int gather_step, int route_step, int *status, cudaStream_t s) {
+  return launch_chain(wait_flags_kernel, dim3(1), dim3(32), 0, s, pt, gather_step, route_step, status);
 }
 
 cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaStream_t s) {
@@ -272,7 +274,7 @@ cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaSt
 
 cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
                                        int sm_count, cudaStream_t s) {
-  const int slice = (T + pt.world - 1) / pt.world;
+  const int slice = slice_rows(T, pt.world);
   const size_t total = (size_t)slice * (H >> 2);
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 16) blocks = sm_count * 16;

@@ -37,6 +37,27 @@ struct RouteBuffers {
   int *tb_prefix;       // [E_local+1]   cumulative count of token blocks (kMaxTileTokens rows) of local experts
 };
 
+// Tokens per owner slice of a batch of T tokens over `world` ranks: contiguous slices of equal size, a multiple of the
+// routing block so that a block of the per-block expert histogram never straddles two ranks.
+__host__ __device__ inline int slice_rows(int T, int world) {
+  const int per = (T + world - 1) / world;
+  return (per + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock * kTokensPerRouteBlock;
+}
+
+// Where the routing result of a token goes: the routing buffers of every rank of the group (this rank's alone when
+// the context has no peers).  Every rank routes its own token slice and stores the rows to all; the last block raises
+// this rank's "routed" flag (flags[r], value step) on every rank when step > 0.
+constexpr int kMaxShareRanks = 16;
+struct RouteShare {
+  int n;         // ranks to store to
+  int step;      // 0 = no flag
+  int *counter;  // blocks finished so far (left at 0)
+  float *topk_w[kMaxShareRanks];
+  int *topk_i[kMaxShareRanks];
+  int *blk_hist[kMaxShareRanks];
+  int *flags[kMaxShareRanks];
+};
+
 struct Dims {
   int H, I, E, k;
   int e_begin, e_end;  // local experts

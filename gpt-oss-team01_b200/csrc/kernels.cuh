@@ -35,8 +35,9 @@ cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
 }
 
 // routing.cu
-cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, const Dims &d,
-                               const RouteBuffers &rb, cudaStream_t s);
+// T rows of partial scores (local row b = token first_token + b of the batch); results to every rank of `share`
+cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, int first_token, const Dims &d,
+                               const RouteBuffers &rb, const RouteShare &share, cudaStream_t s);
 cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
                                 cudaStream_t s);
 cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s);
@@ -55,8 +56,9 @@ struct PeerTable {
   float *y[kMaxRanks];      // every rank's y_pairs  [P,H] fp32 (index = own rank: local memory)
   float *delta[kMaxRanks];  // every rank's delta    [T,H] fp32, or bf16 in the same storage (bf16 wire); in the token-sliced
                             //                       form the same storage holds the gathered activations [T,H] bf16
-  int *flags[kMaxRanks];    // every rank's flags    [3][kMaxRanks]: A = "rank r pushed", B = "owner r delivered",
-                            //                       C = "rank r stored its slice of the gathered activations"
+  int *flags[kMaxRanks];    // every rank's flags    [4][kMaxRanks]: A = "rank r pushed", B = "owner r delivered",
+                            //                       C = "rank r stored its slice of the gathered activations",
+                            //                       D = "rank r stored the routing of its token slice"
 };
 cudaError_t launch_combine_owner(const PeerTable &pt, bool bf16_wire, int T, int H, int k, int step, int *status,
                                  int *counter, int sm_count, cudaStream_t s);
@@ -67,7 +69,8 @@ cudaError_t launch_slice_norm_gather(const PeerTable &pt, int T, int H, float *x
                                      int step, int *counter, cudaStream_t s);
 cudaError_t launch_slice_copy_gather(const PeerTable &pt, int T, int H, const void *t_slice, int step, int *counter,
                                      int sm_count, cudaStream_t s);
-cudaError_t launch_wait_gathered(const PeerTable &pt, int step, int *status, cudaStream_t s);
+// waits for flag C >= gather_step and flag D >= route_step of every rank (a step of 0 skips that flag)
+cudaError_t launch_wait_flags(const PeerTable &pt, int gather_step, int route_step, int *status, cudaStream_t s);
 cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaStream_t s);
 cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
                                        int sm_count, cudaStream_t s);
@@ -77,6 +80,8 @@ struct RouterArgs {
   CUtensorMap map_t;   // activations t [T,H]: 2-D (k, token), box {64,128}
   CUtensorMap map_wr;  // router weight [E,H]: 2-D (k, expert), box {64, n_cols}
   float *partials;     // [splits][T][E]
+  int split_T;         // batch size the split-K factor is derived from (0 = T): a rank that routes only its slice
+                       // of a batch must split K like a rank that routes all of it, or the scores' bits differ
   int T, E;
   int n_cols;          // E rounded up to a multiple of 16 (UMMA N)
   int k_blocks;        // ceil(H / 64)

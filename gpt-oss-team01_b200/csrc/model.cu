@@ -212,7 +212,7 @@ int gptoss_model_create_ep(const gptoss_model_config *cfg, int device, int rank,
   m->max_batch = max_batch;
   m->rank = rank;
   m->world = world;
-  m->max_local = (max_batch + world - 1) / world;
+  m->max_local = slice_rows(max_batch, world) < max_batch ? slice_rows(max_batch, world) : max_batch;
   m->S = max_seq;
   gptoss_moe_dims d{c.hidden_dim, c.intermediate_dim, c.n_experts, c.experts_per_token, c.n_layers, c.swiglu_limit};
   int rc = gptoss_ctx_create(&d, device, rank, world, max_batch, GPTOSS_WIRE_F32, &m->moe);
@@ -452,8 +452,10 @@ int gptoss_model_layer_attention(gptoss_model *m, int layer) {
   }
   if (m->world == 1) {
     MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
-  } else if ((rc = gptoss_moe_gather_slice(m->moe, m->step_B, m->x, m->proj, m->mlp_norm + l * H, s))) {
-    return m->fail(rc, gptoss_last_error(m->moe));
+  } else {  // the normalised rows go to every rank, then this rank routes them and shares the routing rows
+    if ((rc = gptoss_moe_gather_slice(m->moe, m->step_B, m->x, m->proj, m->mlp_norm + l * H, s)) ||
+        (rc = gptoss_moe_sliced_route(m->moe, layer, m->step_B, s)))
+      return m->fail(rc, gptoss_last_error(m->moe));
   }
   return GPTOSS_OK;
 }

@@ -132,12 +132,8 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
 // Fills the launch geometry of `a` (splits, stages, shared memory) for T tokens and launches.
 cudaError_t launch_router_gemm(RouterArgs a, int max_splits, cudaStream_t s) {
   const int n_tiles = (a.T + 127) / 128;
-  int splits = 96 / n_tiles;
-  if (splits < 1) splits = 1;
-  if (splits > max_splits) splits = max_splits;
-  if (splits > a.k_blocks) splits = a.k_blocks;
+  const int splits = router_splits_for(a.split_T > 0 ? a.split_T : a.T, a.k_blocks, max_splits);
   a.k_blocks_per_split = (a.k_blocks + splits - 1) / splits;
-  splits = (a.k_blocks + a.k_blocks_per_split - 1) / a.k_blocks_per_split;
   a.stage_bytes = kRouterATile + ((a.n_cols * kBlockK * 2 + 1023) & ~1023);
   a.stages = kRouterSmemBudget / a.stage_bytes;
   if (a.stages > kRouterMaxStages) a.stages = kRouterMaxStages;

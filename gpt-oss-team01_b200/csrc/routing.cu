@@ -109,10 +109,12 @@ __device__ __forceinline__ void warp_topk_softmax(float (&val)[SLOTS], int E, in
 
 // ---- split-K reduction of the router GEMM + bias + top-k + softmax + per-block expert histogram ---------
 // One warp per token.  scores[b,e] = (partial[0][b,e] + partial[1][b,e] + ...) + br[e], summed in split order.
+// Local row b is token first + b of the batch (first is a multiple of the block's 8 tokens); the gate weights, expert
+// ids and the block's histogram go to the routing buffers of every rank in `sh`.
 template <int GROUPS>
 __global__ void __launch_bounds__(256) router_topk_kernel(const float *__restrict__ partials, int n_splits,
-                                                          const float *__restrict__ br, int T, Dims d,
-                                                          RouteBuffers rb) {
+                                                          const float *__restrict__ br, int T, int first, Dims d,
+                                                          RouteBuffers rb, RouteShare sh) {
   __shared__ int hist[kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * kTokensPerRouteBlock + warp;
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float *__restric
         s = partials[(size_t)b * d.E + eg];
         for (int sp = 1; sp < n_splits; ++sp) s += partials[((size_t)sp * T + b) * d.E + eg];
         s += br[eg];
-        rb.scores[(size_t)b * d.E + eg] = s;
+        rb.scores[(size_t)(first + b) * d.E + eg] = s;
       }
       score[g] = s;
     }
@@ -138,13 +140,32 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float *__restric
     int id;
     warp_topk_softmax<GROUPS>(score, d.E, d.k, lane, w, id);
     if (lane < d.k) {
-      rb.topk_w[(size_t)b * d.k + lane] = w;
-      rb.topk_i[(size_t)b * d.k + lane] = id;
+      const size_t o = (size_t)(first + b) * d.k + lane;
+      for (int r = 0; r < sh.n; ++r) {
+        sh.topk_w[r][o] = w;
+        sh.topk_i[r][o] = id;
+      }
       atomicAdd(&hist[id], 1);
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < d.E; e += blockDim.x) rb.blk_hist[(size_t)blockIdx.x * d.E + e] = hist[e];
+  if (blockIdx.x * kTokensPerRouteBlock < T) {
+    const size_t blk = (size_t)(first / kTokensPerRouteBlock + blockIdx.x) * d.E;
+    for (int e = threadIdx.x; e < d.E; e += blockDim.x)
+      for (int r = 0; r < sh.n; ++r) sh.blk_hist[r][blk + e] = hist[e];
+  }
+  if (sh.step > 0) {  // stores ordered before the count by the barrier plus one system-scope fence (cumulative)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int *>(sh.counter), 1u);
+      if (prev == gridDim.x - 1) {
+        *sh.counter = 0;
+        __threadfence_system();
+        for (int r = 0; r < sh.n; ++r) st_relaxed_sys(sh.flags[r], sh.step);
+      }
+    }
+  }
 }
 
 // ---- stand-alone top-k + softmax on a score matrix ---------------------------------------------------
@@ -337,14 +358,15 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
 // ---- launchers -------------------------------------------------------------------------------------------
 static inline int route_blocks(int T) { return (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock; }
 
-cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, const Dims &d,
-                               const RouteBuffers &rb, cudaStream_t s) {
+cudaError_t launch_router_topk(const float *partials, int n_splits, const float *br, int T, int first_token, const Dims &d,
+                               const RouteBuffers &rb, const RouteShare &share, cudaStream_t s) {
   const int groups = (d.E + 31) / 32;
-  const dim3 grid(route_blocks(T)), block(256);
+  const int nb = route_blocks(T);
+  const dim3 grid(nb > 0 ? nb : 1), block(256);  // a rank without tokens still raises its flag
   cudaError_t err = cudaSuccess;
 #define GPTOSS_ROUTER_CASE(G)                                                            \
   case G:                                                                                \
-    err = launch_chain(router_topk_kernel<G>, grid, block, 0, s, partials, n_splits, br, T, d, rb); \
+    err = launch_chain(router_topk_kernel<G>, grid, block, 0, s, partials, n_splits, br, T, first_token, d, rb, share); \
     break;
   switch (groups) {
     GPTOSS_ROUTER_CASE(1)

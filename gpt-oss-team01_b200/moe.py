@@ -36,8 +36,9 @@ def _ptr(t):
 
 def slice_bounds(rank: int, world: int, n_tokens: int):
     """(first token, token count) of the slice rank ``rank`` owns in a batch of ``n_tokens``: contiguous slices of
-    ceil(n_tokens / world) tokens, the last ones shorter or empty (same rule as gptoss_moe_slice_bounds)."""
-    per = (n_tokens + world - 1) // world
+    ceil(n_tokens / world) tokens rounded up to a multiple of 8, the last ones shorter or empty (same rule as
+    gptoss_moe_slice_bounds)."""
+    per = ((n_tokens + world - 1) // world + 7) // 8 * 8  # a multiple of the routing block of 8 tokens
     first = rank * per
     count = max(0, min(per, n_tokens - first))
     return (first if count else n_tokens), count
@@ -189,6 +190,18 @@ class MoEBlock:
         """this rank's (already normalised) bf16 rows copied into every rank's gathered activations."""
         self._check(self.lib.gptoss_moe_gather_rows(self._ctx, n_tokens, _ptr(t_slice) if t_slice is not None else None,
                                                     _stream(stream)))
+
+    def sliced_route(self, layer, n_tokens, stream=None):
+        """routes this rank's own rows of its gathered buffer, rows stored to every rank (no waiting)"""
+        self._check(self.lib.gptoss_moe_sliced_route(self._ctx, layer, n_tokens, _stream(stream)))
+
+    def route_local(self, layer, t, stream=None):
+        """replicated activations t [T,H]: this rank routes its token slice and stores the rows to every rank"""
+        self._check(self.lib.gptoss_moe_route_local(self._ctx, layer, t.shape[0], _ptr(t), _stream(stream)))
+
+    def route_finish(self, t, stream=None):
+        """waits for every rank's routing rows, then counting sort + gather of the rows of this rank's experts"""
+        self._check(self.lib.gptoss_moe_route_finish(self._ctx, t.shape[0], _ptr(t), _stream(stream)))
 
     def sliced_push(self, layer, n_tokens, stream=None):
         self._check(self.lib.gptoss_moe_sliced_push(self._ctx, layer, n_tokens, _stream(stream)))

@@ -133,13 +133,25 @@ int gptoss_comm_set_timeout_ms(gptoss_ctx *ctx, int ms);
  *   owner_combine  : waits for the "pushed" flags of all ranks, sums the k slots of this rank's token
  *                    slice in slot order, stores the sums to every rank, raises "delivered" everywhere;
  *   add_delta      : waits for the "delivered" flags of all ranks, x += delivered sums. */
+/* Shared routing (what gptoss_moe_forward runs in front of those stages once peers are attached): the activations are
+ * replicated, so instead of every rank routing every token (the reference: router_gemm_v2 + topk_softmax_batched on
+ * the whole batch on all ranks, getp-csrc/src/model.cpp:300-340)
+ *   route_local  : this rank routes only ITS token slice (router GEMM, top-k, softmax, block histograms) and stores the
+ *                  rows into the routing buffers of every rank, then raises its "routed" flag everywhere;
+ *   route_finish : waits for the "routed" flags of all ranks, then counting sort of the whole batch and gather of the
+ *                  token rows of this rank's experts (moe_build_offsets_hip + moe_pack_inputs_hip).
+ * t_dev_bf16: the replicated activations [T,H] (NULL in the token-sliced form: the context's gathered buffer).  The
+ * split-K factor of the router GEMM is derived from T, not from the slice, so a token's scores have the same bits
+ * whoever routes it.  Slices are contiguous and a multiple of 8 tokens (gptoss_moe_slice_bounds). */
+int gptoss_moe_route_local(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream);
+int gptoss_moe_route_finish(gptoss_ctx *ctx, int T, const void *t_dev_bf16, void *stream);
 int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream);
 int gptoss_moe_owner_combine(gptoss_ctx *ctx, void *stream);
 int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream);
 
 /* ---- token-sliced form of the expert-parallel block ------------------------------------------------
  * For callers that keep only a slice of the residual stream on each GPU (data-parallel attention in front
- * of the expert-parallel block): rank r owns tokens [r*ceil(T/world), ...).  It replaces, together,
+ * of the expert-parallel block): rank r owns tokens [r*S, (r+1)*S) with S = ceil(T/world) rounded up to a multiple of 8.  It replaces, together,
  * ring_all_reduce_tb2_quantize_fp8 + residual_rmsnorm (the all-reduce that re-creates the replicated
  * activations, getp-csrc/src/parallelism.cpp:1195, layer_hip_batch.cpp:95) and the second half of
  * ring_reduce_agg_quantize_fp8 (the all-gather of the reduced sums, parallelism.cpp:1605-1670): the owner
@@ -147,10 +159,12 @@ int gptoss_moe_add_delta(gptoss_ctx *ctx, float *x_dev, void *stream);
  *   slice_bounds   : first token and token count of this rank's slice for a batch of T tokens;
  *   gather_slice   : x_slice += add (if add != NULL); bf16(RMSNorm(x_slice) * norm_w) stored into the gathered
  *                    activation buffer [T,H] of EVERY rank; raises this rank's "gathered" flag everywhere;
- *   sliced_push    : waits for the "gathered" flags of all ranks, routes the T gathered tokens, gate/up GEMM +
- *                    SwiGLU, down GEMM pushing to the owners, raises "pushed";
+ *   sliced_route   : routes this rank's own rows (already in its gathered buffer) and stores the routing rows to
+ *                    every rank (route_local); does not wait for anybody;
+ *   sliced_push    : waits for the "gathered" and "routed" flags of all ranks, groups the T tokens by expert, gate/up
+ *                    GEMM + SwiGLU, down GEMM pushing to the owners, raises "pushed";
  *   sliced_combine : waits for "pushed" of all ranks; x_slice += slot-ordered sum of this rank's tokens;
- *   forward_sliced : sliced_push + sliced_combine.
+ *   forward_sliced : sliced_route + sliced_push + sliced_combine.
  * x_slice_dev, add_dev: fp32 [slice count, H] on the device; norm_w_dev: fp32 [H].  Every rank must make the
  * same sequence of these calls; they must not be interleaved with the replicated form within one step. */
 int gptoss_moe_slice_bounds(const gptoss_ctx *ctx, int T, int *first, int *count);
@@ -164,6 +178,7 @@ int gptoss_moe_gather_slice(gptoss_ctx *ctx, int T, float *x_slice_dev, const fl
 /* gather_rows: like gather_slice for rows that are already normalised: copies this rank's bf16 rows
  * [slice count, H] (device, 16-byte aligned) into the gathered activations of every rank and raises "gathered". */
 int gptoss_moe_gather_rows(gptoss_ctx *ctx, int T, const void *t_slice_dev_bf16, void *stream);
+int gptoss_moe_sliced_route(gptoss_ctx *ctx, int layer, int T, void *stream);
 int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream);
 int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream);
 int gptoss_moe_forward_sliced(gptoss_ctx *ctx, int layer, int T, float *x_slice_dev, void *stream);

@@ -95,7 +95,7 @@ def _owner_worker(rank, world, port, out_path):
     bounds = [moe.slice_bounds(r, world, T) for r in range(world)]
     assert sum(n for _, n in bounds) == T and all(bounds[r][0] + bounds[r][1] == bounds[r + 1][0] or bounds[r + 1][1] == 0
                                                   for r in range(world - 1))
-    per = (T + world - 1) // world
+    per = max(n for _, n in bounds)  # slice size: ceil(T / world) rounded up to the routing block of 8 tokens
     send = [torch.zeros(per * k, H) for _ in range(world)]
     masks = [torch.zeros(per * k, dtype=torch.bool) for _ in range(world)]
     for r, (first, n) in enumerate(bounds):

@@ -53,6 +53,48 @@ def test_emulated_ranks_match_single_context_bitwise(world, T):
         b.close()
 
 
+@pytest.mark.parametrize("world,T", [(2, 300), (4, 203), (8, 64)])
+def test_shared_routing_matches_single_context_bitwise(world, T):
+    """Replicated activations, routing shared: every rank routes only its token slice (router GEMM with the split-K
+    factor of the whole batch, top-k, block histograms) and stores the rows to all ranks; after that every rank must
+    hold the routing of the single-context block bit for bit, and the block output must be identical."""
+    from gptoss_b200 import moe
+    H, I, E, k = 256, 192, 16, 4
+    w = synth.MoELayerWeights(H, I, E, 81, sigma=0.05)
+    single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)
+    single.upload_layer(0, w)
+    ranks = [moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, rank=r, world=world)
+             for r in range(world)]
+    for b in ranks:
+        b.upload_layer(0, w)
+    moe.MoEBlock.attach_local(ranks)
+    for step in range(2):
+        t = synth.activations(600 + step, T, H)
+        x0 = synth.normal(700 + step, synth.tensor_id(synth.TID_RESIDUAL), (T, H), 1.0)
+        t_dev = to_dev_bf16(t)
+        want = torch.from_numpy(x0.copy()).cuda()
+        single.forward(0, t_dev, want)
+        xs = [torch.from_numpy(x0.copy()).cuda() for _ in range(world)]
+        for b in ranks:
+            b.route_local(0, t_dev)
+        for b in ranks:
+            b.route_finish(t_dev)
+            b.mlp1_swiglu(0)
+            b.push_to_owners(0)
+        for b in ranks:
+            b.owner_combine()
+        for b, x in zip(ranks, xs):
+            b.add_delta(x)
+        for b in ranks:
+            b.status()
+            for name in ("topk_i", "topk_w", "offsets", "sorted"):
+                assert np.array_equal(b.tap(name, T), single.tap(name, T)), name
+        for x in xs:
+            assert torch.equal(x, want)
+    for b in ranks + [single]:
+        b.close()
+
+
 def test_wait_on_a_silent_peer_times_out_as_status():
     from gptoss_b200 import capi, moe
     H, I, E, k, T = 128, 128, 8, 2, 32
@@ -135,6 +177,7 @@ def test_token_sliced_form_matches_single_context_bitwise(world, T):
         xs = [torch.from_numpy(x0[f:f + n].copy()).cuda() for f, n in bounds]
         for b, (f, n) in zip(ranks, bounds):
             b.gather_rows(T, t_dev[f:f + n].contiguous() if n else None)
+            b.sliced_route(0, T)
         for b in ranks:
             b.sliced_push(0, T)
         for b, x in zip(ranks, xs):
@@ -151,6 +194,7 @@ def test_token_sliced_form_matches_single_context_bitwise(world, T):
     adds = [torch.from_numpy(add[f:f + n].copy()).cuda() for f, n in bounds]
     for b, x, a_ in zip(ranks, xs, adds):
         b.gather_slice(T, x, norm_w, add=a_)
+        b.sliced_route(0, T)
     for b in ranks:
         b.sliced_push(0, T)
     for b, x in zip(ranks, xs):

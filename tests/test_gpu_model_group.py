@@ -26,7 +26,7 @@ def checkpoint(tmp_path_factory):
     return p
 
 
-@pytest.mark.parametrize("world,batch", [(2, 7), (4, 7), (8, 5)])
+@pytest.mark.parametrize("world,batch", [(2, 21), (4, 27), (8, 5)])
 def test_group_matches_single_gpu_bitwise(checkpoint, world, batch):
     from gptoss_b200 import model
     cfg = binfmt.config_7m()
@@ -41,7 +41,9 @@ def test_group_matches_single_gpu_bitwise(checkpoint, world, batch):
     slices = [m.slice(batch) for m in group]
     assert sum(n for _, n in slices) == batch and slices[0][0] == 0
     if world == 8:
-        assert slices[-1][1] == 0  # more ranks than sequences: the last ranks hold none and still take part
+        assert slices[-1][1] == 0  # fewer sequences than one slice (8): the other ranks hold none and still take part
+    else:
+        assert all(n > 0 for _, n in slices) and len({n for _, n in slices}) > 1  # uneven, non-empty slices
     for pos in range(n_pos):
         want = single.step(ids[pos], pos)
         got = model.Model.step_group(group, ids[pos], pos)
