@@ -150,7 +150,7 @@ def load() -> C.CDLL:
         "gptoss_moe_gather_rows": ([ctxp, i32, vp, vp], i32),
         "gptoss_moe_forward_host_sliced": ([ctxp, i32, i32, vp, vp], i32),
         "gptoss_moe_route_local": ([ctxp, i32, i32, vp, vp], i32),
-        "gptoss_moe_route_finish": ([ctxp, i32, vp, vp], i32),
+        "gptoss_moe_route_finish": ([ctxp, i32, i32, vp, vp], i32),
         "gptoss_moe_sliced_route": ([ctxp, i32, i32, vp], i32),
     }
     for name, (args, res) in sig.items():

@@ -2,6 +2,7 @@
 // per-layer MoE operator and its stages, taps.  No call aborts or throws; every failure is a status
 // code plus a message retrievable with gptoss_last_error().
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -47,6 +48,8 @@ struct gptoss_ctx {
   RouteShare share_self{};            // where routing rows go: this rank alone ...
   RouteShare share{};                 // ... or every rank of the group (filled when peers are attached)
   int route_step = 0;                 // number of shared routings so far (flag D carries it)
+  bool share_routing = false;         // groups of 4 or more: each rank routes its slice only (below that the extra
+                                      // meeting point costs more than routing the whole batch everywhere)
   int *comm_counter = nullptr;        // last-block counter of the owner combine
   void *peer_base[kMaxRanks] = {};    // opened IPC mappings (nullptr for the own rank / not attached)
   PeerTable peers{};
@@ -206,6 +209,8 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
                 (rank + 1) * ctx->n_local, dims->swiglu_limit};
   ctx->layers.resize(dims->n_layers);
   ctx->peers.timeout_ns = 2000000000ull;
+  ctx->share_routing = world >= 4;
+  if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
   const size_t P = T * k, nblk = (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock;
@@ -478,7 +483,7 @@ int gptoss_moe_route_local(gptoss_ctx *ctx, int layer, int T, const void *t_dev_
   if ((rc = check_T(ctx, T))) return rc;
   CK(cudaSetDevice(ctx->device));
   ctx->cur_T = T;
-  if (T == 0) return GPTOSS_OK;
+  if (T == 0 || !ctx->share_routing) return GPTOSS_OK;  // small groups: route_finish routes the whole batch here
   const uint8_t *t = static_cast<const uint8_t *>(t_dev_bf16 ? t_dev_bf16 : ctx->sym + ctx->sym_delta_off);
   int first = 0, n = 0;
   gptoss_moe_slice_bounds(ctx, T, &first, &n);
@@ -486,17 +491,22 @@ int gptoss_moe_route_local(gptoss_ctx *ctx, int layer, int T, const void *t_dev_
   return route_rows(ctx, layer, T, t + (size_t)first * ctx->d.H * 2, first, n, ctx->share, static_cast<cudaStream_t>(stream));
 }
 
-int gptoss_moe_route_finish(gptoss_ctx *ctx, int T, const void *t_dev_bf16, void *stream) {
+int gptoss_moe_route_finish(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream) {
   int rc = check_attached(ctx);
   if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
   if ((rc = check_T(ctx, T))) return rc;
-  if (T != ctx->cur_T || ctx->route_step == 0) return ctx->fail(GPTOSS_ERR_STATE, "route_finish without a matching route_local");
+  if (T != ctx->cur_T || (ctx->share_routing && ctx->route_step == 0))
+    return ctx->fail(GPTOSS_ERR_STATE, "route_finish without a matching route_local");
   CK(cudaSetDevice(ctx->device));
   if (T == 0) return GPTOSS_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  CK(launch_wait_flags(ctx->peers, ctx->pending_gather, ctx->route_step, ctx->status, s));
+  const void *t = t_dev_bf16 ? t_dev_bf16 : ctx->sym + ctx->sym_delta_off;
+  if (ctx->pending_gather > 0 || ctx->share_routing)
+    CK(launch_wait_flags(ctx->peers, ctx->pending_gather, ctx->share_routing ? ctx->route_step : 0, ctx->status, s));
   ctx->pending_gather = 0;
-  return route_group(ctx, T, t_dev_bf16 ? t_dev_bf16 : ctx->sym + ctx->sym_delta_off, s);
+  if (!ctx->share_routing) return gptoss_moe_route(ctx, layer, T, t, stream);
+  return route_group(ctx, T, t, s);
 }
 
 int gptoss_moe_mlp1_swiglu(gptoss_ctx *ctx, int layer, void *stream) {
@@ -637,7 +647,7 @@ int gptoss_moe_sliced_route(gptoss_ctx *ctx, int layer, int T, void *stream) {
 }
 
 int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream) {
-  int rc = gptoss_moe_route_finish(ctx, T, nullptr, stream);
+  int rc = gptoss_moe_route_finish(ctx, layer, T, nullptr, stream);
   if (rc) return rc;
   if (T == 0) return GPTOSS_OK;
   if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
@@ -685,7 +695,7 @@ int gptoss_moe_forward(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16
   if (!t_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null activation pointer");
   if ((rc = gptoss_moe_route_local(ctx, layer, T, t_dev_bf16, stream))) return rc;  // each rank routes its token slice
   if (T == 0) return GPTOSS_OK;
-  if ((rc = gptoss_moe_route_finish(ctx, T, t_dev_bf16, stream))) return rc;
+  if ((rc = gptoss_moe_route_finish(ctx, layer, T, t_dev_bf16, stream))) return rc;
   if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
   if ((rc = gptoss_moe_push_to_owners(ctx, layer, stream))) return rc;
   if ((rc = gptoss_moe_owner_combine(ctx, stream))) return rc;

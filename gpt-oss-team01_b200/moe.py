@@ -199,9 +199,9 @@ class MoEBlock:
         """replicated activations t [T,H]: this rank routes its token slice and stores the rows to every rank"""
         self._check(self.lib.gptoss_moe_route_local(self._ctx, layer, t.shape[0], _ptr(t), _stream(stream)))
 
-    def route_finish(self, t, stream=None):
+    def route_finish(self, layer, t, stream=None):
         """waits for every rank's routing rows, then counting sort + gather of the rows of this rank's experts"""
-        self._check(self.lib.gptoss_moe_route_finish(self._ctx, t.shape[0], _ptr(t), _stream(stream)))
+        self._check(self.lib.gptoss_moe_route_finish(self._ctx, layer, t.shape[0], _ptr(t), _stream(stream)))
 
     def sliced_push(self, layer, n_tokens, stream=None):
         self._check(self.lib.gptoss_moe_sliced_push(self._ctx, layer, n_tokens, _stream(stream)))

@@ -78,7 +78,7 @@ def test_shared_routing_matches_single_context_bitwise(world, T):
         for b in ranks:
             b.route_local(0, t_dev)
         for b in ranks:
-            b.route_finish(t_dev)
+            b.route_finish(0, t_dev)
             b.mlp1_swiglu(0)
             b.push_to_owners(0)
         for b in ranks:
