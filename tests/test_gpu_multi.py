@@ -24,6 +24,7 @@ def _worker(rank, world, port, out_dir):
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["GPTOSS_SHARED_ROUTING"] = "1"  # also with two ranks: every rank routes its own token slice only
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.cuda.set_device(rank)
     H, I, E, k, T = 512, 384, 16, 4, 1000
