@@ -78,6 +78,14 @@ class MoeLayerOps {
     for (int r = 0; r < world && r < 16; ++r) ctxs[r] = ranks[r]->ctx_;
     for (int r = 0; r < world; ++r) ranks[r]->check(gptoss_comm_attach_local(ranks[r]->ctx_, ctxs));
   }
+  // router_gemm_v2 + topk_softmax_batched shared between the GPUs: each routes its own token slice and stores the rows
+  // to all (route_local), then moe_build_offsets_hip + moe_pack_inputs_hip on the whole batch (route_finish)
+  void route_local(int layer, const void *t_bf16, int cur_batch_size, void *stream) {
+    check(gptoss_moe_route_local(ctx_, layer, cur_batch_size, t_bf16, stream));
+  }
+  void route_finish(int layer, const void *t_bf16, int cur_batch_size, void *stream) {
+    check(gptoss_moe_route_finish(ctx_, layer, cur_batch_size, t_bf16, stream));
+  }
   // ring_reduce_agg_quantize_fp8 + add_vector_batched, fused with moe_mlp2_forward_hip + moe_scatter_aggregate_ep_hip:
   // the three stages behind forward() once peers are attached
   void moe_mlp2_push_to_owners(int layer, void *stream) { check(gptoss_moe_push_to_owners(ctx_, layer, stream)); }
