@@ -48,8 +48,8 @@ struct gptoss_ctx {
   RouteShare share_self{};            // where routing rows go: this rank alone ...
   RouteShare share{};                 // ... or every rank of the group (filled when peers are attached)
   int route_step = 0;                 // number of shared routings so far (flag D carries it)
-  bool share_routing = false;         // groups of 4 or more: each rank routes its slice only (below that the extra
-                                      // meeting point costs more than routing the whole batch everywhere)
+  bool share_routing = false;         // GPTOSS_SHARED_ROUTING=1: each rank routes its token slice only and shares the rows
+                                      // (off by default: measured neutral, the replicated scatter/gather dominates the stage)
   int *comm_counter = nullptr;        // last-block counter of the owner combine
   void *peer_base[kMaxRanks] = {};    // opened IPC mappings (nullptr for the own rank / not attached)
   PeerTable peers{};
@@ -209,7 +209,6 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
                 (rank + 1) * ctx->n_local, dims->swiglu_limit};
   ctx->layers.resize(dims->n_layers);
   ctx->peers.timeout_ns = 2000000000ull;
-  ctx->share_routing = world >= 4;
   if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;

@@ -142,9 +142,10 @@ int gptoss_comm_set_timeout_ms(gptoss_ctx *ctx, int ms);
  *                  token rows of this rank's experts (moe_build_offsets_hip + moe_pack_inputs_hip).
  * t_dev_bf16: the replicated activations [T,H] (NULL in the token-sliced form: the context's gathered buffer).  The
  * split-K factor of the router GEMM is derived from T, not from the slice, so a token's scores have the same bits
- * whoever routes it.  Slices are contiguous and a multiple of 8 tokens (gptoss_moe_slice_bounds).  Groups of fewer
- * than 4 ranks keep routing the whole batch on every rank (route_local does nothing, route_finish routes): there the
- * extra meeting point costs more than it saves; GPTOSS_SHARED_ROUTING=0/1 in the environment overrides the choice. */
+ * whoever routes it.  Slices are contiguous and a multiple of 8 tokens (gptoss_moe_slice_bounds).  Sharing is OFF unless
+ * the environment holds GPTOSS_SHARED_ROUTING=1 when the context is created (then route_local does nothing and
+ * route_finish routes the whole batch on this rank): measured, the extra meeting point costs what the smaller router
+ * GEMM and top-k save, because the stage is dominated by the scatter/gather that every rank needs anyway. */
 int gptoss_moe_route_local(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream);
 int gptoss_moe_route_finish(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16, void *stream);
 int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream);

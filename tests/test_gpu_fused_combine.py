@@ -54,11 +54,12 @@ def test_emulated_ranks_match_single_context_bitwise(world, T):
 
 
 @pytest.mark.parametrize("world,T", [(2, 300), (4, 203), (8, 64)])
-def test_shared_routing_matches_single_context_bitwise(world, T):
+def test_shared_routing_matches_single_context_bitwise(world, T, monkeypatch):
     """Replicated activations, routing shared: every rank routes only its token slice (router GEMM with the split-K
     factor of the whole batch, top-k, block histograms) and stores the rows to all ranks; after that every rank must
     hold the routing of the single-context block bit for bit, and the block output must be identical."""
     from gptoss_b200 import moe
+    monkeypatch.setenv("GPTOSS_SHARED_ROUTING", "1")  # read when a context is created
     H, I, E, k = 256, 192, 16, 4
     w = synth.MoELayerWeights(H, I, E, 81, sigma=0.05)
     single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)

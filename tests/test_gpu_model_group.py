@@ -26,9 +26,10 @@ def checkpoint(tmp_path_factory):
     return p
 
 
-@pytest.mark.parametrize("world,batch", [(2, 21), (4, 27), (8, 5)])
-def test_group_matches_single_gpu_bitwise(checkpoint, world, batch):
+@pytest.mark.parametrize("world,batch,shared", [(2, 21, "0"), (4, 27, "1"), (8, 5, "1"), (4, 27, "0")])
+def test_group_matches_single_gpu_bitwise(checkpoint, world, batch, shared, monkeypatch):
     from gptoss_b200 import model
+    monkeypatch.setenv("GPTOSS_SHARED_ROUTING", shared)  # with and without each rank routing only its own slice
     cfg = binfmt.config_7m()
     n_pos = 40
     ids = synth.uniform_ids(SEED, 3, batch * n_pos, cfg.vocab_size).reshape(n_pos, batch).astype(np.int32)
