@@ -6,11 +6,18 @@
 
 A step is one pass of the block over one batch of synthetic tokens.  N = 1: hidden 2880, 32 experts,
 top-4, T = 1024 tokens (the single-GPU configuration the headline metric is quoted on).  N > 1 (one
-process per GPU under torchrun): the same layer with its experts sharded E/N per GPU and T = 1024*N
-replicated tokens; the gate-weighted expert rows are pushed to the GPU that owns the token by peer stores
-from the down-GEMM epilogue, summed there and delivered to every rank (an NCCL all-reduce of per-rank
-partials is timed beside it as the baseline) — per-GPU work is fixed, so the scaling is weak.  Weights rotate over several distinct layers (each 1.6 GB >> the 126 MB L2), so
-every step streams its weights from HBM.
+process per GPU under torchrun): the same layer with its experts sharded E/N per GPU and T = 1024*N tokens,
+uniform routing; per-GPU work is fixed, so the scaling is weak.  `value` times the token-sliced form: every GPU holds
+1/N of the tokens (activations and residual rows), routes them, dispatches each token row to the GPUs whose experts
+it selected (peer stores from the grouping kernel), and the gate-weighted expert rows are pushed back to the token's
+GPU from the down-GEMM epilogue and summed there.  The replicated form (tokens and residual on every GPU, sums
+delivered to all), an NCCL all-reduce of per-rank partials, and the same GEMMs with the exchange stubbed are timed
+beside it, and one step of each form is checked against the NCCL result.  Weights rotate over several distinct layers
+(each 1.6 GB >> the 126 MB L2), so every step streams its weights from HBM.  The timed region of K steps is repeated
+until half a second of device time has been measured; `value` is the median region.
+
+Extra keys of the same line: `skewed_T8192` (T = 8192 tokens in total, Zipf s = 1.2 routing, experts sharded E/N) and
+`decode` (whole-model greedy decode of the gpt-oss-20b architecture at N GPUs, gpt-oss-120b at N >= 4).
 
 Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` goes through the
 host-buffer entry point with pinned host memory (H2D + block + D2H inside the timed region).
@@ -200,6 +207,35 @@ def workload_config(n_gpus, T):
 # ----------------------------------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------------------------------
+def timed_regions(step, K, barrier, world, dist, torch, min_seconds=0.5, max_regions=400):
+    """Times regions of exactly K steps (CUDA events on the launching stream, barrier + synchronize on both sides, the
+    slowest rank's time per region) until at least min_seconds of device time has been measured; returns the per-region
+    milliseconds.  The number of regions follows from the first one, so every rank runs the same number."""
+    def one():
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(K):
+            step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+    regions = [one()]
+    n = int(min(max_regions, max(1, -(-min_seconds * 1e3 // max(regions[0], 1e-3)))))
+    for _ in range(n - 1):
+        regions.append(one())
+    return regions
+
+
+def rel_l2_t(a, b):
+    return float(((a - b).double().norm() / b.double().norm().clamp_min(1e-30)).item())
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -213,28 +249,42 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     clocks = ClockSampler(local_rank, enabled=rank == 0).start()  # nvidia-smi needs a second or more before its first line on an 8-GPU box
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     T = (args.tokens_per_gpu or TOKENS_PER_GPU) * world
-    K, W = args.steps, max(args.warmup, 3)
+    K, W = args.steps, args.warmup
+    if W < 3:
+        print(f"bench.py: --warmup {W} raised to 3 (fewer warm-up steps give a cold-start number)", file=sys.stderr)
+        W = 3
+    T_SKEW = 8192  # tokens of the skewed-routing workload (total, over all GPUs)
+    skew_layer = args.weight_sets  # an extra layer slot whose router bias carries the Zipf skew
 
     global N_WEIGHT_SETS
     N_WEIGHT_SETS = args.weight_sets
-    blk = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=K_TOP, n_layers=N_WEIGHT_SETS,
-                       device=local_rank, rank=rank, world=world, max_tokens=T,
-                       wire={"f32": 0, "bf16": 1}[args.wire])
+    wire = {"f32": 0, "bf16": 1}[args.wire]
+    blk = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=K_TOP, n_layers=N_WEIGHT_SETS + (0 if args.no_extras else 1),
+                       device=local_rank, rank=rank, world=world, max_tokens=max(T, 0 if args.no_extras else T_SKEW), wire=wire)
     for layer in range(N_WEIGHT_SETS):
         blk.fill_layer_synthetic(layer, SEED, SIGMA)
-        if args.zipf > 0:  # skewed routing (BASELINE config 3): router_bias[e] += -s * ln(e + 1), hottest expert first
+        if args.zipf > 0:  # skewed routing: router_bias[e] += -s * ln(e + 1), hottest expert first
             blk.set_router_bias(layer, synth.zipf_router_bias(SEED, layer, E, args.zipf))
     t_dev = moe.synth_normal_bf16(T * H, SEED, synth.tensor_id(synth.TID_ACTIVATION), 1.0).view(T, H)
     x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
     partial = torch.empty_like(x) if world > 1 else None
+    first, n_own = blk.slice(T)
+    t_own = t_dev[first:first + n_own].contiguous() if world > 1 else None
+    x_own = torch.zeros((n_own, H), dtype=torch.float32, device="cuda") if world > 1 else None
 
     if world > 1:
-        blk.attach_peers()  # CUDA IPC handles of the combine buffers, exchanged over the process group
+        blk.attach_peers()  # CUDA IPC handles of the exchange buffers, handed round over the process group
 
-    def step(i):  # x += MoE(t); N > 1: fused peer-store combine inside forward()
+    def step_replicated(i):  # x += MoE(t) on replicated t and x; N > 1: fused peer-store combine inside forward()
         blk.forward(i % N_WEIGHT_SETS, t_dev, x)
+
+    def step_dispatch(i):  # N > 1, token-sliced: every rank holds its rows of t and x only
+        blk.forward_dispatch(i % N_WEIGHT_SETS, T, t_own, x_own)
+
+    step = step_replicated if world == 1 or args.form == "replicated" else step_dispatch
 
     def step_nccl(i):  # A/B baseline for N > 1: per-rank partial + NCCL all-reduce + add
         blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
@@ -250,61 +300,75 @@ def run_ours(args):
         step(i)
     barrier()
     blk.status()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with clocks:
-        barrier()
-        ev0.record()
-        for i in range(K):
-            step(i)
-        ev1.record()
-        barrier()
+        l0 = moe.launch_count()
+        regions = timed_regions(step, K, barrier, world, dist, torch)
+        launches = (moe.launch_count() - l0) // len(regions)
     blk.status()
-    ms = ev0.elapsed_time(ev1)
-    if world > 1:
-        tms = torch.tensor([ms], device="cuda")
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms = float(tms.item())
+    ms = statistics.median(regions)
     value = T * K / (ms * 1e-3)
 
-    nccl_ms = stub_ms = stub_free_ms = None
-    if world > 1:
-        # The same kernels with the exchange stubbed: every rank computes the partial of its own experts (no push,
-        # no delivery, no add).  Timed twice: with a device-side rendezvous of the ranks after every step (what the
-        # expert-parallel step costs without moving any data: the ranks still wait for the most loaded one every
-        # step) and free-running (each rank at its own pace; the gap between the two is load imbalance, not exchange).
-        def timed_stub(sync):
-            for i in range(3):
-                blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
-                if sync:
-                    blk.rendezvous()
-            barrier()
-            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record()
-            for i in range(K):
-                blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)
-                if sync:
-                    blk.rendezvous()
-            s1.record()
-            barrier()
-            ts = torch.tensor([s0.elapsed_time(s1)], device="cuda")
-            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
-            return float(ts.item()) / K
-        stub_ms = timed_stub(True)
-        stub_free_ms = timed_stub(False)
-        blk.status()
-    if world > 1:  # the NCCL baseline on the same steps
+    def timed_once(fn, sync_each=None):
         for i in range(3):
-            step_nccl(i)
+            fn(i)
+            if sync_each:
+                sync_each()
         barrier()
-        n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n0.record()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
         for i in range(K):
-            step_nccl(i)
-        n1.record()
+            fn(i)
+            if sync_each:
+                sync_each()
+        s1.record()
         barrier()
-        tn = torch.tensor([n0.elapsed_time(n1)], device="cuda")
-        dist.all_reduce(tn, op=dist.ReduceOp.MAX)
-        nccl_ms = float(tn.item()) / K
+        ts = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        return float(ts.item()) / K
+
+    nccl_ms = stub_ms = stub_free_ms = other_form_ms = None
+    parity = None
+    if world > 1:
+        # The same expert GEMMs with the exchange stubbed: every rank computes the partial of its own experts (no
+        # dispatch, no push, no add).  Timed twice: with a device-side rendezvous of the ranks after every step (what
+        # the expert-parallel step costs without moving any data: the ranks still wait for the most loaded one) and
+        # free-running (each rank at its own pace; the gap between the two is load imbalance, not exchange).
+        stub = lambda i: blk.forward_partial(i % N_WEIGHT_SETS, t_dev, partial)  # noqa: E731
+        stub_ms = timed_once(stub, blk.rendezvous)
+        stub_free_ms = timed_once(stub)
+        blk.status()
+        nccl_ms = timed_once(step_nccl)
+        other_form_ms = timed_once(step_dispatch if step is step_replicated else step_replicated)
+        blk.status()
+
+        # Correctness of what crossed NVLink, outside the timed regions: one step of each form on the same inputs
+        # against the per-rank partials summed by NCCL.
+        gen = torch.Generator(device="cuda").manual_seed(1234)
+        x0 = torch.randn((T, H), dtype=torch.float32, device="cuda", generator=gen)
+        want = x0.clone()
+        blk.forward_partial(0, t_dev, partial)
+        dist.all_reduce(partial)
+        want.add_(partial)
+        xr = x0.clone()
+        blk.forward(0, t_dev, xr)
+        xs = x0[first:first + n_own].clone()
+        blk.forward_dispatch(0, T, t_own, xs)
+        blk.status()
+        errs = torch.tensor([rel_l2_t(xr - x0, want - x0),
+                             rel_l2_t(xs - x0[first:first + n_own], (want - x0)[first:first + n_own]) if n_own else 0.0],
+                            device="cuda", dtype=torch.float64)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        # every rank's replicated residual stream must hold the same bits
+        digest = xr.view(torch.int32).to(torch.int64).sum().reshape(1)
+        digests = [torch.empty_like(digest) for _ in range(world)]
+        dist.all_gather(digests, digest)
+        identical = all(int(d.item()) == int(digests[0].item()) for d in digests)
+        # fp32 rows summed in another order than NCCL's: 1e-5; rows or sums rounded to bf16 on the wire: 2^-9 per row
+        tol = 1e-5 if wire == 0 else 4e-3
+        parity = {"replicated_vs_nccl_rel_l2": float(errs[0].item()), "dispatch_vs_nccl_rel_l2": float(errs[1].item()),
+                  "parity_rel_l2": float(errs.max().item()), "ranks_identical": identical, "tolerance": tol,
+                  "checked": "one step of each form on the same inputs against forward_partial + NCCL all-reduce (fp32)"}
 
     # per-stage device time (same steps, events between the stages), for the roofline of the top kernel
     if world == 1:
@@ -335,6 +399,25 @@ def run_ours(args):
     barrier()
     blk.status()
     stage_ms = {n: sum(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(K)) / K for j, n in enumerate(names)}
+    dispatch_stage_ms = None
+    if world > 1:
+        dn = ["route_own_rows", "group_and_dispatch_rows", "mlp1_mlp2_push", "owner_sum"]
+        evd = [[torch.cuda.Event(enable_timing=True) for _ in range(len(dn) + 1)] for _ in range(K)]
+        barrier()
+        for i in range(K):
+            layer = i % N_WEIGHT_SETS
+            evd[i][0].record()
+            blk.dispatch_route(layer, T, t_own)
+            evd[i][1].record()
+            blk.dispatch_rows(layer, T, t_own)
+            evd[i][2].record()
+            blk.dispatch_push(layer)
+            evd[i][3].record()
+            blk.sliced_combine(x_own)
+            evd[i][4].record()
+        barrier()
+        blk.status()
+        dispatch_stage_ms = {n: sum(evd[i][j].elapsed_time(evd[i][j + 1]) for i in range(K)) / K for j, n in enumerate(dn)}
 
     hbm_peak, tf_burst, tf_sust, peak_kind = measured_peaks()
     n_local = E // world
@@ -343,10 +426,28 @@ def run_ours(args):
     off = blk.tap("offsets", T)
     rows_here = int(off[(rank + 1) * n_local] - off[rank * n_local])
     rows_max = rows_here
+    nvlink = None
     if world > 1:
         rm = torch.tensor([rows_here], device="cuda")
         dist.all_reduce(rm, op=dist.ReduceOp.MAX)
         rows_max = int(rm.item())
+        # bytes this GPU sends over NVLink per step in the dispatch form: token rows to remote experts, expert rows to
+        # remote owners (counted from the routing of the last step)
+        ti = blk.tap("topk_i", T)
+        owner_of_expert = ti // n_local
+        per = moe.slice_bounds(0, world, T)[1]
+        owner_of_token = np.minimum(np.arange(T) // max(per, 1), world - 1)[:, None]
+        mine_tok = owner_of_token == rank
+        rows_out = int(((owner_of_expert != rank) & mine_tok).sum())  # one row per (token, slot) with a remote expert
+        push_out = int(((owner_of_expert == rank) & ~mine_tok).sum())
+        esz = 2 if wire == 1 else 4
+        out_bytes = rows_out * H * 2 + push_out * H * esz
+        t_out = torch.tensor([out_bytes], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t_out, op=dist.ReduceOp.MAX)
+        nvlink = {"bytes_out_per_gpu_per_step_max": int(t_out.item()), "dispatch_rows_out": rows_out, "pushed_rows_out": push_out,
+                  "pushed_row_dtype": "bf16" if wire == 1 else "f32",
+                  "time_at_900_GBs_ms": float(t_out.item()) / 900e9 * 1e3,
+                  "achieved_GBs_over_step": float(t_out.item()) / (ms / K * 1e-3) / 1e9 if step is step_dispatch else None}
     pairs_local = rows_here
     mlp1_bytes = n_local * (2 * I * H * 2 + 2 * I * 4) + pairs_local * H * 2 + pairs_local * I * 2
     mlp1_flops = 2 * pairs_local * H * 2 * I
@@ -357,7 +458,7 @@ def run_ours(args):
     else:
         roof = {"bound": "tensor", "achieved": mlp1_flops / mlp1_s / 1e12, "peak": tf_burst, "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = NCU_TRAFFIC_MLP1_BYTES if world == 1 else None  # captured at the N=1 workload only
+    roof["traffic"] = NCU_TRAFFIC_MLP1_BYTES if world == 1 and T == 1024 else None  # captured at the N=1 workload only
     roof.update({"kernel": "grouped_gemm_kernel<2,true> (gate/up GEMM + SwiGLU)", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)",
                  "algorithmic_bytes_per_launch": mlp1_bytes, "algorithmic_flops_per_launch": mlp1_flops,
                  "avg_launch_ms": stage_ms["mlp1_swiglu"], "tensor_frac_of_burst": mlp1_flops / mlp1_s / 1e12 / tf_burst})
@@ -372,23 +473,35 @@ def run_ours(args):
         "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
         "data": "synthetic", "config": dict(workload_config(world, T), **({"router_skew": f"Zipf s={args.zipf} over expert id "
-                                                                              "(router_bias[e] -= s*ln(e+1))"} if args.zipf > 0 else {})),
+                                                                              "(router_bias[e] -= s*ln(e+1))"} if args.zipf > 0 else
+                                                                             {"routing": "uniform (no router-bias skew)"})),
+        "timing": {"regions": len(regions), "steps_per_region": K, "region_ms_median": ms, "region_ms_min": min(regions),
+                   "region_ms_max": max(regions), "value_from": "median region"},
         "roofline": roof,
         "block_roofline": {"algorithmic_bytes": block_bytes, "algorithmic_flops": block_flops,
                            "roof_ms": block_roof_s * 1e3, "frac": block_roof_s * 1e3 / (ms / K),
                            "busiest_rank_rows": rows_max, "rows_per_rank_if_even": T * K_TOP // world,
                            "roof_ms_busiest_rank": busiest_roof_s * 1e3, "frac_busiest_rank": busiest_roof_s * 1e3 / (ms / K),
                            "bound": "hbm" if block_bytes / (hbm_peak * 1e9) >= block_flops / (tf_sust * 1e12) else "tensor"},
-        "stage_ms": stage_ms, "gpu_launches": (7 if world == 1 else 8) * K,  # router GEMM, top-k, scan, scatter, 2 GEMMs, combine (N > 1: owner combine + add instead)
+        "stage_ms": stage_ms, "gpu_launches": int(launches),  # counted by the library: launches inside one timed region
     }
     if world > 1:
-        comm_ms = ms / K - stub_ms  # exposed exchange = step with the fused combine - step with the exchange stubbed
-        line["combine"] = {"kind": "peer stores (fp32) from the down-GEMM epilogue to the token owner + owner sum in slot "
-                                   f"order + peer delivery of the sums ({args.wire})",
+        line["config"]["form"] = ("token-sliced: each GPU holds its 1/N of the tokens' activations and residual rows; token rows "
+                                  "are dispatched to the experts' GPUs, expert rows pushed back to the token's GPU"
+                                  if step is step_dispatch else "replicated tokens and residual on every GPU")
+        comm_ms = ms / K - stub_ms  # exposed exchange = step with the exchange - step with the exchange stubbed
+        line["combine"] = {"kind": ("dispatch of token rows (bf16) by peer stores from the grouping kernel + push of expert rows "
+                                    f"({'bf16' if wire == 1 else 'fp32'}) from the down-GEMM epilogue to the token owner + owner sum in slot order"
+                                    if step is step_dispatch else
+                                    "peer stores (fp32) from the down-GEMM epilogue to the token owner + owner sum in slot "
+                                    f"order + peer delivery of the sums ({args.wire})"),
                            "exposed_ms": comm_ms, "share_of_step": comm_ms / (ms / K),
                            "stubbed_exchange_ms_per_step": stub_ms,
                            "stubbed_exchange_without_rendezvous_ms_per_step": stub_free_ms,
-                           "nccl_allreduce_baseline_ms_per_step": nccl_ms}
+                           "nccl_allreduce_baseline_ms_per_step": nccl_ms,
+                           ("replicated_form_ms_per_step" if step is step_dispatch else "dispatch_form_ms_per_step"): other_form_ms,
+                           "dispatch_stage_ms": dispatch_stage_ms, "nvlink": nvlink}
+        line["combine"].update(parity)
 
     if rank == 0:
         cs = clocks.summary()
@@ -404,17 +517,17 @@ def run_ours(args):
         for i in range(3):
             blk.forward_host(i % N_WEIGHT_SETS, t_host, x_host)
         torch.cuda.synchronize()
+        n_e2e = max(K, int(0.3 / max(ms / K * 2.5e-3, 1e-6)))  # about 0.3 s of calls
         t0 = time.perf_counter()
-        for i in range(K):
+        for i in range(n_e2e):
             blk.forward_host(i % N_WEIGHT_SETS, t_host, x_host)
-        e2e_s = time.perf_counter() - t0
-        line["e2e"] = {"value": T * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": T * H * 2 + T * H * 4,
-                       "d2h_bytes_per_step": T * H * 4, "ms_per_step": 1e3 * e2e_s / K}
+        e2e_s = (time.perf_counter() - t0) / n_e2e
+        line["e2e"] = {"value": T / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": T * H * 2 + T * H * 4,
+                       "d2h_bytes_per_step": T * H * 4, "ms_per_step": 1e3 * e2e_s, "calls_timed": n_e2e}
     else:
         # The host holds the batch once; every rank moves ITS slice of the tokens over PCIe (t and x in, x out) and the
-        # ranks exchange activations and expert rows over NVLink (token-sliced form of the block): per step the
+        # ranks exchange token rows and expert rows over NVLink (dispatch form of the block): per step the
         # batch crosses the host link once in total, not once per GPU.
-        first, n_own = blk.slice(T)
         t_host = torch.empty((n_own, H), dtype=torch.int16).pin_memory()
         t_host.copy_(t_dev.view(torch.int16)[first:first + n_own].cpu())
         x_host = torch.zeros((n_own, H), dtype=torch.float32).pin_memory()
@@ -432,63 +545,150 @@ def run_ours(args):
                        "ms_per_step": 1e3 * float(e2e_s.item()) / K,
                        "note": "bytes over all GPUs; each GPU copies its own token slice (1/N of them)"}
 
+    # the skewed-routing workload: T = 8192 tokens in total, Zipf s = 1.2 over the expert ids, experts sharded E/N
+    if not args.no_extras:
+        try:
+            line["skewed_T8192"] = run_skewed(blk, moe, torch, dist, world, rank, skew_layer, T_SKEW, K, barrier)
+        except Exception as e:  # an extra must never cost the headline
+            line["skewed_T8192"] = {"error": repr(e)}
+
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         _, info, _ = cpu_arm(T, target_seconds=12.0, repeats=1, warmup=0)
         line["cpu_baseline"] = info
     blk.close()
+    del blk, t_dev, x, partial
+    torch.cuda.empty_cache()
+
+    # whole-model decode beside the layer numbers (own context; the MoE context above is gone)
+    if not args.no_extras:
+        line["decode"] = {}
+        for wl in (["decode20b"] + (["decode120b"] if world >= 4 else [])):
+            try:
+                line["decode"][wl] = decode_leg(args, wl, dist if world > 1 else None)
+            except Exception as e:
+                line["decode"][wl] = {"error": repr(e)}
+
+    bad = parity is not None and not (parity["parity_rel_l2"] <= parity["tolerance"] and parity["ranks_identical"])
     if rank == 0:
         print_line(line)
     if world > 1:
         dist.destroy_process_group()
+    if bad:
+        raise SystemExit(f"cross-GPU parity check failed: {parity}")
 
 
-def run_decode(args):
+def run_skewed(blk, moe, torch, dist, world, rank, layer, T, K, barrier):
+    """One gpt-oss-20b MoE layer at T = 8192 tokens with Zipf-skewed routing (router_bias[e] -= 1.2 ln(e+1): expert 0 the
+    hottest), experts in contiguous shards of E/N per GPU: rank 0 holds the hot experts.  N = 1: replicated form on
+    one GPU; N > 1: dispatch form.  Reports the step time against the tensor roofline of the busiest rank."""
+    hbm_peak, tf_burst, tf_sust, _ = measured_peaks()
+    blk.fill_layer_synthetic(layer, SEED, SIGMA)
+    blk.set_router_bias(layer, synth.zipf_router_bias(SEED, layer, E, 1.2))
+    t_dev = moe.synth_normal_bf16(T * H, SEED + 1, synth.tensor_id(synth.TID_ACTIVATION), 1.0).view(T, H)
+    first, n_own = blk.slice(T)
+    if world == 1:
+        x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+        fn = lambda i: blk.forward(layer, t_dev, x)  # noqa: E731
+    else:
+        t_own = t_dev[first:first + n_own].contiguous()
+        x = torch.zeros((n_own, H), dtype=torch.float32, device="cuda")
+        fn = lambda i: blk.forward_dispatch(layer, T, t_own, x)  # noqa: E731
+    for i in range(3):
+        fn(i)
+    barrier()
+    blk.status()
+    steps = max(5, min(K, 20))
+    with ClockSampler(int(os.environ.get("LOCAL_RANK", "0")), enabled=rank == 0) as cl:
+        regions = timed_regions(fn, steps, barrier, world, dist, torch, min_seconds=0.3)
+    blk.status()
+    ms = statistics.median(regions) / steps
+    off = blk.tap("offsets", T)
+    n_local = E // world
+    rows = [int(off[(r + 1) * n_local] - off[r * n_local]) for r in range(world)]
+    busiest = max(rows)
+    flops_busiest = 2.0 * busiest * 3 * H * I + 2.0 * (T // world if world > 1 else T) * H * E
+    bytes_rank = n_local * 3 * H * I * 2 + T * H * 2 + T * H * 8 / world
+    roof_ms = max(flops_busiest / (tf_sust * 1e12), bytes_rank / (hbm_peak * 1e9)) * 1e3
+    out = {"tokens": T, "router_skew": "Zipf s=1.2 over expert id", "experts_per_gpu": n_local, "ms_per_step": ms,
+           "tok_per_s": T / (ms * 1e-3), "rows_per_rank": rows, "busiest_rank_rows": busiest,
+           "roof_ms_busiest_rank": roof_ms, "frac_busiest_rank": roof_ms / ms,
+           "bound": "tensor (sustained bf16 peak)" if flops_busiest / (tf_sust * 1e12) >= bytes_rank / (hbm_peak * 1e9) else "hbm",
+           "form": "one GPU" if world == 1 else "token-sliced dispatch form", "clocks": cl.summary() if rank == 0 else None,
+           "regions": len(regions), "steps_per_region": steps}
+    if world > 1:
+        partial = torch.empty((T, H), dtype=torch.float32, device="cuda")
+        stub = lambda i: (blk.forward_partial(layer, t_dev, partial), blk.rendezvous())  # noqa: E731
+        for i in range(2):
+            stub(i)
+        stub_regions = timed_regions(stub, steps, barrier, world, dist, torch, min_seconds=0.1)
+        stub_ms = statistics.median(stub_regions) / steps
+        out["combine"] = {"exposed_ms": ms - stub_ms, "share_of_step": (ms - stub_ms) / ms, "stubbed_exchange_ms_per_step": stub_ms}
+        blk.status()
+    return out
+
+
+def decode_leg(args, workload, dist):
     """Whole-model batched greedy decode (random-init weights generated on the device), sequences of random prompt
     ids force-fed one position per step, then greedy tokens.  decode20b: gpt-oss-20b architecture, 1024 x 128 prompt
-    ids, 256 generated (BASELINE config 4); decode120b: gpt-oss-120b architecture, 2048 x 256, 256 generated
-    (config 5; needs the experts spread over >= 4 GPUs).  With N > 1 (one process per GPU) the N GPUs decode the
+    ids, 256 generated; decode120b: gpt-oss-120b architecture, 2048 x 256, 256 generated (needs the experts spread
+    over >= 4 GPUs).  With N > 1 (one process per GPU, process group already up) the N GPUs decode the
     batch together: sequences in slices, experts sharded, per-layer exchange over peer memory.  Reported like the
     reference's getp mode: generated tokens / wall time of the whole inference loop (getp-csrc/getp_eval.cpp:125-131),
-    the slowest rank's time."""
+    the slowest rank's time.  Returns the result as a dict."""
     import torch
     from gptoss_b200 import binfmt, model
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    big = args.workload == "decode120b"
+    big = workload == "decode120b"
     B = args.decode_batch or (2048 if big else 1024)
     n_prompt = args.decode_prompt or (256 if big else 128)
     n_gen = args.decode_gen or 256
     cfg = binfmt.config_120b(seq_len=1024) if big else binfmt.config_20b(seq_len=1024)
     if args.decode_layers:
         cfg.n_layers = args.decode_layers
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     m = model.Model(cfg, device=local_rank, max_batch=B, max_seq=args.decode_first_pos + n_prompt + n_gen, rank=rank, world=world)
-    m.fill_synthetic(SEED, SIGMA)
-    if world > 1:
-        m.attach_peers()
-    first, n = m.slice(B)
-    prompts = synth.uniform_ids(SEED, 11, B * n_prompt, cfg.vocab_size).reshape(B, n_prompt)[first:first + n]
-    m.generate(prompts[:, :2], 2, batch=B)  # warm-up: 3 steps
-    if world > 1:
-        dist.barrier()
-    with ClockSampler(local_rank) as clocks:
-        t0 = time.perf_counter()
-        out = m.generate(prompts, n_gen, batch=B, first_pos=args.decode_first_pos)
-        dt = time.perf_counter() - t0
-    n_distinct = int(len(np.unique(out)))
-    if world > 1:
-        tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dt = float(tt.item())
-        dist.barrier()
+    try:
+        m.fill_synthetic(SEED, SIGMA)
+        if world > 1:
+            m.attach_peers()
+        first, n = m.slice(B)
+        prompts = synth.uniform_ids(SEED, 11, B * n_prompt, cfg.vocab_size).reshape(B, n_prompt)[first:first + n]
+        m.generate(prompts[:, :2], 2, batch=B)  # warm-up: 3 steps
+        if world > 1:
+            dist.barrier()
+        with ClockSampler(local_rank, enabled=rank == 0) as clocks:
+            t0 = time.perf_counter()
+            out = m.generate(prompts, n_gen, batch=B, first_pos=args.decode_first_pos)
+            dt = time.perf_counter() - t0
+        n_distinct = int(len(np.unique(out)))
+        if world > 1:
+            tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt.item())
+            dist.barrier()
+    finally:
+        m.close()
     steps = n_prompt + n_gen - 1
     arch = "gpt-oss-120b" if big else "gpt-oss-20b"
-    line = {"metric": f"batched decode tok/s, {arch} arch (whole model, greedy, lock-step)", "value": B * n_gen / dt,
+    # HBM roofline of the decode: every step streams this GPU's weights once (its experts, the attention projections;
+    # the classifier only on steps that produce a token) and the K/V rows of its sequences up to the position
+    # (windowed on even layers)
+    hbm_peak = measured_peaks()[0]
+    c = cfg
+    qd, kvd = c.head_dim * c.n_attn_heads, c.head_dim * c.n_kv_heads
+    w_layer = (c.n_experts // world) * 3 * c.hidden_dim * c.intermediate_dim * 2 + ((qd + 2 * kvd) * c.hidden_dim + c.hidden_dim * qd) * 2
+    seqs = -(-B // world)
+    total = 0.0
+    for pos in range(args.decode_first_pos, args.decode_first_pos + steps):
+        kv = 0
+        for l in range(c.n_layers):
+            ctx_len = min(pos + 1, c.sliding_window) if (c.sliding_window > 0 and l % 2 == 0) else pos + 1
+            kv += ctx_len * kvd * 2 * 2
+        total += c.n_layers * w_layer + seqs * kv
+        if pos - args.decode_first_pos >= n_prompt - 1:
+            total += c.vocab_size * c.hidden_dim * 2
+    roof_s = total / (hbm_peak * 1e9)
+    return {"metric": f"batched decode tok/s, {arch} arch (whole model, greedy, lock-step)", "value": B * n_gen / dt,
             "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": 1e3 * dt / steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
             "data": "synthetic",
@@ -498,8 +698,22 @@ def run_decode(args):
                        f"{world} GPUs: sequences in {world} slices (data-parallel attention), {cfg.n_experts // world} "
                        "experts per GPU, activations and expert rows exchanged over NVLink peer memory",
                        "positions_per_second": B * steps / dt, "seed": SEED},
-            "clocks": clocks.summary(), "distinct_tokens_generated_rank0": n_distinct}
-    m.close()
+            "roofline": {"bound": "hbm", "bytes_per_gpu_whole_decode": total, "roof_ms_per_step": 1e3 * roof_s / steps,
+                         "frac": roof_s / dt, "peak": hbm_peak, "unit": "GB/s",
+                         "counts": "per step: this GPU's expert and attention weights once, classifier on generating steps, K/V rows of its sequences"},
+            "clocks": clocks.summary() if rank == 0 else None, "distinct_tokens_generated_rank0": n_distinct}
+
+
+def run_decode(args):
+    import torch
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    line = decode_leg(args, args.workload, dist)
     if rank == 0:
         print_line(line)
     if world > 1:
@@ -523,7 +737,8 @@ def main():
     ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
                     help="N > 1: format in which owners deliver the summed rows (rows travel to the owner in fp32)")
     ap.add_argument("--workload", choices=["moe_layer", "decode20b", "decode120b"], default="moe_layer",
-                    help="moe_layer: the MoE block (headline); decode20b: whole-model greedy decode on one GPU")
+                    help="moe_layer: the MoE block (headline, with the other workloads as extra keys); decode20b / "
+                         "decode120b: only the whole-model greedy decode")
     ap.add_argument("--decode-batch", type=int, default=0, help="0 = the config's batch (1024 / 2048)")
     ap.add_argument("--decode-prompt", type=int, default=0, help="0 = the config's prompt length (128 / 256)")
     ap.add_argument("--decode-gen", type=int, default=0, help="0 = 256")
@@ -531,11 +746,14 @@ def main():
     ap.add_argument("--decode-first-pos", type=int, default=0,
                     help="profiling runs: start the timed decode at this position (cache rows before it are zeros)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra legs of the line (skewed T=8192 workload, whole-model decode)")
+    ap.add_argument("--form", choices=["dispatch", "replicated"], default="dispatch",
+                    help="N > 1: which form of the expert-parallel block `value` times (the other is reported beside it)")
     ap.add_argument("--tokens-per-gpu", type=int, default=0,
-                    help="tokens per step and GPU (0 = 1024, the headline workload; 8192 on one GPU = BASELINE config 3's "
-                         "shape, where the block is tensor-bound)")
+                    help="tokens per step and GPU (0 = 1024, the headline workload; 8192 on one GPU: the block is tensor-bound)")
     ap.add_argument("--zipf", type=float, default=0.0,
-                    help="skew the routing: router_bias[e] -= s*ln(e+1) (1.2 = BASELINE config 3); 0 = uniform")
+                    help="skew the routing: router_bias[e] -= s*ln(e+1) (1.2: the skewed-routing workload); 0 = uniform")
     ap.add_argument("--weight-sets", type=int, default=N_WEIGHT_SETS,
                     help="distinct layers of weights the steps rotate over (1 keeps a profiling run small)")
     args = ap.parse_args()

@@ -37,14 +37,18 @@ struct gptoss_ctx {
   int n_local = 0, sm_count = kSmCountFallback;
   int cur_T = 0;
   RouteBuffers rb{};
-  __nv_bfloat16 *x_packed = nullptr;  // [P,H]
+  __nv_bfloat16 *x_packed = nullptr;  // [P,H]   (inside `sym`: peers dispatch token rows into it)
   __nv_bfloat16 *gate_up = nullptr;   // [P,I]
   float *y_pairs = nullptr;           // [P,H]   (inside `sym`)
   // symmetric buffer: same layout on every rank, exported to the peers over CUDA IPC
   //   [flags: 4*kMaxRanks ints, padded to 1 KiB][delta: T*H fp32][y_pairs: P*H fp32][topk_w: P fp32][topk_i: P i32]
-  //   [blk_hist: n_route_blocks*E i32]
+  //   [blk_hist: n_route_blocks*E i32][x_packed: P*H bf16]
   uint8_t *sym = nullptr;
-  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0, sym_tw_off = 0, sym_ti_off = 0, sym_hist_off = 0;
+  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0, sym_tw_off = 0, sym_ti_off = 0, sym_hist_off = 0, sym_xp_off = 0;
+  RowDispatch rows_self{};            // token rows go to this rank's x_packed (its own experts only) ...
+  RowDispatch rows_all{};             // ... or to the x_packed of the expert's owner (filled when peers are attached)
+  TileBalance balance{};              // how expert_scan_kernel cuts the experts' rows into token blocks
+  bool pushed_bf16 = false;           // the rows of the last push travelled as bf16 (token-sliced forms on the bf16 wire)
   RouteShare share_self{};            // where routing rows go: this rank alone ...
   RouteShare share{};                 // ... or every rank of the group (filled when peers are attached)
   int route_step = 0;                 // number of shared routings so far (flag D carries it)
@@ -152,7 +156,7 @@ GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
   a.map_w = mlp1 ? w.map_w1 : w.map_w2;
   a.map_act = mlp1 ? ctx->map_x : ctx->map_h;
   a.offsets = ctx->rb.offsets;
-  a.tb_prefix = ctx->rb.tb_prefix;
+  a.tb_prefix = mlp1 ? ctx->rb.tb_prefix : ctx->rb.tb_prefix2;
   a.e_begin = ctx->d.e_begin;
   a.n_local = ctx->n_local;
   a.n_feat = mlp1 ? ctx->d.I : ctx->d.H;
@@ -176,7 +180,9 @@ GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
 
 extern "C" {
 
-const char *gptoss_version(void) { return "gptoss_b200 0.1 sm_100a"; }
+const char *gptoss_version(void) { return "gptoss_b200 0.2 sm_100a"; }
+
+uint64_t gptoss_launch_count(void) { return launch_counter().load(); }
 
 int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int world, int max_tokens,
                       int wire_dtype, gptoss_ctx **out) {
@@ -210,6 +216,10 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->layers.resize(dims->n_layers);
   ctx->peers.timeout_ns = 2000000000ull;
   if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
+  ctx->balance.sm_count = ctx->sm_count;
+  ctx->balance.nft1 = (dims->intermediate + kTileF - 1) / kTileF;
+  ctx->balance.nft2 = dims->hidden <= kTileF ? 1 : (dims->hidden + 2 * kTileF - 1) / (2 * kTileF);
+  if (const char *e = getenv("GPTOSS_TOKEN_BLOCK")) ctx->balance.force_rows = atoi(e);  // measurement aid: fixed token-block size
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
   const size_t P = T * k, nblk = (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock;
@@ -222,7 +232,7 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->rb.offsets, E + 1));
   A(dev_alloc(&ctx->rb.sorted, P));
   A(dev_alloc(&ctx->rb.tb_prefix, E + 1));
-  A(dev_alloc(&ctx->x_packed, P * H));
+  A(dev_alloc(&ctx->rb.tb_prefix2, E + 1));
   A(dev_alloc(&ctx->gate_up, P * I));
   ctx->sym_delta_off = 1024;
   ctx->sym_y_off = ctx->sym_delta_off + ((T * H * sizeof(float) + 1023) & ~(size_t)1023);
@@ -230,7 +240,8 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->sym_tw_off = up(ctx->sym_y_off + P * H * sizeof(float));
   ctx->sym_ti_off = up(ctx->sym_tw_off + P * sizeof(float));
   ctx->sym_hist_off = up(ctx->sym_ti_off + P * sizeof(int));
-  ctx->sym_bytes = up(ctx->sym_hist_off + nblk * E * sizeof(int));
+  ctx->sym_xp_off = up(ctx->sym_hist_off + nblk * E * sizeof(int));
+  ctx->sym_bytes = up(ctx->sym_xp_off + P * H * sizeof(__nv_bfloat16));
   A(cudaMalloc(reinterpret_cast<void **>(&ctx->sym), ctx->sym_bytes));
   if (e == cudaSuccess) A(cudaMemset(ctx->sym, 0, 1024));
   if (e == cudaSuccess) {
@@ -238,13 +249,17 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
     ctx->rb.topk_w = reinterpret_cast<float *>(ctx->sym + ctx->sym_tw_off);
     ctx->rb.topk_i = reinterpret_cast<int *>(ctx->sym + ctx->sym_ti_off);
     ctx->rb.blk_hist = reinterpret_cast<int *>(ctx->sym + ctx->sym_hist_off);
+    ctx->x_packed = reinterpret_cast<__nv_bfloat16 *>(ctx->sym + ctx->sym_xp_off);
+    ctx->rows_self.n = 1;
+    ctx->rows_self.experts_per_rank = ctx->n_local;
+    ctx->rows_self.xp[0] = ctx->x_packed;
     ctx->share_self.n = 1;
     ctx->share_self.topk_w[0] = ctx->rb.topk_w;
     ctx->share_self.topk_i[0] = ctx->rb.topk_i;
     ctx->share_self.blk_hist[0] = ctx->rb.blk_hist;
   }
-  A(dev_alloc(&ctx->comm_counter, 2));  // [0] exchange kernels, [1] shared routing
-  if (e == cudaSuccess) A(cudaMemset(ctx->comm_counter, 0, 2 * sizeof(int)));
+  A(dev_alloc(&ctx->comm_counter, 4));  // [0] exchange kernels, [1] shared routing, [2] row dispatch
+  if (e == cudaSuccess) A(cudaMemset(ctx->comm_counter, 0, 4 * sizeof(int)));
   A(dev_alloc(&ctx->status, kStatusWords));
   A(dev_alloc(&ctx->t_stage, T * H));
   A(dev_alloc(&ctx->x_stage, T * H));
@@ -273,7 +288,7 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->rb.offsets);
   cudaFree(ctx->rb.sorted);
   cudaFree(ctx->rb.tb_prefix);
-  cudaFree(ctx->x_packed);
+  cudaFree(ctx->rb.tb_prefix2);
   cudaFree(ctx->gate_up);
   for (int r = 0; r < kMaxRanks; ++r)
     if (ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
@@ -454,9 +469,9 @@ static int route_rows(gptoss_ctx *ctx, int layer, int T, const void *rows, int f
 // Counting sort of the whole batch from the routing rows present in this rank's buffers + gather of the token rows
 // of this rank's experts.
 static int route_group(gptoss_ctx *ctx, int T, const void *t_full, cudaStream_t s) {
-  CK(launch_expert_scan(ctx->rb, T, ctx->d, s));
-  CK(launch_scatter_gather(static_cast<const __nv_bfloat16 *>(t_full), ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base,
-                           ctx->rb.sorted, ctx->x_packed, s));
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, s));
+  CK(launch_scatter_gather(static_cast<const __nv_bfloat16 *>(t_full), 0, T, ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base,
+                           ctx->rb.sorted, ctx->rows_self, s));
   return GPTOSS_OK;
 }
 
@@ -546,7 +561,9 @@ static int check_attached(gptoss_ctx *ctx) {
   return GPTOSS_OK;
 }
 
-int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) {
+// Down GEMM whose epilogue stores each gate-weighted row into the y_pairs buffer of the token's owner; bf16: the rows
+// travel (and are kept) as bf16, the owner still sums them in fp32.
+static int push_rows(gptoss_ctx *ctx, int layer, bool bf16, void *stream) {
   int rc = check_attached(ctx);
   if (rc) return rc;
   if ((rc = check_layer(ctx, layer, true))) return rc;
@@ -555,6 +572,8 @@ int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int step = ++ctx->comm_step;
   GemmArgs a = gemm_args(ctx, ctx->layers[layer], false);
+  a.out_bf16 = bf16 ? 1 : 0;
+  ctx->pushed_bf16 = bf16;
   a.n_owners = ctx->world;
   a.slice_tokens = slice_rows(ctx->cur_T, ctx->world);
   for (int r = 0; r < ctx->world; ++r) {
@@ -566,6 +585,8 @@ int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) {
   CK(launch_grouped_mlp2(a, ctx->sm_count, s));
   return GPTOSS_OK;
 }
+
+int gptoss_moe_push_to_owners(gptoss_ctx *ctx, int layer, void *stream) { return push_rows(ctx, layer, false, stream); }
 
 int gptoss_moe_owner_combine(gptoss_ctx *ctx, void *stream) {
   int rc = check_attached(ctx);
@@ -650,7 +671,67 @@ int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream) {
   if (rc) return rc;
   if (T == 0) return GPTOSS_OK;
   if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
-  return gptoss_moe_push_to_owners(ctx, layer, stream);
+  return push_rows(ctx, layer, ctx->wire == GPTOSS_WIRE_BF16, stream);
+}
+
+// ---- dispatch form of the token-sliced block: only the rows an expert needs cross NVLink ------------------------
+int gptoss_moe_dispatch_route(gptoss_ctx *ctx, int layer, int T, const void *t_slice_dev_bf16, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  CK(cudaSetDevice(ctx->device));
+  ctx->cur_T = T;
+  if (T == 0) return GPTOSS_OK;
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(ctx, T, &first, &n);
+  if (n > 0 && !t_slice_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
+  ctx->share.step = ++ctx->route_step;
+  return route_rows(ctx, layer, T, t_slice_dev_bf16, first, n, ctx->share, static_cast<cudaStream_t>(stream));
+}
+
+int gptoss_moe_dispatch_rows(gptoss_ctx *ctx, int layer, int T, const void *t_slice_dev_bf16, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
+  if ((rc = check_T(ctx, T))) return rc;
+  if (T != ctx->cur_T || ctx->route_step == 0) return ctx->fail(GPTOSS_ERR_STATE, "dispatch_rows without a matching dispatch_route");
+  CK(cudaSetDevice(ctx->device));
+  if (T == 0) return GPTOSS_OK;
+  int first = 0, n = 0;
+  gptoss_moe_slice_bounds(ctx, T, &first, &n);
+  if (n > 0 && !t_slice_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
+  if (n > 0 && (reinterpret_cast<uintptr_t>(t_slice_dev_bf16) & 15)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "slice must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CK(launch_wait_flags(ctx->peers, 0, ctx->route_step, ctx->status, s));  // every rank's routing rows have arrived
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, s));
+  RowDispatch rd = ctx->rows_all;
+  rd.step = ctx->pending_gather = ++ctx->gather_step;
+  // a rank without tokens still places the pair ids and raises its flag
+  CK(launch_scatter_gather(n > 0 ? static_cast<const __nv_bfloat16 *>(t_slice_dev_bf16) : nullptr, first, n, ctx->rb.topk_i, T, ctx->d,
+                           ctx->rb.blk_base, ctx->rb.sorted, rd, s));
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_dispatch_push(gptoss_ctx *ctx, int layer, void *stream) {
+  int rc = check_attached(ctx);
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, true))) return rc;
+  if (ctx->cur_T > 0 && ctx->pending_gather == 0) return ctx->fail(GPTOSS_ERR_STATE, "dispatch_push without a matching dispatch_rows");
+  CK(cudaSetDevice(ctx->device));
+  if (ctx->cur_T == 0) return GPTOSS_OK;
+  CK(launch_wait_flags(ctx->peers, ctx->pending_gather, 0, ctx->status, static_cast<cudaStream_t>(stream)));  // every rank's rows have arrived
+  ctx->pending_gather = 0;
+  if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, stream))) return rc;
+  return push_rows(ctx, layer, ctx->wire == GPTOSS_WIRE_BF16, stream);
+}
+
+int gptoss_moe_forward_dispatch(gptoss_ctx *ctx, int layer, int T, const void *t_slice_dev_bf16, float *x_slice_dev, void *stream) {
+  int rc = gptoss_moe_dispatch_route(ctx, layer, T, t_slice_dev_bf16, stream);
+  if (rc || T == 0) return rc;
+  if ((rc = gptoss_moe_dispatch_rows(ctx, layer, T, t_slice_dev_bf16, stream))) return rc;
+  if ((rc = gptoss_moe_dispatch_push(ctx, layer, stream))) return rc;
+  return gptoss_moe_sliced_combine(ctx, x_slice_dev, stream);
 }
 
 int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream) {
@@ -661,7 +742,7 @@ int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream)
   if (n > 0 && !x_slice_dev) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
   CK(cudaSetDevice(ctx->device));
   if (ctx->cur_T == 0) return GPTOSS_OK;
-  CK(launch_combine_owner_slice(ctx->peers, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, x_slice_dev, ctx->status,
+  CK(launch_combine_owner_slice(ctx->peers, ctx->pushed_bf16, ctx->cur_T, ctx->d.H, ctx->d.k, ctx->comm_step, x_slice_dev, ctx->status,
                                 ctx->sm_count, static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }
@@ -772,9 +853,9 @@ int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint
   CK(cudaStreamWaitEvent(ctx->s_copy, ctx->ev_t, 0));  // the residual rows follow the activations on the copy engine
   if (n) CK(cudaMemcpyAsync(ctx->x_stage, x_host_slice, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
   CK(cudaEventRecord(ctx->ev_x, ctx->s_copy));
-  if ((rc = gptoss_moe_gather_rows(ctx, T, ctx->t_stage, ctx->s_main))) return rc;
-  if ((rc = gptoss_moe_sliced_route(ctx, layer, T, ctx->s_main))) return rc;
-  if ((rc = gptoss_moe_sliced_push(ctx, layer, T, ctx->s_main))) return rc;
+  if ((rc = gptoss_moe_dispatch_route(ctx, layer, T, ctx->t_stage, ctx->s_main))) return rc;
+  if ((rc = gptoss_moe_dispatch_rows(ctx, layer, T, ctx->t_stage, ctx->s_main))) return rc;
+  if ((rc = gptoss_moe_dispatch_push(ctx, layer, ctx->s_main))) return rc;
   CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
   if ((rc = gptoss_moe_sliced_combine(ctx, ctx->x_stage, ctx->s_main))) return rc;
   if (n) CK(cudaMemcpyAsync(x_host_slice, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_main));
@@ -794,6 +875,12 @@ static void set_share(gptoss_ctx *ctx, int r, uint8_t *base) {
   sh.topk_i[r] = reinterpret_cast<int *>(base + ctx->sym_ti_off);
   sh.blk_hist[r] = reinterpret_cast<int *>(base + ctx->sym_hist_off);
   sh.flags[r] = reinterpret_cast<int *>(base) + 3 * kMaxRanks + ctx->rank;
+  RowDispatch &rd = ctx->rows_all;
+  rd.n = ctx->world;
+  rd.experts_per_rank = ctx->n_local;
+  rd.counter = ctx->comm_counter + 2;
+  rd.xp[r] = reinterpret_cast<__nv_bfloat16 *>(base + ctx->sym_xp_off);
+  rd.flags[r] = reinterpret_cast<int *>(base) + 2 * kMaxRanks + ctx->rank;  // flag C of this rank on rank r
 }
 
 int gptoss_comm_export(gptoss_ctx *ctx, void *handle_out) {
@@ -895,10 +982,19 @@ int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int 
   RouteBuffers rb = ctx->rb;  // block histograms/bases live in the context scratch; results go to the caller
   rb.offsets = offsets_dev;
   rb.sorted = sorted_pair_ids_dev;
+  rb.tb_prefix = rb.tb_prefix2 = nullptr;  // the token-block prefixes of the context's own batch stay as they are
   CK(launch_pair_hist(topk_i_dev, T, ctx->d, rb.blk_hist, s));
-  CK(launch_expert_scan(rb, T, ctx->d, s));
-  CK(launch_scatter_gather(nullptr, topk_i_dev, T, ctx->d, rb.blk_base, rb.sorted, nullptr, s));
+  CK(launch_expert_scan(rb, T, ctx->d, ctx->balance, s));
+  CK(launch_scatter_gather(nullptr, 0, 0, topk_i_dev, T, ctx->d, rb.blk_base, rb.sorted, RowDispatch{}, s));
   return GPTOSS_OK;
+}
+
+// sample_argmax (run.cpp:739-750) on caller-supplied device rows
+int gptoss_argmax_rows(const float *logits_dev, int B, int V, int *next_dev, void *stream) {
+  if (B < 0 || V <= 0) return GPTOSS_ERR_BAD_ARG;
+  if (B == 0) return GPTOSS_OK;
+  if (!logits_dev || !next_dev) return GPTOSS_ERR_BAD_ARG;
+  return launch_argmax(logits_dev, B, V, next_dev, static_cast<cudaStream_t>(stream)) == cudaSuccess ? GPTOSS_OK : GPTOSS_ERR_CUDA;
 }
 
 // ---- taps --------------------------------------------------------------------------------------------------------

@@ -178,26 +178,32 @@ __global__ void __launch_bounds__(256) slice_copy_gather_kernel(PeerTable pt, in
 
 // Returns once every rank has raised flag C to gather_step (its slice of the gathered activations has arrived) and
 // flag D to route_step (the routing of its token slice has arrived); a step of 0 skips that flag.
+//
+// The successor is released only AFTER the waits: a kernel that became resident while this one still polled would
+// sit in its own (poll-count bounded) mbarrier waits for as long as the slowest peer takes, and could give up there
+// although the peer is well inside the wall-time limit of the flag wait.
 __global__ void wait_flags_kernel(PeerTable pt, int gather_step, int route_step, int *status) {
   pdl_wait();
-  pdl_launch_dependents();
   if (gather_step > 0) wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, gather_step, pt.timeout_ns, status, 0x2300);
   if (route_step > 0) wait_all_ranks(pt.flags[pt.rank] + 3 * kMaxRanks, pt.world, route_step, pt.timeout_ns, status, 0x2600);
+  pdl_launch_dependents();
 }
 
 // Device-side rendezvous of the ranks (no data): raises this rank's flag C everywhere, then waits for everyone's.
 __global__ void rendezvous_kernel(PeerTable pt, int step, int *status) {
   pdl_wait();
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     __threadfence_system();
     for (int r = 0; r < pt.world; ++r) st_relaxed_sys(pt.flags[r] + 2 * kMaxRanks + pt.rank, step);
   }
   __syncthreads();
   wait_all_ranks(pt.flags[pt.rank] + 2 * kMaxRanks, pt.world, step, pt.timeout_ns, status, 0x2500);
+  pdl_launch_dependents();  // after the wait, like wait_flags_kernel
 }
 
 // Token-sliced form, owner side: x_slice[i,:] += ((s0+s1)+s2)+s3 for the rows of this rank's slice, slots in order.
+// BF16: the pushed rows are bf16 (same indexing, half the bytes); the sum is fp32 either way.
+template <bool BF16>
 __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, int T, int H, int k, int step,
                                                                   float *__restrict__ x_slice, int *status) {
   pdl_wait();
@@ -207,13 +213,14 @@ __global__ void __launch_bounds__(256) combine_owner_slice_kernel(PeerTable pt, 
   const int h4 = H >> 2;
   const size_t total = (size_t)max(0, b1 - b0) * h4;
   const float4 *y = reinterpret_cast<const float4 *>(pt.y[pt.rank]);
+  const uint2 *yb = reinterpret_cast<const uint2 *>(pt.y[pt.rank]);
   float4 *xp = reinterpret_cast<float4 *>(x_slice);
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int b = b0 + (int)(i / h4), c = (int)(i % h4);
     const size_t row4 = (size_t)b * k * h4 + c;
-    float4 a = y[row4];
+    float4 a = BF16 ? unpack_bf16x4(yb[row4]) : y[row4];
     for (int j = 1; j < k; ++j) {
-      const float4 v = y[row4 + (size_t)j * h4];
+      const float4 v = BF16 ? unpack_bf16x4(yb[row4 + (size_t)j * h4]) : y[row4 + (size_t)j * h4];
       a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
     }
     float4 o = xp[i];
@@ -272,14 +279,15 @@ cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaSt
   return launch_chain(rendezvous_kernel, dim3(1), dim3(32), 0, s, pt, step, status);
 }
 
-cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
-                                       int sm_count, cudaStream_t s) {
+cudaError_t launch_combine_owner_slice(const PeerTable &pt, bool bf16_rows, int T, int H, int k, int step, float *x_slice,
+                                       int *status, int sm_count, cudaStream_t s) {
   const int slice = slice_rows(T, pt.world);
   const size_t total = (size_t)slice * (H >> 2);
   int blocks = (int)((total + 255) / 256);
   if (blocks > sm_count * 16) blocks = sm_count * 16;
   if (blocks < 1) blocks = 1;
-  return launch_chain(combine_owner_slice_kernel, dim3(blocks), dim3(256), 0, s, pt, T, H, k, step, x_slice, status);
+  return launch_chain(bf16_rows ? combine_owner_slice_kernel<true> : combine_owner_slice_kernel<false>, dim3(blocks), dim3(256), 0, s,
+                      pt, T, H, k, step, x_slice, status);
 }
 
 }  // namespace gptoss

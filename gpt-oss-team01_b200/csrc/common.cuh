@@ -34,7 +34,28 @@ struct RouteBuffers {
   int *blk_base;        // [n_route_blocks, E]   global start row of each block's pairs per expert
   int *offsets;         // [E+1]
   int *sorted;          // [T*k]
-  int *tb_prefix;       // [E_local+1]   cumulative count of token blocks (kMaxTileTokens rows) of local experts
+  int *tb_prefix;       // [E_local+1]   cumulative count of token blocks of the local experts, as the gate/up GEMM cuts them
+  int *tb_prefix2;      // [E_local+1]   the same for the down GEMM (it has half as many feature tiles, so another cut may
+                        //               fill the rounds of the persistent CTAs better); null = not wanted
+};
+
+// What the prefix-sum kernel needs to choose the token-block size of the two expert GEMMs (see expert_scan_kernel).
+struct TileBalance {
+  int sm_count;   // persistent CTAs of a GEMM launch
+  int nft1, nft2; // feature tiles per (expert, token block) of the gate/up and of the down GEMM
+  int force_rows; // > 0: use this block size for both (measurement aid)
+};
+
+// Where the gathered token rows go.  n == 1: into this rank's own x_packed, rows of its experts only.  n > 1 (dispatch
+// of a token slice): the row of pair (token, slot) goes to the x_packed of the rank that owns the slot's expert, at its
+// position in the global sorted order; the last block raises flags[r] = step on every rank when step > 0.
+struct RowDispatch {
+  int n;
+  int experts_per_rank;
+  int step;
+  int *counter;
+  __nv_bfloat16 *xp[16];
+  int *flags[16];
 };
 
 // Tokens per owner slice of a batch of T tokens over `world` ranks: contiguous slices of equal size, a multiple of the

@@ -21,8 +21,10 @@
 // of this launch (read from the expert offsets, rounded to 32 rows), and the ring takes as many stages as
 // fit into shared memory (decode: 4 x 52 KiB).
 //
-// Every mbarrier wait is bounded: when a wait gives up the CTA raises an abort flag, records a
-// time-out in the status words, drains its outstanding copies, frees its TMEM and returns.
+// Every mbarrier wait is bounded: when a wait gives up the CTA raises an abort flag and records a time-out in
+// the status words.  Every role then leaves its tile loop at once: the producer waits (bounded) for the copies
+// it has armed, the MMA thread for the MMAs it has issued, the epilogue warps agree on leaving through a
+// barrier reduction (so their named-barrier counts stay equal); then the CTA frees its TMEM and returns.
 #include <cstdlib>
 
 #include "kernels.cuh"
@@ -49,7 +51,6 @@ constexpr int kRingBytes = 216 * 1024;
 template <int NA, bool GLU>
 struct TileCfg {
   static constexpr int kAStageBytes = NA * kATileBytes;
-  static constexpr int kAccBuffers = (NA == 2) ? 1 : 2;   // two tiles fill all 512 TMEM columns at 256 tokens
   static constexpr int kMetaTokens = GLU ? 1 : kMaxTileTokens;  // pair/weight staging only for the down projection
   static constexpr int kTileFeat = (NA == 2 && !GLU) ? 2 * kTileF : kTileF;  // output features per tile
   static constexpr int kSlabs = GLU ? 2 : 1;                // weight slabs per expert in the tensor map
@@ -61,12 +62,13 @@ struct Ctrl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t mma_done;  // abort path only: completion of every MMA issued so far
   uint32_t tmem_base;
   int abort;
   int max_rows;
   int tbp[kMaxExperts + 1];
   int off[kMaxExperts + 1];
-  float *dst_s[2][TileCfg<NA, GLU>::kMetaTokens];  // mlp2: destination row of each token column (local or peer)
+  char *dst_s[2][TileCfg<NA, GLU>::kMetaTokens];   // mlp2: destination row of each token column (local or peer)
   float w_s[2][TileCfg<NA, GLU>::kMetaTokens];     // mlp2: gate weight of each token column
 };
 
@@ -102,6 +104,32 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
 }
 
+// Lanes 2i and 2i+1 hold two adjacent output features of the token columns j and j+1.  After the exchange the even
+// lane holds both features of column j and the odd lane both features of column j+1 (lo = even feature), so that
+// every lane stores two adjacent elements at once: half the store instructions, twice the bytes each.
+__device__ __forceinline__ void pair_exchange(float vj, float vj1, bool odd, float &lo, float &hi) {
+  const float recv = __shfl_xor_sync(0xffffffffu, odd ? vj : vj1, 1);
+  lo = odd ? recv : vj;
+  hi = odd ? vj1 : recv;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&p);
+}
+// OR of `pred` over the eight epilogue warps (named barrier 1): every epilogue thread gets the same answer
+__device__ __forceinline__ bool epilogue_any(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
 template <int NA, bool GLU>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmArgs a) {
   using Cfg = TileCfg<NA, GLU>;
@@ -129,6 +157,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
       mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpilogueThreads);
     }
+    mbar_init(smem_u32(&ctrl->mma_done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -158,6 +187,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   const int b_rows = max(kTokChunk, (ctrl->max_rows + kTokChunk - 1) / kTokChunk * kTokChunk);
   const int stage_bytes = Cfg::kAStageBytes + b_rows * kBlockK * 2;
   const int n_stages = min(kMaxStages, kRingBytes / stage_bytes);
+  // accumulators: each weight tile of a stage owns cols_per_tile TMEM columns; when no tile of this launch has more
+  // than 128 token rows two sets fit into the 512 columns and the epilogue of a tile overlaps the MMAs of the next
+  const int cols_per_tile = ctrl->max_rows <= 128 ? 128 : kMaxTileTokens;
+  const int acc_stride = NA * cols_per_tile;
+  const int n_acc = min(2, kTmemCols / acc_stride);
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -200,8 +234,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const int n_chunks = (n_mma + kTokChunk - 1) / kTokChunk;
         const uint32_t tx = Cfg::kAStageBytes + n_chunks * kBChunkBytes;
+        bool ok = true;
         for (int kb = (idx == (int)blockIdx.x) ? pre : 0; kb < a.k_blocks; ++kb) {
-          mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x100 | stage);
+          if (!(ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x100 | stage))) break;
           const uint32_t bar = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = ring + stage * stage_bytes;
           armed |= 1u << stage;
@@ -219,8 +254,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             phase ^= 1u;
           }
         }
+        if (!ok) break;  // aborting: arm nothing more
       }
-      // drain: every armed stage must have landed before the CTA may exit (bounded)
+      // drain: every armed stage must have landed before the CTA may exit (bounded).  A stage is re-armed only
+      // after its previous phase was consumed, so only the last armed phase of a stage can still be in flight.
       for (int s = 0; s < n_stages; ++s)
         if (armed & (1u << s)) {
           const uint32_t par = (last_par >> s) & 1u;
@@ -238,11 +275,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const uint32_t idesc = umma_idesc(n_mma);
-        mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1u, &ctrl->abort, a.status, 0x200 | acc);
+        if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1u, &ctrl->abort, a.status, 0x200 | acc)) break;
         tc_fence_after();
-        const uint32_t d0 = tmem_base + (uint32_t)(acc * kMaxTileTokens);
+        const uint32_t d0 = tmem_base + (uint32_t)(acc * acc_stride);
+        bool ok = true;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x300 | stage);
+          if (!(ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x300 | stage))) break;
           tc_fence_after();
           const uint32_t sa = ring + stage * stage_bytes;
           const uint64_t da0 = smem_desc_sw128(sa);
@@ -252,7 +290,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           for (int k = 0; k < kBlockK / 16; ++k) {
             const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
             umma_bf16(d0, da0 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
-            if (NA == 2) umma_bf16(d0 + kMaxTileTokens, da1 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            if (NA == 2) umma_bf16(d0 + cols_per_tile, da1 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));
           if (++stage == n_stages) {
@@ -260,11 +298,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             phase ^= 1u;
           }
         }
+        if (!ok) break;
         umma_commit(smem_u32(&ctrl->tmem_full[acc]));
-        if (++acc == Cfg::kAccBuffers) {
+        if (++acc == n_acc) {
           acc = 0;
           acc_phase ^= 1u;
         }
+      }
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
+        // aborting: the MMAs issued so far must have retired before TMEM and the ring are given up (bounded)
+        umma_commit(smem_u32(&ctrl->mma_done));
+        for (uint32_t i = 0; i < kSpinLimit; ++i)
+          if (mbar_try_wait(smem_u32(&ctrl->mma_done), 0)) break;
       }
     }
   } else {
@@ -276,19 +321,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     uint32_t acc_phase = 0;
     Tile t;
     const uint64_t pol_keep = l2_policy_evict_last();  // the outputs are read again by the next kernel
+    const bool odd = lane & 1;
+    const size_t esize = a.out_bf16 ? 2 : 4;  // mlp2 output element: fp32, or bf16 on the bf16 wire
     for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
       if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
+      // Top of every tile: all epilogue threads meet and learn whether any role gave up.  The answer is the same for
+      // all of them, so they leave together; the meeting also means that every thread has left the previous tile
+      // before its staging slots (dst_s / w_s) are overwritten below.
+      if (epilogue_any(*reinterpret_cast<volatile int *>(&ctrl->abort) != 0)) break;
       const int f = t.f0 + q * 32 + lane;
-      const bool f_ok = f < a.n_feat;
+      const int fe = f & ~1;                  // the even feature of this lane pair
+      const bool f_ok = f < a.n_feat;         // n_feat is even: both features of a pair are valid or neither is
       if constexpr (!GLU) {
-        // one staging buffer per accumulator buffer: with a single one, every epilogue thread must have left the
-        // previous tile before its slots are overwritten
-        if (Cfg::kAccBuffers == 1) epilogue_bar_sync();
         for (int n = et; n < t.n_valid; n += kEpilogueThreads) {
           const int pair = a.sorted[t.row0 + n];
-          float *base = a.y_pairs;
-          if (a.n_owners > 1) base = a.y_owner[min(a.n_owners - 1, (pair / a.top_k) / a.slice_tokens)];
-          ctrl->dst_s[acc][n] = base + (size_t)pair * a.n_feat;
+          char *base = reinterpret_cast<char *>(a.y_pairs);
+          if (a.n_owners > 1) base = reinterpret_cast<char *>(a.y_owner[min(a.n_owners - 1, (pair / a.top_k) / a.slice_tokens)]);
+          ctrl->dst_s[acc][n] = base + (size_t)pair * a.n_feat * esize;
           ctrl->w_s[acc][n] = a.topk_w[pair];
         }
         epilogue_bar_sync();
@@ -298,49 +347,63 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const float bias1 = (GLU && f_ok)            ? a.bias_b[(size_t)t.e * a.n_feat + f]
                           : (f1_ok && a.bias_a) ? a.bias_a[(size_t)t.e * a.n_feat + f + kTileF]
                                                 : 0.f;
-      mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
+      const bool got = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
       tc_fence_after();
-      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kMaxTileTokens);
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_stride);
       // 16 token columns at a time, alternating between the two warps of the quadrant; the 16 values of a
       // chunk are independent chains, computed branch-free so that they overlap
-      for (int c0 = half * 16; c0 < t.n_valid; c0 += 32) {
+      for (int c0 = half * 16; got && c0 < t.n_valid; c0 += 32) {
         uint32_t r0[16], r1[16];
         tmem_ld16(tbase + c0, r0);
-        if (NA == 2) tmem_ld16(tbase + kMaxTileTokens + c0, r1);
+        if (NA == 2) tmem_ld16(tbase + cols_per_tile + c0, r1);
         tmem_ld_wait();
         float v[16];
         if constexpr (GLU) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             v[j] = swiglu(__uint_as_float(r0[j]) + bias0, __uint_as_float(r1[j]) + bias1, a.limit);
-          __nv_bfloat16 *dst = a.gate_up + (size_t)(t.row0 + c0) * a.n_feat + f;
+          __nv_bfloat16 *dst = a.gate_up + (size_t)(t.row0 + c0) * a.n_feat + fe;
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(v[j], v[j + 1]);
-            if (f_ok && c0 + j < t.n_valid) st_b16_hint(dst + (size_t)j * a.n_feat, __bfloat16_as_ushort(pk.x), pol_keep);
-            if (f_ok && c0 + j + 1 < t.n_valid) st_b16_hint(dst + (size_t)(j + 1) * a.n_feat, __bfloat16_as_ushort(pk.y), pol_keep);
+            float lo, hi;
+            pair_exchange(v[j], v[j + 1], odd, lo, hi);
+            const int col = j + (odd ? 1 : 0);
+            if (f_ok && c0 + col < t.n_valid) st_b32_hint(dst + (size_t)col * a.n_feat, pack_bf16x2(lo, hi), pol_keep);
           }
         } else {
-          float *pr[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            pr[j] = ctrl->dst_s[acc][c0 + j];
-            v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
+          for (int j = 0; j < 16; ++j) v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            float lo, hi;
+            pair_exchange(v[j], v[j + 1], odd, lo, hi);
+            const int col = c0 + j + (odd ? 1 : 0);
+            char *row = ctrl->dst_s[acc][col];
+            if (f_ok && col < t.n_valid) {
+              if (a.out_bf16) st_b32_hint(row + (size_t)fe * 2, pack_bf16x2(lo, hi), pol_keep);
+              else st_f32x2_hint(row + (size_t)fe * 4, lo, hi, pol_keep);
+            }
           }
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (f_ok && c0 + j < t.n_valid) st_f32_hint(pr[j] + f, v[j], pol_keep);
           if constexpr (NA == 2) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (f1_ok && c0 + j < t.n_valid)
-                st_f32_hint(pr[j] + f + kTileF, (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j], pol_keep);
+            for (int j = 0; j < 16; ++j) v[j] = (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float lo, hi;
+              pair_exchange(v[j], v[j + 1], odd, lo, hi);
+              const int col = c0 + j + (odd ? 1 : 0);
+              char *row = ctrl->dst_s[acc][col];
+              if (f1_ok && col < t.n_valid) {
+                if (a.out_bf16) st_b32_hint(row + (size_t)(fe + kTileF) * 2, pack_bf16x2(lo, hi), pol_keep);
+                else st_f32x2_hint(row + (size_t)(fe + kTileF) * 4, lo, hi, pol_keep);
+              }
+            }
           }
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
-      if (++acc == Cfg::kAccBuffers) {
+      if (++acc == n_acc) {
         acc = 0;
         acc_phase ^= 1u;
       }

@@ -3,6 +3,7 @@
 
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <utility>
 
@@ -19,6 +20,13 @@ inline bool pdl_enabled() {
   }();
   return on;
 }
+// Kernels this library has launched in this process (every launch goes through launch_chain or count_launch).
+inline std::atomic<uint64_t> &launch_counter() {
+  static std::atomic<uint64_t> n{0};
+  return n;
+}
+inline void count_launch() { launch_counter().fetch_add(1, std::memory_order_relaxed); }
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
   cudaLaunchConfig_t cfg = {};
@@ -31,6 +39,7 @@ cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
@@ -41,10 +50,10 @@ cudaError_t launch_router_topk(const float *partials, int n_splits, const float 
 cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
                                 cudaStream_t s);
 cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s);
-cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, cudaStream_t s);
-cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int T, const Dims &d,
-                                  const int *blk_base, int *sorted, __nv_bfloat16 *x_packed,
-                                  cudaStream_t s);
+cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, const TileBalance &tb, cudaStream_t s);
+// t: rows of tokens [t_first, t_first + t_count) (null: pair ids only)
+cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, int t_first, int t_count, const int *topk_i, int T, const Dims &d,
+                                  const int *blk_base, int *sorted, const RowDispatch &rd, cudaStream_t s);
 cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
                            int residual, int sm_count, cudaStream_t s);
 
@@ -72,8 +81,8 @@ cudaError_t launch_slice_copy_gather(const PeerTable &pt, int T, int H, const vo
 // waits for flag C >= gather_step and flag D >= route_step of every rank (a step of 0 skips that flag)
 cudaError_t launch_wait_flags(const PeerTable &pt, int gather_step, int route_step, int *status, cudaStream_t s);
 cudaError_t launch_rendezvous(const PeerTable &pt, int step, int *status, cudaStream_t s);
-cudaError_t launch_combine_owner_slice(const PeerTable &pt, int T, int H, int k, int step, float *x_slice, int *status,
-                                       int sm_count, cudaStream_t s);
+cudaError_t launch_combine_owner_slice(const PeerTable &pt, bool bf16_rows, int T, int H, int k, int step, float *x_slice,
+                                       int *status, int sm_count, cudaStream_t s);
 
 // router.cu
 struct RouterArgs {
@@ -110,6 +119,7 @@ struct GemmArgs {
   const float *bias_b;   // mlp1: up bias   [E_local, I];  mlp2: unused
   __nv_bfloat16 *gate_up;  // mlp1 out [P, I]
   float *y_pairs;          // mlp2 out [P, H] by pair id (local)
+  int out_bf16;            // mlp2: rows are stored as bf16 (same row/element indexing, half the bytes)
   float *y_owner[kMaxRanks];  // mlp2 with n_owners > 1: y_pairs of the rank that owns the token slice
   int n_owners;            // 1 = store locally; > 1 = push each row to its owner
   int slice_tokens;        // tokens per owner slice

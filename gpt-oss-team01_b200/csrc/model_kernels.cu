@@ -330,7 +330,9 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   }
 }
 
-// next[b] = index of the FIRST maximum of logits[b,:]   (run.cpp:739-750)
+// next[b] = index of the FIRST maximum of logits[b,:]   (run.cpp:739-750).  Like the reference's scan (which starts
+// from element 0 and replaces it only on a strict '>'), a row without any comparable maximum (all -inf or NaN, or a
+// NaN in front) yields index 0, never an index outside [0, V).
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ next) {
   __shared__ float bv[32];
   __shared__ int bi[32];
@@ -383,7 +385,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
         idx = oi;
       }
     }
-    if (threadIdx.x == 0) next[b] = idx;
+    if (threadIdx.x == 0) next[b] = (idx == 0x7fffffff || row[0] != row[0]) ? 0 : idx;
   }
 }
 

@@ -2,7 +2,8 @@
 // (bf16 x bf16 -> fp32).  Tokens are the UMMA M side (128 per CTA, one TMEM lane each), experts the N side
 // (E rounded up to 16, at most 256), K is split over gridDim.y CTAs so that even T = 1024 keeps ~64 SMs
 // streaming; the splits are summed in a fixed order by the top-k kernel, so the scores are bit-identical
-// on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs.
+// on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs; a role whose wait
+// gives up stops issuing work, and the kernel leaves the scores of its tile unwritten (the host sees the time-out).
 #include "kernels.cuh"
 #include "tcgen05.cuh"
 
@@ -19,6 +20,7 @@ struct RouterCtrl {
   uint64_t full[kRouterMaxStages];
   uint64_t empty[kRouterMaxStages];
   uint64_t tmem_full;
+  uint64_t mma_done;  // abort path only: completion of every MMA issued so far
   uint32_t tmem_base;
   int abort;
 };
@@ -39,6 +41,7 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
       mbar_init(smem_u32(&ctrl->empty[s]), 1);
     }
     mbar_init(smem_u32(&ctrl->tmem_full), 1);
+    mbar_init(smem_u32(&ctrl->mma_done), 1);
     ctrl->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -59,7 +62,7 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
       uint32_t phase = 0, armed = 0, last_par = 0;
       const uint32_t tx = kRouterATile + a.n_cols * kBlockK * 2;
       for (int kb = kb0; kb < kb1; ++kb) {
-        mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x1100 | stage);
+        if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x1100 | stage)) break;
         const uint32_t bar = smem_u32(&ctrl->full[stage]);
         const uint32_t sa = tiles_base + stage * a.stage_bytes;
         armed |= 1u << stage;
@@ -85,7 +88,7 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
       uint32_t phase = 0;
       const uint32_t idesc = umma_idesc(a.n_cols);
       for (int kb = kb0; kb < kb1; ++kb) {
-        mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x1300 | stage);
+        if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x1300 | stage)) break;
         tc_fence_after();
         const uint32_t sa = tiles_base + stage * a.stage_bytes;
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + kRouterATile);
@@ -98,16 +101,23 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
           phase ^= 1u;
         }
       }
-      umma_commit(smem_u32(&ctrl->tmem_full));
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
+        // aborting: the MMAs issued so far must have retired before TMEM and the ring are given up (bounded)
+        umma_commit(smem_u32(&ctrl->mma_done));
+        for (uint32_t i = 0; i < kSpinLimit; ++i)
+          if (mbar_try_wait(smem_u32(&ctrl->mma_done), 0)) break;
+      } else {
+        umma_commit(smem_u32(&ctrl->tmem_full));
+      }
     }
   } else {
     const int q = warp & 3;
     const int b = row0 + q * 32 + lane;
-    mbar_wait(smem_u32(&ctrl->tmem_full), 0, &ctrl->abort, a.status, 0x1400);
+    const bool got = mbar_wait(smem_u32(&ctrl->tmem_full), 0, &ctrl->abort, a.status, 0x1400);
     tc_fence_after();
     float *dst = a.partials + ((size_t)blockIdx.y * a.T + b) * a.E;
     const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16);
-    for (int c0 = 0; c0 < a.n_cols; c0 += 16) {
+    for (int c0 = 0; got && c0 < a.n_cols; c0 += 16) {  // after an abort the accumulator is not read
       uint32_t r[16];
       tmem_ld16(tbase + c0, r);
       tmem_ld_wait();

@@ -208,9 +208,22 @@ __global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ 
 }
 
 // ---- prefix sums: expert offsets, per-block bases, token-block prefix for the GEMM tile scheduler -----
-__global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d) {
+// Token-block size of an expert GEMM.  The work items of a launch, (expert, token block, feature tile), go round-robin
+// over the persistent CTAs, so a launch takes (rounds of items) x (time of one item).  An item costs about its block's
+// rows, but not less than kItemFloorRows (below that the ring of weight tiles, whose stages have a fixed round trip,
+// bounds the item, not the MMAs), plus a fixed part (pipeline fill, epilogue).  One block size, a multiple of 16 in
+// [64, 256], is chosen for all local experts: expert e is cut into ceil(rows_e / size) blocks of equal size.  The
+// largest size wins ties, so a batch whose experts all fit one block is never cut (its weights are streamed once).
+constexpr int kItemFloorRows = 176;
+constexpr int kItemFixedRows = 32;
+constexpr int kBlockSizeChoices = 13;  // 256, 240, ..., 64
+
+__device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + size - 1) / size; }
+
+__global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d, TileBalance tb) {
   __shared__ int seg_sum[1024];
   __shared__ int off_s[kMaxExperts + 1];
+  __shared__ long long cost_s[2 * kBlockSizeChoices];
   const int E = d.E;
   const int nseg = 1024 / E;
   const int tid = threadIdx.x;
@@ -239,12 +252,6 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
   if (tid == 0) {
     off_s[0] = 0;
     for (int x = 0; x < E; ++x) off_s[x + 1] += off_s[x];
-    int tb = 0;
-    rb.tb_prefix[0] = 0;
-    for (int x = d.e_begin; x < d.e_end; ++x) {
-      tb += (off_s[x + 1] - off_s[x] + kMaxTileTokens - 1) / kMaxTileTokens;
-      rb.tb_prefix[x - d.e_begin + 1] = tb;
-    }
   }
   __syncthreads();
   if (tid <= E) rb.offsets[tid] = off_s[tid];
@@ -255,14 +262,53 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
       run += rb.blk_hist[(size_t)b * E + e];
     }
   }
+  // token-block prefix of each GEMM: lane g * 13 + c of warp 0 prices block size 256 - 16 c for GEMM g
+  if (tid < 2 * kBlockSizeChoices && rb.tb_prefix != nullptr) {
+    const int g = tid / kBlockSizeChoices, c = tid % kBlockSizeChoices;
+    const int size = kMaxTileTokens - 16 * c;
+    long long items = 0;
+    int max_rows = 0;
+    for (int x = d.e_begin; x < d.e_end; ++x) {
+      const int rows = off_s[x + 1] - off_s[x];
+      if (rows > 0) {
+        const int nb = blocks_of(rows, size);
+        items += nb;
+        max_rows = max(max_rows, (blocks_of(rows, nb) + 15) & ~15);
+      }
+    }
+    items *= g ? tb.nft2 : tb.nft1;
+    const long long rounds = (items + tb.sm_count - 1) / tb.sm_count;
+    cost_s[tid] = rounds * (max(max_rows, kItemFloorRows) + kItemFixedRows);
+  }
+  __syncthreads();
+  if ((tid == 0 || tid == kBlockSizeChoices) && rb.tb_prefix != nullptr) {
+    const int g = tid / kBlockSizeChoices;
+    int *out = g ? rb.tb_prefix2 : rb.tb_prefix;
+    if (out != nullptr) {
+      int best = 0;
+      for (int c = 1; c < kBlockSizeChoices; ++c)
+        if (cost_s[g * kBlockSizeChoices + c] < cost_s[g * kBlockSizeChoices + best]) best = c;
+      int size = kMaxTileTokens - 16 * best;
+      if (tb.force_rows > 0) size = min(kMaxTileTokens, max(16, tb.force_rows & ~15));
+      int n = 0;
+      out[0] = 0;
+      for (int x = d.e_begin; x < d.e_end; ++x) {
+        n += blocks_of(off_s[x + 1] - off_s[x], size);
+        out[x - d.e_begin + 1] = n;
+      }
+    }
+  }
 }
 
-// ---- stable scatter of pair ids (+ optional gather of the token rows of local experts) ---------------
-__global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat16 *__restrict__ t,
+// ---- stable scatter of pair ids (+ optional gather / dispatch of the token rows) ----------------------
+// Every block places the pair ids of its 8 tokens (all tokens of the batch: `sorted` is complete on every rank).
+// Rows: `t` holds the bf16 rows of tokens [t_first, t_first + t_count) (null = ids only); the row of each pair of
+// those tokens is copied to its position in x_packed — of this rank, for slots of its own experts (rd.n == 1), or of
+// the rank that owns the slot's expert (rd.n > 1: the dispatch half of the expert-parallel exchange, peer stores).
+__global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat16 *__restrict__ t, int t_first, int t_count,
                                                              const int *__restrict__ topk_i, int T, Dims d,
                                                              const int *__restrict__ blk_base,
-                                                             int *__restrict__ sorted,
-                                                             __nv_bfloat16 *__restrict__ x_packed) {
+                                                             int *__restrict__ sorted, RowDispatch rd) {
   __shared__ int ids[kTokensPerRouteBlock * kMaxTopK];
   __shared__ int pos_s[kTokensPerRouteBlock * kMaxTopK];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -287,21 +333,23 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
   }
   __syncthreads();
   // gather: blockDim.x / 256 warps share one token row (its 16-byte chunks interleaved), so that a block
-  // keeps enough loads in flight; the row is read once and written to each local slot
+  // keeps enough loads in flight; the row is read once and written to each slot that wants it
   const int wpt = blockDim.x >> 8;            // warps per token
   const int tok = warp / wpt, part = warp - tok * wpt;
   const int b = blockIdx.x * kTokensPerRouteBlock + tok;
-  if (t != nullptr && b < T) {
+  if (t != nullptr && b < T && b >= t_first && b < t_first + t_count) {
     const int nchunk = d.H >> 3;
-    const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)b * d.H);
-    uint4 *dst = reinterpret_cast<uint4 *>(x_packed);
-    int pos[kMaxTopK];
+    const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)(b - t_first) * d.H);
+    uint4 *dst[kMaxTopK];
 #pragma unroll
     for (int j = 0; j < kMaxTopK; ++j) {
-      pos[j] = -1;
+      dst[j] = nullptr;
       if (j < k) {
-        const int e = ids[tok * k + j];
-        if (e >= d.e_begin && e < d.e_end) pos[j] = pos_s[tok * k + j];
+        const int e = ids[tok * k + j], pos = pos_s[tok * k + j];
+        if (pos >= 0) {
+          if (rd.n > 1) dst[j] = reinterpret_cast<uint4 *>(rd.xp[min(rd.n - 1, e / rd.experts_per_rank)]) + (size_t)pos * nchunk;
+          else if (e >= d.e_begin && e < d.e_end) dst[j] = reinterpret_cast<uint4 *>(rd.xp[0]) + (size_t)pos * nchunk;
+        }
       }
     }
 #pragma unroll 4
@@ -309,7 +357,19 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
       const uint4 v = __ldg(src + c);
 #pragma unroll
       for (int j = 0; j < kMaxTopK; ++j)
-        if (pos[j] >= 0) dst[(size_t)pos[j] * nchunk + c] = v;
+        if (dst[j] != nullptr) dst[j][c] = v;
+    }
+  }
+  if (rd.step > 0) {  // stores ordered before the count by the barrier plus one system-scope fence (cumulative)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(reinterpret_cast<unsigned int *>(rd.counter), 1u);
+      if (prev == gridDim.x - 1) {
+        *rd.counter = 0;
+        __threadfence_system();
+        for (int r = 0; r < rd.n; ++r) st_relaxed_sys(rd.flags[r], rd.step);
+      }
     }
   }
 }
@@ -392,6 +452,7 @@ cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float 
   case G:                                                                     \
     topk_softmax_kernel<G><<<grid, block, 0, s>>>(scores, T, E, k, topk_w, topk_i); \
     break;
+  count_launch();
   switch (groups) {
     GPTOSS_TOPK_CASE(1)
     GPTOSS_TOPK_CASE(2)
@@ -409,19 +470,19 @@ cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float 
 }
 
 cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s) {
+  count_launch();
   pair_hist_kernel<<<route_blocks(T), 256, 0, s>>>(topk_i, T, d.k, d.E, blk_hist);
   return cudaGetLastError();
 }
 
-cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, cudaStream_t s) {
-  return launch_chain(expert_scan_kernel, dim3(1), dim3(1024), 0, s, rb, route_blocks(T), d);
+cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, const TileBalance &tb, cudaStream_t s) {
+  return launch_chain(expert_scan_kernel, dim3(1), dim3(1024), 0, s, rb, route_blocks(T), d, tb);
 }
 
-cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, const int *topk_i, int T, const Dims &d,
-                                  const int *blk_base, int *sorted, __nv_bfloat16 *x_packed,
-                                  cudaStream_t s) {
-  return launch_chain(scatter_gather_kernel, dim3(route_blocks(T)), dim3(t ? 1024 : 256), 0, s, t, topk_i, T, d,
-                      blk_base, sorted, x_packed);
+cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, int t_first, int t_count, const int *topk_i, int T, const Dims &d,
+                                  const int *blk_base, int *sorted, const RowDispatch &rd, cudaStream_t s) {
+  return launch_chain(scatter_gather_kernel, dim3(route_blocks(T)), dim3(t ? 1024 : 256), 0, s, t, t_first, t_count, topk_i, T,
+                      d, blk_base, sorted, rd);
 }
 
 cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,
@@ -493,14 +554,15 @@ extern "C" int gptoss_moe_build_offsets_noalloc(int T, int n_experts, int top_k,
   RouteBuffers rb{};
   rb.blk_hist = scratch;
   rb.blk_base = scratch + kNoAllocMaxEntries;
-  rb.tb_prefix = scratch + 2 * kNoAllocMaxEntries;
+  rb.tb_prefix = nullptr;  // no GEMM follows: the token-block prefixes are not computed
+  rb.tb_prefix2 = nullptr;
   rb.offsets = offsets_dev;
   rb.sorted = sorted_pair_ids_dev;
   // every entry of the scratch that the scan and the scatter read is first written by this call, so
   // nothing has to start at zero
   if (launch_pair_hist(topk_i_dev, T, d, rb.blk_hist, s) != cudaSuccess ||
-      launch_expert_scan(rb, T, d, s) != cudaSuccess ||
-      launch_scatter_gather(nullptr, topk_i_dev, T, d, rb.blk_base, rb.sorted, nullptr, s) != cudaSuccess)
+      launch_expert_scan(rb, T, d, TileBalance{1, 1, 1, 0}, s) != cudaSuccess ||
+      launch_scatter_gather(nullptr, 0, 0, topk_i_dev, T, d, rb.blk_base, rb.sorted, RowDispatch{}, s) != cudaSuccess)
     return noalloc_fail(GPTOSS_ERR_CUDA, "kernel launch failed");
   return GPTOSS_OK;
 }

@@ -212,6 +212,26 @@ class MoEBlock:
     def forward_sliced(self, layer, n_tokens, x_slice, stream=None):
         self._check(self.lib.gptoss_moe_forward_sliced(self._ctx, layer, n_tokens, _ptr(x_slice), _stream(stream)))
 
+    # -- dispatch form: token rows go only to the ranks whose experts they selected -----------------------------
+    def dispatch_route(self, layer, n_tokens, t_slice, stream=None):
+        """routes this rank's rows t_slice [slice count, H] (bf16 cuda) and stores the routing rows to every rank"""
+        self._check(self.lib.gptoss_moe_dispatch_route(self._ctx, layer, n_tokens, _ptr(t_slice) if t_slice is not None else None,
+                                                       _stream(stream)))
+
+    def dispatch_rows(self, layer, n_tokens, t_slice, stream=None):
+        """waits for every rank's routing rows; grouping of the batch; this rank's rows to the experts' owners"""
+        self._check(self.lib.gptoss_moe_dispatch_rows(self._ctx, layer, n_tokens, _ptr(t_slice) if t_slice is not None else None,
+                                                      _stream(stream)))
+
+    def dispatch_push(self, layer, stream=None):
+        """waits for every rank's rows; gate/up GEMM + SwiGLU; down GEMM pushing to the tokens' owners"""
+        self._check(self.lib.gptoss_moe_dispatch_push(self._ctx, layer, _stream(stream)))
+
+    def forward_dispatch(self, layer, n_tokens, t_slice, x_slice, stream=None):
+        """x_slice (+)= MoE(t_slice) for this rank's rows of a batch of n_tokens; every rank calls it"""
+        self._check(self.lib.gptoss_moe_forward_dispatch(self._ctx, layer, n_tokens, _ptr(t_slice) if t_slice is not None else None,
+                                                         _ptr(x_slice) if x_slice is not None else None, _stream(stream)))
+
     def forward_host_sliced(self, layer, n_tokens, t_bits_slice, x_slice):
         """Host buffers holding THIS RANK'S rows of a batch of n_tokens: t_bits_slice uint16 [n,H], x_slice fp32 [n,H]
         in/out.  Synchronous; every rank calls it."""
@@ -273,6 +293,11 @@ class MoEBlock:
         out = np.empty(shape, dt)
         self._check(self.lib.gptoss_read_tap(self._ctx, tap, _ptr(out), out.nbytes))
         return out
+
+
+def launch_count() -> int:
+    """kernels launched by the library in this process so far"""
+    return int(capi.load().gptoss_launch_count())
 
 
 def synth_normal_bf16(n, seed, tensor_id, sigma, start=0, device="cuda"):

@@ -185,7 +185,27 @@ int gptoss_moe_sliced_route(gptoss_ctx *ctx, int layer, int T, void *stream);
 int gptoss_moe_sliced_push(gptoss_ctx *ctx, int layer, int T, void *stream);
 int gptoss_moe_sliced_combine(gptoss_ctx *ctx, float *x_slice_dev, void *stream);
 int gptoss_moe_forward_sliced(gptoss_ctx *ctx, int layer, int T, float *x_slice_dev, void *stream);
-/* The token-sliced block through HOST buffers (pinned memory recommended): t_host_slice bf16 [slice count, H] and
+/* Dispatch form of the token-sliced block: instead of gathering every rank's activations on every rank, each rank
+ * routes ITS tokens and sends each token row only to the ranks whose experts the token selected (top-4 of 32 experts
+ * on 8 GPUs: 3.0 remote rows per token on average instead of 7), straight into the row's position in the receiver's
+ * grouped input.  Together with the push of the expert outputs to the token's owner this is the dispatch / combine
+ * pair of an expert-parallel layer, both halves by peer stores from the kernels that produce the rows; it replaces
+ * moe_build_local_ep_data + ring_reduce_agg_quantize_fp8 (getp-csrc/src/parallelism.cpp:1848-1873,1605-1670).
+ *   dispatch_route : router GEMM + top-k + softmax + block histograms of this rank's rows t_slice [slice count, H]
+ *                    (bf16, device, 16-byte aligned), results stored to every rank; raises "routed"; waits for nobody;
+ *   dispatch_rows  : waits for "routed" of all ranks; prefix sums and pair-id placement of the whole batch (every rank
+ *                    holds the complete, identical grouping); copies each row of t_slice to the grouped input of the
+ *                    rank that owns the selected expert; raises "gathered";
+ *   dispatch_push  : waits for "gathered" of all ranks; gate/up GEMM + SwiGLU; down GEMM pushing to the owners;
+ *   then gptoss_moe_sliced_combine.  forward_dispatch runs all four.
+ * With the context's wire format GPTOSS_WIRE_BF16 the pushed rows travel as bf16 (summed in fp32 by the owner); with
+ * GPTOSS_WIRE_F32 the result is bit-identical to one GPU.  Same calling rules as the forms above. */
+int gptoss_moe_dispatch_route(gptoss_ctx *ctx, int layer, int T, const void *t_slice_dev_bf16, void *stream);
+int gptoss_moe_dispatch_rows(gptoss_ctx *ctx, int layer, int T, const void *t_slice_dev_bf16, void *stream);
+int gptoss_moe_dispatch_push(gptoss_ctx *ctx, int layer, void *stream);
+int gptoss_moe_forward_dispatch(gptoss_ctx *ctx, int layer, int T, const void *t_slice_dev_bf16, float *x_slice_dev,
+                                void *stream);
+/* The token-sliced block (dispatch form) through HOST buffers (pinned memory recommended): t_host_slice bf16 [slice count, H] and
  * x_host_slice fp32 [slice count, H] hold THIS RANK'S rows of a batch of T tokens; on return x_host_slice holds
  * x + MoE(t) for them.  Per step each GPU moves only its slice over PCIe (the batch crosses the host link once in
  * total, not once per GPU); the other ranks' activations arrive over NVLink.  Synchronous; every rank must call it. */
@@ -214,8 +234,15 @@ int gptoss_topk_softmax(gptoss_ctx *ctx, int T, const float *scores_dev, float *
 /* moe_build_offsets (getp-csrc/src/kernel.cpp:851, kernel :504): topk_i [T*k] -> offsets [E+1],
  * sorted_pair_ids [T*k] (pair id = token*k + slot), stable within an expert; ids outside [0,E) are
  * skipped and the tail of sorted_pair_ids beyond offsets[E] is left untouched. */
+/* It uses the context's routing scratch (block histograms and bases): do not let it run concurrently with a
+ * gptoss_moe_forward / gptoss_moe_route of the same context on another stream. */
 int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int *offsets_dev,
                              int *sorted_pair_ids_dev, void *stream);
+
+/* sample_argmax (run.cpp:739-750; GPU: layer_hip_batch.cpp:1542-1583) on device rows: next[b] = index of the FIRST
+ * maximum of logits[b, 0..V) (fp32).  A row with no comparable maximum (all -inf / NaN, or NaN in front) gives 0, as
+ * the reference's scan does; the result is always inside [0, V). */
+int gptoss_argmax_rows(const float *logits_dev, int B, int V, int *next_dev, void *stream);
 
 /* Grouping for callers that must not allocate: same result as gptoss_moe_build_offsets, but it needs no
  * context and calls no cudaMalloc/cudaFree or any other allocating routine.  It has no counterpart in
@@ -322,6 +349,8 @@ int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out);
 
 /* Library build info: "gptoss_b200 <version> sm_100a". */
 const char *gptoss_version(void);
+/* Number of kernels this library has launched in this process so far (all contexts); measurement aid. */
+uint64_t gptoss_launch_count(void);
 
 #ifdef __cplusplus
 }

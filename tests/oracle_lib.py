@@ -15,7 +15,8 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent.parent
 ORACLE_DIR = ROOT / "oracle"
-REF_SRC = Path(os.environ.get("GPTOSS_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: GPTOSS_REFERENCE_DIR, else a directory called `reference` beside this repository (may be absent)
+REF_SRC = Path(os.environ.get("GPTOSS_REFERENCE_DIR") or ROOT.parent / "reference")
 
 MODE_CPU, MODE_GPU_BF16 = 0, 1
 RULE_SELECTION, RULE_QSORT = 0, 1

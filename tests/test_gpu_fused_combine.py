@@ -111,6 +111,7 @@ def test_wait_on_a_silent_peer_times_out_as_status():
     with pytest.raises(moe.GptossError) as e:
         ranks[0].status()
     assert e.value.code == capi.ERR_TIMEOUT
+    assert "site 0x2100" in str(e.value)   # the owner's wait for the "pushed" flags, not a wait inside a GEMM
     ranks[0].status()                      # the error word is cleared, the context stays usable
     part = torch.empty_like(x)
     ranks[0].forward_partial(0, t_dev, part)
@@ -213,5 +214,93 @@ def test_token_sliced_form_matches_single_context_bitwise(world, T):
     want = torch.from_numpy(xr.copy()).cuda()
     single.forward(0, torch.from_numpy(gathered.view(np.int16)).cuda().view(torch.bfloat16), want)
     assert torch.equal(torch.cat(xs), want)
+    for b in ranks + [single]:
+        b.close()
+
+
+@pytest.mark.parametrize("world,T", [(2, 300), (4, 203), (8, 64), (8, 5)])
+def test_dispatch_form_matches_single_context_bitwise(world, T):
+    """Dispatch form: every rank routes its own rows, shares the routing, and sends each row only to the ranks whose
+    experts it selected (into its place in the receiver's grouped input); expert rows are pushed back to the token's
+    owner.  fp32 wire: identical to one context bit for bit, routing and grouping included.  Stage by stage over
+    emulated ranks; uneven and empty slices."""
+    from gptoss_b200 import moe
+    H, I, E, k = 256, 192, 16, 4
+    w = synth.MoELayerWeights(H, I, E, 91, sigma=0.05)
+    single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)
+    single.upload_layer(0, w)
+    ranks = [moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, rank=r, world=world)
+             for r in range(world)]
+    for b in ranks:
+        b.upload_layer(0, w)
+    moe.MoEBlock.attach_local(ranks)
+    bounds = [b.slice(T) for b in ranks]
+    for step in range(3):
+        t = synth.activations(800 + step, T, H)
+        x0 = synth.normal(900 + step, synth.tensor_id(synth.TID_RESIDUAL), (T, H), 1.0)
+        t_dev = to_dev_bf16(t)
+        want = torch.from_numpy(x0.copy()).cuda()
+        single.forward(0, t_dev, want)
+        ts = [t_dev[f:f + n].contiguous() if n else None for f, n in bounds]
+        xs = [torch.from_numpy(x0[f:f + n].copy()).cuda() for f, n in bounds]
+        for b, tsl in zip(ranks, ts):
+            b.dispatch_route(0, T, tsl)
+        for b, tsl in zip(ranks, ts):
+            b.dispatch_rows(0, T, tsl)
+        for b in ranks:
+            b.dispatch_push(0)
+        for b, x in zip(ranks, xs):
+            b.sliced_combine(x)
+        for b in ranks:
+            b.status()
+            for name in ("topk_i", "topk_w", "offsets", "sorted"):
+                assert np.array_equal(b.tap(name, T), single.tap(name, T)), name
+        # every rank received exactly the rows of its experts, in the grouped order
+        off, xp = single.tap("offsets", T), single.tap("x_packed", T)
+        n_local = E // world
+        for r, b in enumerate(ranks):
+            lo, hi = off[r * n_local], off[(r + 1) * n_local]
+            assert np.array_equal(b.tap("x_packed", T)[lo:hi], xp[lo:hi])
+        assert torch.equal(torch.cat(xs), want)
+    for b in ranks + [single]:
+        b.close()
+
+
+def test_dispatch_form_bf16_wire_rounds_each_pushed_row_once():
+    """bf16 wire: the gate-weighted expert rows travel as bf16 and the owner sums them in fp32 in slot order, i.e. the
+    result is exactly x0 + ((r0 + r1) + r2) + r3 with r_j the bf16 rounding of the fp32 row of slot j."""
+    from gptoss_b200 import capi, moe
+    H, I, E, k, T, world = 256, 192, 16, 4, 300, 4
+    w = synth.MoELayerWeights(H, I, E, 93, sigma=0.05)
+    single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)
+    single.upload_layer(0, w)
+    ranks = [moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, rank=r, world=world,
+                          wire=capi.WIRE_BF16) for r in range(world)]
+    for b in ranks:
+        b.upload_layer(0, w)
+    moe.MoEBlock.attach_local(ranks)
+    bounds = [b.slice(T) for b in ranks]
+    t_dev = to_dev_bf16(synth.activations(94, T, H))
+    x0 = synth.normal(95, synth.tensor_id(synth.TID_RESIDUAL), (T, H), 1.0)
+    ref = torch.from_numpy(x0.copy()).cuda()
+    single.forward(0, t_dev, ref)
+    y = torch.from_numpy(single.tap("y_pairs", T)).reshape(T, k, H)
+    r = y.to(torch.bfloat16).to(torch.float32)
+    want = torch.from_numpy(x0.copy()) + (((r[:, 0] + r[:, 1]) + r[:, 2]) + r[:, 3])
+    ts = [t_dev[f:f + n].contiguous() if n else None for f, n in bounds]
+    xs = [torch.from_numpy(x0[f:f + n].copy()).cuda() for f, n in bounds]
+    for b, tsl in zip(ranks, ts):
+        b.dispatch_route(0, T, tsl)
+    for b, tsl in zip(ranks, ts):
+        b.dispatch_rows(0, T, tsl)
+    for b in ranks:
+        b.dispatch_push(0)
+    for b, x in zip(ranks, xs):
+        b.sliced_combine(x)
+        b.status()
+    got = torch.cat(xs).cpu()
+    assert torch.equal(got, want)
+    delta, delta_ref = got - torch.from_numpy(x0), ref.cpu() - torch.from_numpy(x0)
+    assert float((delta - delta_ref).norm() / delta_ref.norm()) < 4e-3  # one bf16 rounding per row: 2^-9 relative
     for b in ranks + [single]:
         b.close()

@@ -36,6 +36,7 @@ def _worker(rank, world, port, out_dir):
     if rank == 0:
         single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, device=0)
         single.fill_layer_synthetic(0, 9, 0.05)
+    dist.barrier()  # nobody starts waiting on a peer's flags while rank 0 is still setting up
     ok = True
     for step in range(4):
         t = synth.activations(300 + step, T, H)
@@ -69,6 +70,23 @@ def _worker(rank, world, port, out_dir):
             want = torch.empty((T, H), dtype=torch.float32)
         dist.broadcast(want, src=0)
         ok = ok and bool(torch.equal(x_slice, want[first:first + n]))
+    # the dispatch form on device buffers: rows only to the ranks whose experts they selected
+    for step in range(3):
+        t = synth.activations(600 + step, T, H)
+        x0 = synth.normal(700 + step, synth.tensor_id(synth.TID_RESIDUAL), (T, H), 1.0)
+        t_dev = torch.from_numpy(synth.f32_to_bf16_bits(t).view(np.int16).reshape(T, H)).cuda().view(torch.bfloat16)
+        t_slice = t_dev[first:first + n].contiguous()
+        x_slice = torch.from_numpy(x0[first:first + n].copy()).cuda()
+        blk.forward_dispatch(0, T, t_slice, x_slice)
+        blk.status()
+        if rank == 0:
+            want = torch.from_numpy(x0.copy()).cuda()
+            single.forward(0, t_dev, want)
+            want = want.cpu()
+        else:
+            want = torch.empty((T, H), dtype=torch.float32)
+        dist.broadcast(want, src=0)
+        ok = ok and bool(torch.equal(x_slice.cpu(), want[first:first + n]))
     dist.barrier()
     blk.close()
     if single:

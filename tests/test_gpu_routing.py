@@ -120,3 +120,25 @@ def test_route_stage_matches_oracle(oracle, H, E, T, zipf):
     tb = synth.f32_to_bf16_bits(t).reshape(T, H)
     assert np.array_equal(xp, tb[srt // k])
     blk.close()
+
+
+def test_argmax_first_maximum_and_degenerate_rows():
+    """sample_argmax (run.cpp:739-750): first maximum; rows without a comparable maximum give index 0."""
+    import ctypes as C
+    from gptoss_b200 import capi
+    lib = capi.load()
+    V = 201088
+    rng = np.random.default_rng(7)
+    rows = rng.standard_normal((6, V)).astype(np.float32)
+    rows[1, [5, 70000, 200000]] = 9.0          # three equal maxima: the first wins
+    rows[2, :] = -np.inf                       # nothing comparable
+    rows[3, :] = np.nan
+    rows[4, 0] = np.nan                        # NaN in front: the reference's running maximum never moves
+    rows[5, V - 1] = 50.0                      # maximum in the last (scalar-tail) position
+    want = np.array([int(rows[0].argmax()), 5, 0, 0, 0, V - 1], np.int32)
+    dev = torch.from_numpy(rows).cuda()
+    out = torch.full((6,), -1, dtype=torch.int32, device="cuda")
+    rc = lib.gptoss_argmax_rows(C.c_void_p(dev.data_ptr()), 6, V, C.c_void_p(out.data_ptr()), None)
+    assert rc == capi.OK
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want)

@@ -42,6 +42,27 @@ def test_noalloc_build_offsets_matches_context_entry_point_twice_in_a_row():
         blk.close()
 
 
+def test_noalloc_call_leaves_free_device_memory_unchanged():
+    """What the entry point promises: after its one-time set-up on a device, a call allocates nothing — the free
+    device memory reported by the driver is the same before and after."""
+    from gptoss_b200 import capi
+    lib = capi.load()
+    torch.cuda.set_device(0)
+    E, k, T = 32, 4, 4096
+    ids_dev = torch.from_numpy(np.random.default_rng(5).integers(0, E, size=(T, k), dtype=np.int32)).cuda()
+    off = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    srt = torch.empty(T * k, dtype=torch.int32, device="cuda")
+    call = lambda: lib.gptoss_moe_build_offsets_noalloc(T, E, k, _ptr(ids_dev), _ptr(off), _ptr(srt), None)  # noqa: E731
+    assert call() == capi.OK  # the first call on the device resolves the scratch array's address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert call() == capi.OK
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
 def test_noalloc_rejects_batches_beyond_the_static_scratch():
     from gptoss_b200 import capi
     lib = capi.load()
