@@ -77,15 +77,19 @@ struct Tile {
   int f0;       // first output feature
   int row0;     // first row (sorted order)
   int n_valid;  // rows in the tile
+  int tb;       // index of the token block within the expert
 };
 
+// Items of an expert are ordered feature tile by feature tile with the token block fastest (concurrently running
+// CTAs then share a weight tile in L2), or, with ft_fastest, token block by token block with the feature tile fastest
+// (they share the token rows instead: right when the "token" side is the large streamed operand).
 template <int TILE_FEAT, class C>
-__device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, int nft, int &cur, Tile &t) {
+__device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, int nft, bool ft_fastest, int &cur, Tile &t) {
   while (cur < n_local && idx >= c->tbp[cur + 1] * nft) ++cur;
   if (cur >= n_local) return false;
   const int r = idx - c->tbp[cur] * nft;
   const int nb = c->tbp[cur + 1] - c->tbp[cur];
-  const int ft = r / nb, tb = r - ft * nb;
+  const int ft = ft_fastest ? r % nft : r / nb, tb = ft_fastest ? r / nft : r - ft * nb;
   // an expert with more than 256 rows is cut into nb blocks of (almost) equal size, a multiple of 16 rows
   const int rows = c->off[cur + 1] - c->off[cur];
   const int blk = (((rows + nb - 1) / nb) + 15) & ~15;
@@ -93,6 +97,7 @@ __device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, in
   t.f0 = ft * TILE_FEAT;
   t.row0 = c->off[cur] + tb * blk;
   t.n_valid = min(blk, rows - tb * blk);
+  t.tb = tb;
   return true;
 }
 
@@ -130,8 +135,13 @@ __device__ __forceinline__ bool epilogue_any(bool pred) {
   return r != 0;
 }
 
-template <int NA, bool GLU>
+// AMAX (with !GLU): instead of storing the products, the epilogue keeps for every output feature (a TMEM lane) the
+// largest value over the token columns of the tile and the row id it came from, i.e. one (max, argmax) partial per
+// (token block, feature).  With the operand roles swapped — the batch's activations as the "weights", a vocabulary-
+// sized matrix as the "tokens" — this is the classifier with the greedy argmax fused: the logits never reach memory.
+template <int NA, bool GLU, bool AMAX = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmArgs a) {
+  static_assert(!AMAX || (NA == 2 && !GLU), "the argmax epilogue exists for the two-tile row GEMM only");
   using Cfg = TileCfg<NA, GLU>;
   using CtrlT = Ctrl<NA, GLU>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -140,6 +150,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_local = a.n_local, nft = a.n_feat_tiles;
+  const bool ftf = a.ft_fastest != 0;
 
   if (threadIdx.x == 0) {
     ctrl->max_rows = 0;
@@ -199,11 +210,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       int stage = 0, cur = 0;
       uint32_t phase = 0, armed = 0, last_par = 0;
       Tile t;
-      const uint64_t pol_w = l2_policy_evict_first();  // each weight byte is used once per launch
+      // each weight byte is used once per launch; with the roles swapped (ft_fastest) the "weights" are the small
+      // operand that every item reads again
+      const uint64_t pol_w = ftf ? l2_policy_evict_last() : l2_policy_evict_first();
       // Head start: the weights do not depend on the kernel before this one, so the weight tiles of the first
       // ring fill are requested before waiting for it; its outputs (the activation rows) are loaded after.
       int pre = 0;
-      if ((int)blockIdx.x < total_tiles && decode_tile<Cfg::kTileFeat>(blockIdx.x, ctrl, n_local, nft, cur, t)) {
+      if ((int)blockIdx.x < total_tiles && decode_tile<Cfg::kTileFeat>(blockIdx.x, ctrl, n_local, nft, ftf, cur, t)) {
         const int n_chunks = (max(16, (t.n_valid + 15) & ~15) + kTokChunk - 1) / kTokChunk;
         pre = min(n_stages, a.k_blocks);
         for (int kb = 0; kb < pre; ++kb) {
@@ -230,7 +243,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         pdl_launch_dependents();
       }
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
+        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const int n_chunks = (n_mma + kTokChunk - 1) / kTokChunk;
         const uint32_t tx = Cfg::kAStageBytes + n_chunks * kBChunkBytes;
@@ -272,7 +285,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       uint32_t phase = 0, acc_phase = 0;
       Tile t;
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
+        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const uint32_t idesc = umma_idesc(n_mma);
         if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1u, &ctrl->abort, a.status, 0x200 | acc)) break;
@@ -324,7 +337,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     const bool odd = lane & 1;
     const size_t esize = a.out_bf16 ? 2 : 4;  // mlp2 output element: fp32, or bf16 on the bf16 wire
     for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-      if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, cur, t)) break;
+      if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
       // Top of every tile: all epilogue threads meet and learn whether any role gave up.  The answer is the same for
       // all of them, so they leave together; the meeting also means that every thread has left the previous tile
       // before its staging slots (dst_s / w_s) are overwritten below.
@@ -332,6 +345,55 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const int f = t.f0 + q * 32 + lane;
       const int fe = f & ~1;                  // the even feature of this lane pair
       const bool f_ok = f < a.n_feat;         // n_feat is even: both features of a pair are valid or neither is
+      if constexpr (AMAX) {
+        // running first maximum of this thread's columns for its two features (f: first tile, f + 128: second tile)
+        float best0 = -3.402823466e+38f, best1 = -3.402823466e+38f;
+        int at0 = 0x7fffffff, at1 = 0x7fffffff;
+        const bool got = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
+        tc_fence_after();
+        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_stride);
+        for (int c0 = half * 16; got && c0 < t.n_valid; c0 += 32) {
+          uint32_t r0[16], r1[16];
+          tmem_ld16(tbase + c0, r0);
+          tmem_ld16(tbase + cols_per_tile + c0, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int id = t.row0 + c0 + j;
+            float v0 = __uint_as_float(r0[j]), v1 = __uint_as_float(r1[j]);
+            // a scan that starts from element 0 never leaves it when it is NaN (every '>' fails): rank it above all
+            if (id == 0 && v0 != v0) v0 = __int_as_float(0x7f800000);
+            if (id == 0 && v1 != v1) v1 = __int_as_float(0x7f800000);
+            const bool in = c0 + j < t.n_valid;
+            if (in && v0 > best0) best0 = v0, at0 = id;  // ascending ids, strict '>': the first maximum stays
+            if (in && v1 > best1) best1 = v1, at1 = id;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+        if (++acc == n_acc) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+        // the two warps of a quadrant saw alternate 16-column chunks: merge through shared memory (first maximum)
+        int *at_s = reinterpret_cast<int *>(ctrl->w_s[1]);
+        const int lane_f = q * 32 + lane;
+        if (half == 1) {
+          ctrl->w_s[0][lane_f] = best0, ctrl->w_s[0][kTileF + lane_f] = best1;
+          at_s[lane_f] = at0, at_s[kTileF + lane_f] = at1;
+        }
+        epilogue_bar_sync();
+        if (half == 0) {
+          const float o0 = ctrl->w_s[0][lane_f], o1 = ctrl->w_s[0][kTileF + lane_f];
+          const int p0 = at_s[lane_f], p1 = at_s[kTileF + lane_f];
+          if (o0 > best0 || (o0 == best0 && p0 < at0)) best0 = o0, at0 = p0;
+          if (o1 > best1 || (o1 == best1 && p1 < at1)) best1 = o1, at1 = p1;
+          const size_t o = (size_t)t.tb * a.n_feat;
+          if (f_ok) a.amax_val[o + f] = best0, a.amax_at[o + f] = at0;
+          if (f + kTileF < a.n_feat) a.amax_val[o + f + kTileF] = best1, a.amax_at[o + f + kTileF] = at1;
+        }
+        continue;  // the meeting at the top of the next tile keeps the merge slots of this one intact until read
+      }
       if constexpr (!GLU) {
         for (int n = et; n < t.n_valid; n += kEpilogueThreads) {
           const int pair = a.sorted[t.row0 + n];
@@ -432,14 +494,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   }
 }
 
-template <int NA, bool GLU>
+template <int NA, bool GLU, bool AMAX = false>
 cudaError_t launch_grouped(const GemmArgs &a, int sm_count, cudaStream_t s) {
   const size_t smem = (size_t)kRingBytes + sizeof(Ctrl<NA, GLU>);
   static_assert(kRingBytes + sizeof(Ctrl<NA, GLU>) <= 232448, "exceeds the 227 KiB dynamic shared memory of an SM");
   static_assert(kRingBytes >= 2 * (2 * kATileBytes + kMaxTileTokens * kBlockK * 2), "ring must hold two full stages");
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA, GLU, AMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return launch_chain(grouped_gemm_kernel<NA, GLU>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
+  return launch_chain(grouped_gemm_kernel<NA, GLU, AMAX>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -480,6 +542,14 @@ cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s)
   }
   b.n_feat_tiles = (a.n_feat + 2 * kTileF - 1) / (2 * kTileF);
   return launch_grouped<2, false>(b, sm_count, s);
+}
+
+// Row GEMM with the (max, argmax)-over-rows epilogue: amax_val / amax_at [token blocks][n_feat]
+cudaError_t launch_grouped_amax(const GemmArgs &a, int sm_count, cudaStream_t s) {
+  if (!a.amax_val || !a.amax_at || a.n_local != 1) return cudaErrorInvalidValue;
+  GemmArgs b = a;
+  b.n_feat_tiles = (a.n_feat + 2 * kTileF - 1) / (2 * kTileF);
+  return launch_grouped<2, false, true>(b, sm_count, s);
 }
 
 cudaError_t encode_weight_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs) {

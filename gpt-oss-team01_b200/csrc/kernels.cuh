@@ -127,12 +127,16 @@ struct GemmArgs {
   int signal_step;               // signal_step by the last CTA to finish (0 = no signalling)
   int *signal_counter;           // CTAs finished so far (left at 0)
   int top_k;
+  int ft_fastest;          // order of the items of an expert: 0 = token block fastest, 1 = feature tile fastest
+  float *amax_val;         // argmax epilogue (launch_grouped_amax): per (token block, feature) the largest product over
+  int *amax_at;            // the block's rows, and the id of the row that gave it (first one on ties)
   const int *sorted;       // mlp2: [P]
   const float *topk_w;     // mlp2: [P] by pair id
   int *status;             // device status words
 };
 cudaError_t launch_grouped_mlp1(const GemmArgs &a, int sm_count, cudaStream_t s);
 cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s);
+cudaError_t launch_grouped_amax(const GemmArgs &a, int sm_count, cudaStream_t s);
 // Encodes the two tensor maps (driver entry point resolved at run time; no link-time libcuda).
 // weights: base of [slabs][rows][K] bf16;  activations: base of [rows][K] bf16.
 cudaError_t encode_weight_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs);
@@ -144,10 +148,15 @@ cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, 
                                     cudaStream_t s);
 cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
                                   int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
-                                  cudaStream_t s);
+                                  const int *cache_rows, cudaStream_t s);
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
-                             int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s);
+                             int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, const int *cache_rows,
+                             cudaStream_t s);
+// cache_rows (both launchers above): null, or for each of the B sequences of the step the row of the KV cache that holds
+// it (a batch from which finished sequences were dropped keeps the cache rows of the remaining ones)
 cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s);
+// next[b] = id of the first maximum over the (max, id) partials val/at [n_blocks][B] (blocks in ascending id order)
+cudaError_t launch_argmax_partials(const float *val, const int *at, int n_blocks, int B, int *next, cudaStream_t s);
 cudaError_t launch_iota_ones(int *iota, float *ones, int n, cudaStream_t s);
 
 // convert.cu

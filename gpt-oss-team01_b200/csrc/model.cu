@@ -40,12 +40,19 @@ struct gptoss_model {
   float *attn_norm = nullptr, *mlp_norm = nullptr, *final_norm = nullptr, *b_qkv = nullptr, *b_o = nullptr, *sinks = nullptr;
   std::vector<CUtensorMap> map_qkv, map_o;
   CUtensorMap map_unemb, map_t, map_att;
+  CUtensorMap map_t_as_w, map_unemb_rows;  // fused classifier + argmax: the batch as the MMA's M side, the vocabulary as its N side
+  float *amax_val = nullptr;            // [vocab blocks][sequences] largest logit of the block
+  int *amax_at = nullptr;               //                           and its vocabulary id
+  int *amax_sched = nullptr;            // offsets {0, V}, token-block prefix {0, vocab blocks}; then {0, 1}, {0, 1} for one row
+  int n_vocab_blocks = 0;
   float *cos_t = nullptr, *sin_t = nullptr;
   __nv_bfloat16 *k_cache = nullptr, *v_cache = nullptr;
   // scratch
   float *x = nullptr, *qkv = nullptr, *q = nullptr, *proj = nullptr, *logits = nullptr, *ones = nullptr, *staging = nullptr;
   __nv_bfloat16 *t = nullptr, *att = nullptr;
   int *tokens_dev = nullptr, *next_dev = nullptr, *iota = nullptr, *dense_off = nullptr, *dense_tbp = nullptr, *status = nullptr;
+  int *rows_dev = nullptr;              // cache row of each sequence of a compacted step
+  const int *step_rows = nullptr;       // rows_dev during such a step, else null (sequence i lives in cache row i)
   int cur_B = -1;
   cudaStream_t stream = nullptr;
   bool weights_ready = false;
@@ -181,6 +188,7 @@ int set_batch(gptoss_model *m, int B) {
   MK(cudaMemcpyAsync(m->dense_tbp, tbp, sizeof tbp, cudaMemcpyHostToDevice, m->stream));
   MK(cudaStreamSynchronize(m->stream));
   MK(encode_map_2d(&m->map_t, m->t, m->c.hidden_dim, B, (uint32_t)kTokChunk));
+  MK(encode_weight_map(&m->map_t_as_w, m->t, m->c.hidden_dim, B, 1));
   MK(encode_map_2d(&m->map_att, m->att, (uint64_t)m->c.head_dim * m->c.n_attn_heads, B, (uint32_t)kTokChunk));
   m->cur_B = B;
   return GPTOSS_OK;
@@ -250,10 +258,15 @@ int gptoss_model_create_ep(const gptoss_model_config *cfg, int device, int rank,
   A(dalloc(&m->q, B * qd));
   A(dalloc(&m->att, B * qd));
   A(dalloc(&m->proj, B * H));
-  A(dalloc(&m->logits, B * V));
+  m->n_vocab_blocks = (int)((V + kMaxTileTokens - 1) / kMaxTileTokens);
+  A(dalloc(&m->logits, V));  // one row, filled on demand by gptoss_model_read_logits
+  A(dalloc(&m->amax_val, (size_t)m->n_vocab_blocks * B));
+  A(dalloc(&m->amax_at, (size_t)m->n_vocab_blocks * B));
+  A(dalloc(&m->amax_sched, 8));
   A(dalloc(&m->tokens_dev, B));
   A(dalloc(&m->next_dev, B));
   A(dalloc(&m->iota, B));
+  A(dalloc(&m->rows_dev, B));
   A(dalloc(&m->ones, B));
   A(dalloc(&m->dense_off, 2));
   A(dalloc(&m->dense_tbp, 6));
@@ -270,6 +283,11 @@ int gptoss_model_create_ep(const gptoss_model_config *cfg, int device, int rank,
     A(encode_weight_map(&m->map_o[l], m->w_o + l * H * qd, qd, H, 1));
   }
   if (e == cudaSuccess) A(encode_weight_map(&m->map_unemb, m->unemb, H, V, 1));
+  if (e == cudaSuccess) A(encode_map_2d(&m->map_unemb_rows, m->unemb, H, V, (uint32_t)kTokChunk));
+  if (e == cudaSuccess) {
+    const int sched[8] = {0, (int)V, 0, m->n_vocab_blocks, 0, 1, 0, 1};
+    A(cudaMemcpy(m->amax_sched, sched, sizeof sched, cudaMemcpyHostToDevice));
+  }
   if (e == cudaSuccess) {
     std::vector<float> cs, sn;
     rope_tables(c, (int)S, cs, sn);
@@ -292,7 +310,7 @@ int gptoss_model_destroy(gptoss_model *m) {
   if (m->moe) gptoss_ctx_destroy(m->moe);
   void *ptrs[] = {m->emb, m->unemb, m->attn_norm, m->mlp_norm, m->final_norm, m->w_qkv, m->b_qkv, m->w_o, m->b_o, m->sinks,
                   m->cos_t, m->sin_t, m->k_cache, m->v_cache, m->x, m->t, m->qkv, m->q, m->att, m->proj, m->logits,
-                  m->tokens_dev, m->next_dev, m->iota, m->ones, m->dense_off, m->dense_tbp, m->status, m->staging};
+                  m->tokens_dev, m->next_dev, m->iota, m->rows_dev, m->amax_val, m->amax_at, m->amax_sched, m->ones, m->dense_off, m->dense_tbp, m->status, m->staging};
   for (void *p : ptrs) cudaFree(p);
   if (m->stream) cudaStreamDestroy(m->stream);
   delete m;
@@ -422,6 +440,7 @@ int gptoss_model_step_begin(gptoss_model *m, const int *tokens_host, int pos, in
   gptoss_moe_slice_bounds(m->moe, B, &first, &n);
   if (n > 0 && !tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
   m->step_B = B, m->step_pos = pos, m->step_first = first, m->step_n = n;
+  m->step_rows = nullptr;
   if (n == 0) return GPTOSS_OK;
   int rc = set_batch(m, n);
   if (rc) return rc;
@@ -444,10 +463,10 @@ int gptoss_model_layer_attention(gptoss_model *m, int layer) {
     MK(launch_residual_rmsnorm(m->x, nullptr, m->attn_norm + l * H, B, (int)H, m->t, s));
     if ((rc = dense(m, kDenseQkv, m->map_qkv[l], m->map_t, (int)H, (int)qkvd, m->b_qkv + l * qkvd, m->qkv))) return rc;
     __nv_bfloat16 *kc = m->k_cache + l * (size_t)m->max_local * S * kvd, *vc = m->v_cache + l * (size_t)m->max_local * S * kvd;
-    MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, s));
+    MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, m->step_rows, s));
     const bool windowed = c.sliding_window > 0 && (l % 2 == 0);  // run.cpp:582
     const int t_lo = windowed ? (pos - c.sliding_window + 1 > 0 ? pos - c.sliding_window + 1 : 0) : 0;
-    MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, s));
+    MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, m->step_rows, s));
     if ((rc = dense(m, kDenseOut, m->map_o[l], m->map_att, (int)qd, (int)H, m->b_o + l * H, m->proj))) return rc;
   }
   if (m->world == 1) {
@@ -486,8 +505,27 @@ int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host) {
   int rc;
   if (next_tokens_host && B > 0) {  // a step whose outputs are all overridden by prompt tokens needs no logits
     MK(launch_residual_rmsnorm(m->x, nullptr, m->final_norm, B, H, m->t, s));
-    if ((rc = dense(m, kDenseVocab, m->map_unemb, m->map_t, H, c.vocab_size, nullptr, m->logits))) return rc;
-    MK(launch_argmax(m->logits, B, c.vocab_size, m->next_dev, s));
+    // classifier + greedy argmax in one GEMM (layer_hip_batch.cpp:1465-1712 + sample_argmax, run.cpp:739-750): the
+    // sequences are the MMA's M side, blocks of 256 vocabulary rows its N side, and the epilogue keeps one
+    // (max, id) per (vocabulary block, sequence) instead of storing B x V logits; a small kernel merges the blocks
+    GemmArgs a;
+    memset(&a, 0, sizeof a);
+    a.map_w = m->map_t_as_w;
+    a.map_act = m->map_unemb_rows;
+    a.offsets = m->amax_sched;
+    a.tb_prefix = m->amax_sched + 2;
+    a.n_local = 1;
+    a.n_feat = B;
+    a.k_blocks = (H + kBlockK - 1) / kBlockK;
+    a.status = m->status;
+    a.n_owners = 1;
+    a.top_k = 1;
+    a.slice_tokens = m->max_local;
+    a.ft_fastest = 1;  // the sequence tiles of one vocabulary block run side by side and share its rows in L2
+    a.amax_val = m->amax_val;
+    a.amax_at = m->amax_at;
+    MK(launch_grouped_amax(a, m->sm_count, s));
+    MK(launch_argmax_partials(m->amax_val, m->amax_at, m->n_vocab_blocks, B, m->next_dev, s));
     MK(cudaMemcpyAsync(next_tokens_host, m->next_dev, B * sizeof(int), cudaMemcpyDeviceToHost, s));
   }
   int st[kStatusWords];
@@ -519,13 +557,64 @@ int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, i
   return gptoss_model_step_end(m, next_tokens_host);
 }
 
-// Copies the logits of one sequence of the last step to the host (debug/parity tap).
+// The same step for a batch from which finished sequences were dropped (dead-sequence compaction of the lock-step
+// scheduler): n live sequences, sequence i keeps the KV-cache row rows_host[i] it has had since position 0.  Every
+// kernel of the step works on n rows; only the cache accesses go through the row map.
+int gptoss_model_step_rows(gptoss_model *m, const int *tokens_host, const int *rows_host, int pos, int n, int *next_tokens_host) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (m->world != 1) return m->fail(GPTOSS_ERR_UNSUPPORTED, "compacted steps are for a single-GPU model (a group keeps its slices)");
+  if (!rows_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null row map");
+  if (n <= 0 || n > m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "batch out of range");
+  for (int i = 0; i < n; ++i)
+    if (rows_host[i] < 0 || rows_host[i] >= m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "cache row out of range");
+  int rc = gptoss_model_step_begin(m, tokens_host, pos, n);
+  if (rc) return rc;
+  MK(cudaMemcpyAsync(m->rows_dev, rows_host, n * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+  m->step_rows = m->rows_dev;
+  for (int l = 0; !rc && l < m->c.n_layers; ++l) {
+    if ((rc = gptoss_model_layer_attention(m, l))) break;
+    rc = gptoss_model_layer_moe_push(m, l);
+  }
+  if (rc) {
+    m->step_B = 0;
+    m->step_rows = nullptr;
+    return rc;
+  }
+  rc = gptoss_model_step_end(m, next_tokens_host);
+  m->step_rows = nullptr;
+  return rc;
+}
+
+// Logits of one sequence of the last step that produced tokens (debug/parity tap).  The step itself never stores
+// logits (the classifier's epilogue keeps only the argmax), so they are computed here for the one row asked for:
+// the classifier GEMM on that row of the final-norm output, which the step left in place.
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out) {
   if (!m || !host_out) return GPTOSS_ERR_BAD_ARG;
   if (row < 0 || row >= m->max_local) return m->fail(GPTOSS_ERR_BAD_ARG, "row out of range");
   MK(cudaSetDevice(m->device));
-  MK(cudaMemcpy(host_out, m->logits + (size_t)row * m->c.vocab_size, (size_t)m->c.vocab_size * sizeof(float),
-                cudaMemcpyDeviceToHost));
+  const int H = m->c.hidden_dim, V = m->c.vocab_size;
+  CUtensorMap map_row;
+  MK(encode_map_2d(&map_row, m->t + (size_t)row * H, H, 1, (uint32_t)kTokChunk));
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.map_w = m->map_unemb;
+  a.map_act = map_row;
+  a.offsets = m->amax_sched + 4;
+  a.tb_prefix = m->amax_sched + 6;
+  a.n_local = 1;
+  a.n_feat = V;
+  a.n_feat_tiles = (V + kTileF - 1) / kTileF;
+  a.k_blocks = (H + kBlockK - 1) / kBlockK;
+  a.y_pairs = m->logits;
+  a.sorted = m->iota;
+  a.topk_w = m->ones;
+  a.status = m->status;
+  a.n_owners = 1;
+  a.top_k = 1;
+  a.slice_tokens = m->max_local;
+  MK(launch_grouped_mlp2(a, m->sm_count, m->stream));
+  MK(cudaMemcpyAsync(host_out, m->logits, (size_t)V * sizeof(float), cudaMemcpyDeviceToHost, m->stream));
+  MK(cudaStreamSynchronize(m->stream));
   return GPTOSS_OK;
 }
 

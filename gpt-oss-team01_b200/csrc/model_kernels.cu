@@ -59,9 +59,11 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
                                                              const float *__restrict__ sin_t, int pos, int nq, int nkv,
                                                              int hd, int S, float *__restrict__ q_out,
                                                              __nv_bfloat16 *__restrict__ k_cache,
-                                                             __nv_bfloat16 *__restrict__ v_cache) {
+                                                             __nv_bfloat16 *__restrict__ v_cache,
+                                                             const int *__restrict__ cache_rows) {
   pdl_wait();
   const int b = blockIdx.x;
+  const int cb = cache_rows ? cache_rows[b] : b;  // cache row of sequence b (a compacted batch keeps its rows)
   const int half = hd >> 1, hp = half >> 1;  // hp: pairs of adjacent rotation indices per head (hd is 32 or 64)
   const int qdim = nq * hd, kvdim = nkv * hd;
   const float *row = qkv + (size_t)b * (qdim + 2 * kvdim);
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
       *reinterpret_cast<float2 *>(dst) = o1;
       *reinterpret_cast<float2 *>(dst + half) = o2;
     } else {
-      __nv_bfloat16 *dst = k_cache + (((size_t)b * nkv + (h - nq)) * S + pos) * hd + j;
+      __nv_bfloat16 *dst = k_cache + (((size_t)cb * nkv + (h - nq)) * S + pos) * hd + j;
       *reinterpret_cast<__nv_bfloat162 *>(dst) = __floats2bfloat162_rn(o1.x, o1.y);
       *reinterpret_cast<__nv_bfloat162 *>(dst + half) = __floats2bfloat162_rn(o2.x, o2.y);
     }
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
     const int h = (4 * i) / hd, j = 4 * i - h * hd;
     const float4 v = reinterpret_cast<const float4 *>(vsrc)[i];
     const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-    *reinterpret_cast<uint2 *>(v_cache + (((size_t)b * nkv + h) * S + pos) * hd + j) =
+    *reinterpret_cast<uint2 *>(v_cache + (((size_t)cb * nkv + h) * S + pos) * hd + j) =
         make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
   }
   pdl_launch_dependents();
@@ -133,7 +135,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
                                                         const __nv_bfloat16 *__restrict__ v_cache,
                                                         const float *__restrict__ sinks, int pos, int t_lo, int nq,
                                                         int nkv, int kvm, int S, int n_problems,
-                                                        __nv_bfloat16 *__restrict__ out) {
+                                                        __nv_bfloat16 *__restrict__ out,
+                                                        const int *__restrict__ cache_rows) {
   constexpr int PS = 4 / G;    // warps (position groups) per problem
   constexpr int D4 = HD / 4;   // K dims per thread
   constexpr int KS = HD / 16;  // k-steps of the score MMA
@@ -147,6 +150,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   const bool active = prob < n_problems;
   const int b = active ? prob / nkv : 0, kvh = active ? prob % nkv : 0;
   pdl_wait();  // q and this position's K/V rows come from the kernel before
+  const int cb = cache_rows ? cache_rows[b] : b;  // cache row of sequence b
   uint32_t qh[KS][2], ql[KS][2];
 #pragma unroll
   for (int s = 0; s < KS; ++s) {
@@ -157,8 +161,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   }
   const float scale = 1.0f / sqrtf((float)HD);
   // cache rows of this problem: [b, kvh, t, :], contiguous over t
-  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + ((size_t)b * nkv + kvh) * S * HD + D4 * c;
-  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + ((size_t)b * nkv + kvh) * S * HD + DV * g;
+  const uint16_t *kbase = reinterpret_cast<const uint16_t *>(k_cache) + ((size_t)cb * nkv + kvh) * S * HD + D4 * c;
+  const uint16_t *vbase = reinterpret_cast<const uint16_t *>(v_cache) + ((size_t)cb * nkv + kvh) * S * HD + DV * g;
 
   float m_run = -FLT_MAX, l_part = 0.f;  // l_part: this thread's share of the denominator (its own positions)
   float o[DV][4];
@@ -389,6 +393,24 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
   }
 }
 
+// Second stage of the fused classifier argmax: per sequence the first maximum over the per-vocabulary-block partials
+// (blocks ascend in vocabulary id, so a strict '>' keeps the first).  A sequence without any comparable logit gets 0.
+__global__ void __launch_bounds__(256) argmax_partials_kernel(const float *__restrict__ val, const int *__restrict__ at,
+                                                              int n_blocks, int B, int *__restrict__ next) {
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) {
+    float best = -FLT_MAX;
+    int idx = 0x7fffffff;
+    for (int i = 0; i < n_blocks; ++i) {
+      const float v = val[(size_t)i * B + b];
+      if (v > best) best = v, idx = at[(size_t)i * B + b];
+    }
+    next[b] = idx == 0x7fffffff ? 0 : idx;
+  }
+  pdl_launch_dependents();
+}
+
 __global__ void iota_ones_kernel(int *__restrict__ iota, float *__restrict__ ones, int n) {
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     iota[i] = i;
@@ -407,12 +429,13 @@ cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, 
 }
 cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
                                   int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
-                                  cudaStream_t s) {
+                                  const int *cache_rows, cudaStream_t s) {
   return launch_chain(qkv_rope_store_kernel, dim3(B), dim3(256), 0, s, qkv, cos_t, sin_t, pos, nq, nkv, hd, S, q_out, k_cache,
-                      v_cache);
+                      v_cache, cache_rows);
 }
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
-                             int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, cudaStream_t s) {
+                             int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, const int *cache_rows,
+                             cudaStream_t s) {
   const int kv_mul = nq / nkv;
   if (kv_mul < 1 || kv_mul > 8 || kv_mul * nkv != nq) return cudaErrorInvalidValue;  // query rows of one MMA tile
   const int n_chunks = (pos - t_lo) / 32 + 1, n_prob = B * nkv;
@@ -425,7 +448,7 @@ cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const
 #define GPTOSS_ATT_CASE(HD, G)                                                                                             \
   if (hd == HD && g == G) {                                                                                                \
     return launch_chain(attention_kernel<HD, G>, dim3(grid), dim3(128), 0, s, q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv,   \
-                        kv_mul, S, n_prob, out);                                                                           \
+                        kv_mul, S, n_prob, out, cache_rows);                                                               \
   }
   GPTOSS_ATT_CASE(64, 4)
   GPTOSS_ATT_CASE(64, 2)
@@ -438,6 +461,9 @@ cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const
 }
 cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s) {
   return launch_chain(argmax_kernel, dim3(B), dim3(1024), 0, s, logits, V, next);
+}
+cudaError_t launch_argmax_partials(const float *val, const int *at, int n_blocks, int B, int *next, cudaStream_t s) {
+  return launch_chain(argmax_partials_kernel, dim3((B + 255) / 256), dim3(256), 0, s, val, at, n_blocks, B, next);
 }
 cudaError_t launch_iota_ones(int *iota, float *ones, int n, cudaStream_t s) {
   iota_ones_kernel<<<(n + 255) / 256, 256, 0, s>>>(iota, ones, n);

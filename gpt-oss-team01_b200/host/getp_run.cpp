@@ -17,6 +17,12 @@
 // host thread per GPU meeting at a pthread barrier, getp-csrc/getp_run.cpp): the experts are sharded over the GPUs,
 // the sequences of a batch are dealt out in slices, and the ranks exchange activations over peer memory on the
 // device.  Batch size: environment GPTOSS_BATCH (default 1024; with GPTOSS_EP the batch of the whole group).
+//
+// Beyond the reference's scheduler (which keeps stepping a finished sequence until its whole batch has drained,
+// getp_run_submit.cpp:60-96): a data-parallel replica drops finished sequences from its batch between steps.  The
+// survivors keep their KV-cache rows (gptoss_model_step_rows takes the row of each live sequence), nothing is copied,
+// and since a sequence's tokens do not depend on its batch mates the output is unchanged; GPTOSS_NO_COMPACT=1 switches
+// it off.  GPTOSS_STOP_IDS="id,id,..." names further token ids that end a sequence like 199999 / 200002 do.
 #include "getp_eval.cpp"
 
 #include <pthread.h>
@@ -39,6 +45,10 @@ std::vector<gptoss_model *> g_models;  // one per GPU
 int g_batch = 1024;
 int g_max_seq = 0;
 bool g_group = false;  // GPTOSS_EP: the models are the ranks of one group
+bool g_compact = true;  // drop finished sequences from a replica's batch between steps
+std::vector<int> g_stop_ids = {199999, 200002};  // run.cpp:939, getp_run_submit.cpp:249
+
+bool is_stop(int tok) { return std::find(g_stop_ids.begin(), g_stop_ids.end(), tok) != g_stop_ids.end(); }
 
 void die(const char *what, gptoss_model *m) {
   fprintf(stderr, "gptoss_b200: %s: %s\n", what, m ? gptoss_model_last_error(m) : "");
@@ -98,10 +108,26 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
   int n_active = n;
   for (int i = 0; i < n; ++i) cur[i] = prompt[i][0];
   int running = sync ? sync->total_active(rank, n_active) : n_active;
+  const bool compact = g_compact && !sync;  // the ranks of a group keep their slices
+  std::vector<int> live, cur_live, next_live;  // compacted batch: sequence indices (= KV-cache rows), inputs, outputs
   for (int pos = 0; pos < max_seq_len - 1 && running > 0; ++pos) {
     bool need_next = false;  // does any running sequence take the model's token this step?
     for (int i = 0; i < n && !need_next; ++i) need_next = active[i] && pos_of[i] >= (int)prompt[i].size() - 1;
-    if (gptoss_model_step(model, cur.data(), pos, batch, need_next ? next.data() : nullptr)) die("decode step failed", model);
+    if (compact && n_active < n) {
+      if ((int)live.size() != n_active) {  // somebody finished since the last step
+        live.clear();
+        for (int i = 0; i < n; ++i)
+          if (active[i]) live.push_back(i);
+        cur_live.resize(live.size());
+        next_live.resize(live.size());
+      }
+      for (size_t j = 0; j < live.size(); ++j) cur_live[j] = cur[live[j]];
+      if (gptoss_model_step_rows(model, cur_live.data(), live.data(), pos, (int)live.size(), need_next ? next_live.data() : nullptr))
+        die("decode step failed", model);
+      for (size_t j = 0; j < live.size(); ++j) next[live[j]] = next_live[j];
+    } else if (gptoss_model_step(model, cur.data(), pos, batch, need_next ? next.data() : nullptr)) {
+      die("decode step failed", model);
+    }
     for (int i = 0; i < n; ++i) {
       if (!active[i]) continue;
       int tok = next[i];
@@ -110,7 +136,7 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
         tok = prompt[i][pos_of[i] + 1];  // still inside the prompt: force-feed
       else
         get_tok_gen_ptr(reqs, first + i)[pos_of[i] - (n_prompt - 1)] = tok;
-      if (tok == 199999 || tok == 200002) {
+      if (is_stop(tok)) {
         active[i] = 0;
         --n_active;
       }
@@ -136,6 +162,15 @@ void warm_up(Transformer *transformer, Tokenizer *tokenizer) {
   int n_gpus = 1;
   if (const char *g = getenv("GPTOSS_GPUS")) n_gpus = std::max(1, atoi(g));
   if (const char *e = getenv("GPTOSS_EP")) g_group = atoi(e) != 0 && n_gpus > 1;
+  if (const char *e = getenv("GPTOSS_NO_COMPACT")) g_compact = atoi(e) == 0;
+  if (const char *e = getenv("GPTOSS_STOP_IDS"))
+    for (const char *p = e; *p;) {
+      char *end = nullptr;
+      const long v = strtol(p, &end, 10);
+      if (end == p) break;
+      g_stop_ids.push_back((int)v);
+      p = *end ? end + 1 : end;
+    }
   const Config &c = transformer->config;
   g_max_seq = c.seq_len;
   if (const char *s = getenv("GPTOSS_MAX_SEQ")) g_max_seq = std::min(c.seq_len, std::max(2, atoi(s)));

@@ -99,6 +99,21 @@ class MoeLayerOps {
   void forward_sliced(int layer, float *x_slice, int cur_batch_size, void *stream) {
     check(gptoss_moe_forward_sliced(ctx_, layer, cur_batch_size, x_slice, stream));
   }
+  // dispatch form of the token-sliced block: this rank routes ITS rows (router_gemm_v2 + topk_softmax_batched on the
+  // slice), every rank groups the whole batch (moe_build_offsets_hip), each row goes only to the GPUs whose experts it
+  // selected (what moe_pack_inputs_hip + moe_build_local_ep_data copy locally), then the expert GEMMs with the rows
+  // pushed back to the token's GPU; moe_sliced_combine adds the slot-ordered sums to this rank's residual rows
+  void dispatch_route(int layer, const void *t_slice_bf16, int cur_batch_size, void *stream) {
+    check(gptoss_moe_dispatch_route(ctx_, layer, cur_batch_size, t_slice_bf16, stream));
+  }
+  void dispatch_rows(int layer, const void *t_slice_bf16, int cur_batch_size, void *stream) {
+    check(gptoss_moe_dispatch_rows(ctx_, layer, cur_batch_size, t_slice_bf16, stream));
+  }
+  void dispatch_push(int layer, void *stream) { check(gptoss_moe_dispatch_push(ctx_, layer, stream)); }
+  void moe_sliced_combine(float *x_slice, void *stream) { check(gptoss_moe_sliced_combine(ctx_, x_slice, stream)); }
+  void forward_dispatch(int layer, const void *t_slice_bf16, float *x_slice, int cur_batch_size, void *stream) {
+    check(gptoss_moe_forward_dispatch(ctx_, layer, cur_batch_size, t_slice_bf16, x_slice, stream));
+  }
   void slice_bounds(int cur_batch_size, int *first, int *count) const {
     gptoss_moe_slice_bounds(ctx_, cur_batch_size, first, count);
   }

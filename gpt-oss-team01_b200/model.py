@@ -100,6 +100,16 @@ class Model:
                                                nxt.ctypes.data_as(C.c_void_p) if need_next else None))
         return nxt
 
+    def step_rows(self, tokens, rows, pos, need_next=True):
+        """A step of a compacted batch: ``tokens[i]`` is the input of the live sequence whose KV-cache row is ``rows[i]``."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        rows = np.ascontiguousarray(rows, dtype=np.int32)
+        assert tokens.shape == rows.shape
+        nxt = np.empty_like(tokens) if need_next else None
+        self._check(self.lib.gptoss_model_step_rows(self._m, tokens.ctypes.data_as(C.c_void_p), rows.ctypes.data_as(C.c_void_p),
+                                                    int(pos), tokens.size, nxt.ctypes.data_as(C.c_void_p) if need_next else None))
+        return nxt
+
     @staticmethod
     def step_group(models, tokens, pos, need_next=True):
         """One step of a whole group driven from this thread: ``tokens`` int32 [B] for the whole batch; every phase

@@ -331,6 +331,15 @@ int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma);
  * caller would discard anyway (every sequence still inside its prompt): the KV caches are updated, the
  * final norm, classifier and argmax are skipped.  Synchronous. */
 int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, int *next_tokens_host);
+/* The same step for a batch from which finished sequences have been dropped — the dead-sequence compaction the
+ * reference's scheduler lacks (getp-csrc/submit/getp_run_submit.cpp:60-96 keeps stepping a finished sequence until
+ * the whole batch has drained).  n live sequences; sequence i keeps the KV-cache row rows_host[i] (in
+ * [0, max_batch), distinct) that it has used since position 0, so nothing is moved: every kernel of the step works on
+ * n rows and only the cache accesses go through the map.  A sequence's tokens do not depend on which other
+ * sequences share its batch, so the survivors continue bit for bit as if nothing had been dropped.  Single-GPU models
+ * only (the ranks of a group keep their slices). */
+int gptoss_model_step_rows(gptoss_model *m, const int *tokens_host, const int *rows_host, int pos, int n,
+                           int *next_tokens_host);
 /* The phases of gptoss_model_step, which runs begin, then per layer attention / moe_push / moe_combine, then end.
  * In a group, B is the batch of the group and tokens_host / next_tokens_host hold this rank's sequences only.
  * Separate entry points so that one host thread can drive the ranks of a group in turn (each phase for every rank
@@ -344,7 +353,9 @@ int gptoss_model_layer_attention(gptoss_model *m, int layer);
 int gptoss_model_layer_moe_push(gptoss_model *m, int layer);
 int gptoss_model_layer_moe_combine(gptoss_model *m, int layer);
 int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host);
-/* Logits (fp32 [vocab]) of one sequence of the last step; debug/parity tap (PRINT_LOGITS, getp_run.cpp:236). */
+/* Logits (fp32 [vocab]) of one sequence of the last step that produced tokens; debug/parity tap (PRINT_LOGITS,
+ * getp_run.cpp:236).  A step keeps no logits (the classifier's epilogue reduces them to the greedy token, as
+ * layer_hip_batch.cpp:1465-1712 does for the reference): the row is computed when asked for. */
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out);
 
 /* Library build info: "gptoss_b200 <version> sm_100a". */

@@ -36,9 +36,44 @@ entry.load_package()
 from gptoss_b200 import binfmt, synth  # noqa: E402
 import oracle_lib  # noqa: E402
 
-SEED = 20240607
+# Seed of the checkpoint and the prompt.  The 7m model's logits have a spread of only ~0.1, so for most seeds some of
+# the greedy steps are near-ties that a bf16 engine may legitimately resolve the other way, and many continuations
+# collapse to one repeated token.  `--scan-seeds A B` prints, per seed, the smallest top-2 logit gap of the reference
+# over the first 32 generated tokens and how many different tokens those are; this seed is the one of
+# 20240607..20241008 with the widest such gap (0.0096: more than twice the 4e-3 to which the parity test holds every
+# logit, and ten times the bf16-vs-fp32 noise actually seen) among the seeds whose first 32 tokens take more than 8
+# different values, so "the first 32 greedy tokens are identical" can be asserted without any escape clause.
+SEED = 20240618
 N_PROMPT, N_GEN = 32, 64
 PROMPT_STREAM = 7
+
+
+def scan_seeds(first, last):
+    """Prints the reference's smallest top-2 logit gap over the first 32 generated tokens for each seed."""
+    ref = oracle_lib.reference()
+    assert ref is not None, "reference sources not found"
+    cfg = binfmt.config_7m()
+    logits = np.empty(cfg.vocab_size, np.float32)
+    for seed in range(first, last):
+        with tempfile.TemporaryDirectory() as td:
+            path = Path(td) / "m.bin"
+            binfmt.write_synthetic(str(path), cfg, seed)
+            prompt = synth.uniform_ids(seed, PROMPT_STREAM, N_PROMPT, cfg.vocab_size)
+            h = ref.open(path)
+            tok, margins, gen = int(prompt[0]), [], []
+            for pos in range(N_PROMPT + N_GEN - 1):
+                nxt = ref.forward(h, tok, pos, logits)
+                top2 = np.partition(logits, -2)[-2:]
+                margins.append(float(top2[1] - top2[0]))
+                if pos + 1 < N_PROMPT:
+                    tok = int(prompt[pos + 1])
+                else:
+                    gen.append(nxt)
+                    tok = nxt
+            ref.close(h)
+        m = np.array(margins)
+        print(f"{seed} min top-2 gap, first 32 generated {m[N_PROMPT - 1:N_PROMPT + 31].min():.4f}, all {m[N_PROMPT - 1:].min():.4f}, "
+              f"distinct tokens in the first 32: {len(set(gen[:32]))}", flush=True)
 
 
 def main():
@@ -116,6 +151,10 @@ def make_attention_fixture(n_pos=200):
 
 
 if __name__ == "__main__":
+    if "--scan-seeds" in sys.argv:
+        i = sys.argv.index("--scan-seeds")
+        scan_seeds(int(sys.argv[i + 1]), int(sys.argv[i + 2]))
+        sys.exit(0)
     if "--attention-only" not in sys.argv:
         main()
     make_attention_fixture()

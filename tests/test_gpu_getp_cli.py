@@ -68,6 +68,46 @@ def test_getp_mode_writes_the_tokens_of_the_stepwise_decode(tmp_path):
 
 
 @pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")
+def test_getp_mode_drops_finished_sequences_without_changing_the_output(tmp_path):
+    """Sequences that stop early (here: on an extra stop id that some of them generate) leave the batch; the rows
+    written for every request must be the same with and without that compaction, and the early stoppers' rows end
+    at the stop id."""
+    cfg = binfmt.config_7m()
+    ckpt, tok, inp = (tmp_path / n for n in ("m.bin", "tokenizer.bin", "in.txt"))
+    binfmt.write_synthetic(str(ckpt), cfg, 4242)
+    binfmt.write_synthetic_tokenizer(str(tok), cfg.vocab_size)
+    prompts = ["hello world", "a", "The quick brown fox", "B200", "mixture of experts", "peer memory", "x y z", "q"]
+    inp.write_text(f"{len(prompts)}\n" + "\n".join(prompts) + "\n")
+    steps = 40
+
+    def run(name, **env):
+        out = tmp_path / name
+        r = subprocess.run([str(EXE), str(ckpt), "-z", str(tok), "-m", "getp", "-i", str(inp), "-o", str(out), "-n", str(steps)],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
+                           env={"GPTOSS_BATCH": "8", "GPTOSS_MAX_SEQ": str(steps), "PATH": "/usr/bin:/bin", **env})
+        assert r.returncode == 0, r.stdout[-2000:]
+        return [[int(x) for x in line.split()] for line in out.read_text().splitlines()]
+
+    plain = run("plain.txt")
+    # a token that some, but not all, requests generate, and not as their first token
+    candidates = {}
+    for row in plain:
+        for j, t in enumerate(row[1:12], start=1):
+            if t > 255:
+                candidates.setdefault(t, set()).add(j)
+    stop = next(t for t in sorted(candidates) if sum(t in row[:12] for row in plain) < len(plain))
+    a = run("compact.txt", GPTOSS_STOP_IDS=str(stop))
+    b = run("nocompact.txt", GPTOSS_STOP_IDS=str(stop), GPTOSS_NO_COMPACT="1")
+    assert a == b
+    lengths = {len(r) for r in a}
+    assert len(lengths) > 1                                  # some stopped early, some ran on
+    for row, full in zip(a, plain):
+        assert row == full[:len(row)]                        # a prefix of the unstopped run ...
+        if len(row) < len(full):
+            assert row[-1] == stop                           # ... that ends at the stop id
+
+
+@pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")
 def test_getp_mode_group_of_gpus_writes_the_same_tokens(tmp_path):
     """GPTOSS_EP=1: the GPUs decode every batch together (experts sharded, sequences in slices, one host thread per
     GPU); the written ids must equal those of the single-GPU run of the same command."""
