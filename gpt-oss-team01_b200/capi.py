@@ -45,6 +45,7 @@ EXPORTS = [
     "gptoss_moe_route_local", "gptoss_moe_route_finish", "gptoss_moe_sliced_route",
     "gptoss_moe_dispatch_route", "gptoss_moe_dispatch_rows", "gptoss_moe_dispatch_push", "gptoss_moe_forward_dispatch",
     "gptoss_launch_count", "gptoss_argmax_rows", "gptoss_model_step_rows",
+    "gptoss_model_layer_moe_dispatch",
 ]
 
 
@@ -146,6 +147,7 @@ def load() -> C.CDLL:
         "gptoss_model_step_begin": ([vp, vp, i32, i32], i32),
         "gptoss_model_layer_attention": ([vp, i32], i32),
         "gptoss_model_layer_moe_push": ([vp, i32], i32),
+        "gptoss_model_layer_moe_dispatch": ([vp, i32], i32),
         "gptoss_model_layer_moe_combine": ([vp, i32], i32),
         "gptoss_model_step_end": ([vp, vp], i32),
         "gptoss_comm_rendezvous": ([ctxp, vp], i32),

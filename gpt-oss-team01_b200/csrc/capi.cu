@@ -25,6 +25,7 @@ struct LayerWeights {
   __nv_bfloat16 *w2 = nullptr;        // [E_local][H][I]
   float *b2 = nullptr;                // [E_local][H]
   CUtensorMap map_w1, map_w2, map_wr;
+  CUtensorMap map_w1_wide, map_w2_wide;  // both weight tiles of a ring stage in one box
   bool ready = false;
 };
 
@@ -74,6 +75,8 @@ struct gptoss_ctx {
   float *staging = nullptr;           // fp32 scratch for weight conversion
   size_t staging_elems = 0;
   CUtensorMap map_x, map_h;
+  CUtensorMap map_x_wide[3], map_h_wide[3];  // the same rows with boxes of 64, 128 and 256 rows
+  bool wide_copies = true;                   // GPTOSS_NARROW_COPIES=1: one box per weight tile and per 32 rows (A/B runs)
   std::vector<LayerWeights> layers;
   std::string err;
 
@@ -130,6 +133,8 @@ int alloc_layer(gptoss_ctx *ctx, LayerWeights &w) {
   CK(dev_alloc(&w.b2, EL * H));
   CK(encode_weight_map(&w.map_w1, w.w1, H, I, EL * 2));
   CK(encode_weight_map(&w.map_w2, w.w2, I, H, EL));
+  CK(encode_weight_map_wide(&w.map_w1_wide, w.w1, H, I, EL * 2, true));
+  CK(encode_weight_map_wide(&w.map_w2_wide, w.w2, I, H, EL, false));
   CK(encode_map_2d(&w.map_wr, w.router_w, H, E, (uint32_t)((E + 15) & ~(size_t)15)));
   return GPTOSS_OK;
 }
@@ -155,8 +160,13 @@ GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
   memset(&a, 0, sizeof a);
   a.map_w = mlp1 ? w.map_w1 : w.map_w2;
   a.map_act = mlp1 ? ctx->map_x : ctx->map_h;
+  if (ctx->wide_copies && (mlp1 || ctx->d.H > kTileF)) {  // the one-tile down GEMM (at most 128 features) has no pair of tiles
+    a.wide = 1;
+    a.map_w_wide = mlp1 ? w.map_w1_wide : w.map_w2_wide;
+    for (int i = 0; i < 3; ++i) a.map_act_wide[i] = mlp1 ? ctx->map_x_wide[i] : ctx->map_h_wide[i];
+  }
   a.offsets = ctx->rb.offsets;
-  a.tb_prefix = mlp1 ? ctx->rb.tb_prefix : ctx->rb.tb_prefix2;
+  a.tb_prefix = ctx->rb.tb_prefix;
   a.e_begin = ctx->d.e_begin;
   a.n_local = ctx->n_local;
   a.n_feat = mlp1 ? ctx->d.I : ctx->d.H;
@@ -216,9 +226,6 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->layers.resize(dims->n_layers);
   ctx->peers.timeout_ns = 2000000000ull;
   if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
-  ctx->balance.sm_count = ctx->sm_count;
-  ctx->balance.nft1 = (dims->intermediate + kTileF - 1) / kTileF;
-  ctx->balance.nft2 = dims->hidden <= kTileF ? 1 : (dims->hidden + 2 * kTileF - 1) / (2 * kTileF);
   if (const char *e = getenv("GPTOSS_TOKEN_BLOCK")) ctx->balance.force_rows = atoi(e);  // measurement aid: fixed token-block size
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
@@ -232,7 +239,6 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->rb.offsets, E + 1));
   A(dev_alloc(&ctx->rb.sorted, P));
   A(dev_alloc(&ctx->rb.tb_prefix, E + 1));
-  A(dev_alloc(&ctx->rb.tb_prefix2, E + 1));
   A(dev_alloc(&ctx->gate_up, P * I));
   ctx->sym_delta_off = 1024;
   ctx->sym_y_off = ctx->sym_delta_off + ((T * H * sizeof(float) + 1023) & ~(size_t)1023);
@@ -270,6 +276,9 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   if (e == cudaSuccess) A(cudaMemset(ctx->gate_up, 0, P * I * sizeof(__nv_bfloat16)));
   if (e == cudaSuccess) A(encode_act_map(&ctx->map_x, ctx->x_packed, H, P));
   if (e == cudaSuccess) A(encode_act_map(&ctx->map_h, ctx->gate_up, I, P));
+  if (e == cudaSuccess) A(encode_act_maps_wide(ctx->map_x_wide, ctx->x_packed, H, P));
+  if (e == cudaSuccess) A(encode_act_maps_wide(ctx->map_h_wide, ctx->gate_up, I, P));
+  if (const char *v = getenv("GPTOSS_NARROW_COPIES")) ctx->wide_copies = !(v[0] == '1');
   if (e != cudaSuccess) {
     gptoss_ctx_destroy(ctx);
     return GPTOSS_ERR_CUDA;
@@ -288,7 +297,6 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->rb.offsets);
   cudaFree(ctx->rb.sorted);
   cudaFree(ctx->rb.tb_prefix);
-  cudaFree(ctx->rb.tb_prefix2);
   cudaFree(ctx->gate_up);
   for (int r = 0; r < kMaxRanks; ++r)
     if (ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
@@ -982,7 +990,7 @@ int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int 
   RouteBuffers rb = ctx->rb;  // block histograms/bases live in the context scratch; results go to the caller
   rb.offsets = offsets_dev;
   rb.sorted = sorted_pair_ids_dev;
-  rb.tb_prefix = rb.tb_prefix2 = nullptr;  // the token-block prefixes of the context's own batch stay as they are
+  rb.tb_prefix = nullptr;  // the token-block prefix of the context's own batch stays as it is
   CK(launch_pair_hist(topk_i_dev, T, ctx->d, rb.blk_hist, s));
   CK(launch_expert_scan(rb, T, ctx->d, ctx->balance, s));
   CK(launch_scatter_gather(nullptr, 0, 0, topk_i_dev, T, ctx->d, rb.blk_base, rb.sorted, RowDispatch{}, s));

@@ -34,16 +34,13 @@ struct RouteBuffers {
   int *blk_base;        // [n_route_blocks, E]   global start row of each block's pairs per expert
   int *offsets;         // [E+1]
   int *sorted;          // [T*k]
-  int *tb_prefix;       // [E_local+1]   cumulative count of token blocks of the local experts, as the gate/up GEMM cuts them
-  int *tb_prefix2;      // [E_local+1]   the same for the down GEMM (it has half as many feature tiles, so another cut may
-                        //               fill the rounds of the persistent CTAs better); null = not wanted
+  int *tb_prefix;       // [E_local+1]   cumulative count of token blocks (at most kMaxTileTokens rows each) of the local
+                        //               experts; null = not wanted (grouping only)
 };
 
-// What the prefix-sum kernel needs to choose the token-block size of the two expert GEMMs (see expert_scan_kernel).
+// How the prefix-sum kernel cuts the experts' rows into token blocks (see expert_scan_kernel).
 struct TileBalance {
-  int sm_count;   // persistent CTAs of a GEMM launch
-  int nft1, nft2; // feature tiles per (expert, token block) of the gate/up and of the down GEMM
-  int force_rows; // > 0: use this block size for both (measurement aid)
+  int force_rows; // > 0: blocks of at most this many rows instead of kMaxTileTokens (measurement aid)
 };
 
 // Where the gathered token rows go.  n == 1: into this rank's own x_packed, rows of its experts only.  n > 1 (dispatch

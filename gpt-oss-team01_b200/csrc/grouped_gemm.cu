@@ -109,18 +109,6 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
 }
 
-// Lanes 2i and 2i+1 hold two adjacent output features of the token columns j and j+1.  After the exchange the even
-// lane holds both features of column j and the odd lane both features of column j+1 (lo = even feature), so that
-// every lane stores two adjacent elements at once: half the store instructions, twice the bytes each.
-__device__ __forceinline__ void pair_exchange(float vj, float vj1, bool odd, float &lo, float &hi) {
-  const float recv = __shfl_xor_sync(0xffffffffu, odd ? vj : vj1, 1);
-  lo = odd ? recv : vj;
-  hi = odd ? vj1 : recv;
-}
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t *>(&p);
-}
 // OR of `pred` over the eight epilogue warps (named barrier 1): every epilogue thread gets the same answer
 __device__ __forceinline__ bool epilogue_any(bool pred) {
   uint32_t r;
@@ -135,13 +123,44 @@ __device__ __forceinline__ bool epilogue_any(bool pred) {
   return r != 0;
 }
 
+// The operands of one k-block into a ring stage.  With the wide tensor maps (a.wide) the two weight tiles come as ONE
+// box (the gate and up slabs of the same 128 features, or 256 adjacent features) and the token rows as boxes of 256,
+// 128, 64 and 32 rows (largest first), so a stage is 2 to 5 copy instructions instead of up to 10: the copy engine
+// takes its requests one at a time, and at 256-row blocks the request rate, not the bytes, bounded the ring.
+template <int NA, bool GLU>
+__device__ __forceinline__ void load_weights(const GemmArgs &a, uint32_t sa, uint32_t bar, int kb, const Tile &t, uint64_t pol) {
+  constexpr int kSlabs = GLU ? 2 : 1;
+  if (NA == 2 && a.wide) {
+    tma_load_3d_hint(sa, &a.map_w_wide, bar, kb * kBlockK, t.f0, t.e * kSlabs, pol);
+    return;
+  }
+  tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * kSlabs, pol);
+  if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
+    tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF, GLU ? t.e * kSlabs + 1 : t.e * kSlabs,
+                     pol);
+}
+__device__ __forceinline__ void load_rows(const GemmArgs &a, uint32_t sb, uint32_t bar, int kb, int row0, int n_chunks) {
+  int c = 0;
+  if (a.wide) {
+#pragma unroll
+    for (int lg = 3; lg >= 1; --lg)  // boxes of 256, 128, 64 rows
+      while (n_chunks - c >= (1 << lg)) {
+        tma_load_2d(sb + c * kBChunkBytes, &a.map_act_wide[lg - 1], bar, kb * kBlockK, row0 + c * kTokChunk);
+        c += 1 << lg;
+      }
+  }
+  for (; c < n_chunks; ++c) tma_load_2d(sb + c * kBChunkBytes, &a.map_act, bar, kb * kBlockK, row0 + c * kTokChunk);
+}
+
 // AMAX (with !GLU): instead of storing the products, the epilogue keeps for every output feature (a TMEM lane) the
 // largest value over the token columns of the tile and the row id it came from, i.e. one (max, argmax) partial per
 // (token block, feature).  With the operand roles swapped — the batch's activations as the "weights", a vocabulary-
 // sized matrix as the "tokens" — this is the classifier with the greedy argmax fused: the logits never reach memory.
-template <int NA, bool GLU, bool AMAX = false>
+// OUT16 (with !GLU): the output rows are bf16 instead of fp32 (same row and element indexing).
+template <int NA, bool GLU, bool AMAX = false, bool OUT16 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmArgs a) {
   static_assert(!AMAX || (NA == 2 && !GLU), "the argmax epilogue exists for the two-tile row GEMM only");
+  static_assert(!OUT16 || (!GLU && !AMAX), "bf16 rows are an option of the row GEMM only");
   using Cfg = TileCfg<NA, GLU>;
   using CtrlT = Ctrl<NA, GLU>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -224,17 +243,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           const uint32_t sa = ring + kb * stage_bytes;
           armed |= 1u << kb;
           mbar_expect_tx(bar, Cfg::kAStageBytes + n_chunks * kBChunkBytes);
-          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * Cfg::kSlabs, pol_w);
-          if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
-            tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF,
-                             GLU ? t.e * Cfg::kSlabs + 1 : t.e * Cfg::kSlabs, pol_w);
+          load_weights<NA, GLU>(a, sa, bar, kb, t, pol_w);
         }
         pdl_wait();
         pdl_launch_dependents();
         for (int kb = 0; kb < pre; ++kb)
-          for (int c = 0; c < n_chunks; ++c)
-            tma_load_2d(ring + kb * stage_bytes + Cfg::kAStageBytes + c * kBChunkBytes, &a.map_act,
-                        smem_u32(&ctrl->full[kb]), kb * kBlockK, t.row0 + c * kTokChunk);
+          load_rows(a, ring + kb * stage_bytes + Cfg::kAStageBytes, smem_u32(&ctrl->full[kb]), kb, t.row0, n_chunks);
         stage = pre % n_stages;
         phase = (pre == n_stages) ? 1u : 0u;
         cur = 0;
@@ -255,13 +269,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           armed |= 1u << stage;
           last_par = (last_par & ~(1u << stage)) | (phase << stage);
           mbar_expect_tx(bar, tx);
-          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * Cfg::kSlabs, pol_w);
-          if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
-            tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF,
-                             GLU ? t.e * Cfg::kSlabs + 1 : t.e * Cfg::kSlabs, pol_w);
-          const uint32_t sb = sa + Cfg::kAStageBytes;
-          for (int c = 0; c < n_chunks; ++c)
-            tma_load_2d(sb + c * kBChunkBytes, &a.map_act, bar, kb * kBlockK, t.row0 + c * kTokChunk);
+          load_weights<NA, GLU>(a, sa, bar, kb, t, pol_w);
+          load_rows(a, sa + Cfg::kAStageBytes, bar, kb, t.row0, n_chunks);
           if (++stage == n_stages) {
             stage = 0;
             phase ^= 1u;
@@ -334,8 +343,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     uint32_t acc_phase = 0;
     Tile t;
     const uint64_t pol_keep = l2_policy_evict_last();  // the outputs are read again by the next kernel
-    const bool odd = lane & 1;
-    const size_t esize = a.out_bf16 ? 2 : 4;  // mlp2 output element: fp32, or bf16 on the bf16 wire
+    constexpr size_t esize = OUT16 ? 2 : 4;  // mlp2 output element: fp32, or bf16 on the bf16 wire
     for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
       if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
       // Top of every tile: all epilogue threads meet and learn whether any role gave up.  The answer is the same for
@@ -343,8 +351,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       // before its staging slots (dst_s / w_s) are overwritten below.
       if (epilogue_any(*reinterpret_cast<volatile int *>(&ctrl->abort) != 0)) break;
       const int f = t.f0 + q * 32 + lane;
-      const int fe = f & ~1;                  // the even feature of this lane pair
-      const bool f_ok = f < a.n_feat;         // n_feat is even: both features of a pair are valid or neither is
+      const bool f_ok = f < a.n_feat;
       if constexpr (AMAX) {
         // running first maximum of this thread's columns for its two features (f: first tile, f + 128: second tile)
         float best0 = -3.402823466e+38f, best1 = -3.402823466e+38f;
@@ -420,45 +427,49 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         if (NA == 2) tmem_ld16(tbase + cols_per_tile + c0, r1);
         tmem_ld_wait();
         float v[16];
+        // One lane = one feature, so a warp's store of one token column covers 32 adjacent features of that row (128
+        // bytes of fp32, 64 of bf16).  Pairing lanes through shuffles to store two adjacent elements per lane was
+        // measured slower: the down GEMM's epilogue is exposed (one accumulator set), and the shuffles lengthen it.
         if constexpr (GLU) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             v[j] = swiglu(__uint_as_float(r0[j]) + bias0, __uint_as_float(r1[j]) + bias1, a.limit);
-          __nv_bfloat16 *dst = a.gate_up + (size_t)(t.row0 + c0) * a.n_feat + fe;
+          __nv_bfloat16 *dst = a.gate_up + (size_t)(t.row0 + c0) * a.n_feat + f;
 #pragma unroll
           for (int j = 0; j < 16; j += 2) {
-            float lo, hi;
-            pair_exchange(v[j], v[j + 1], odd, lo, hi);
-            const int col = j + (odd ? 1 : 0);
-            if (f_ok && c0 + col < t.n_valid) st_b32_hint(dst + (size_t)col * a.n_feat, pack_bf16x2(lo, hi), pol_keep);
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(v[j], v[j + 1]);
+            if (f_ok && c0 + j < t.n_valid) st_b16_hint(dst + (size_t)j * a.n_feat, __bfloat16_as_ushort(pk.x), pol_keep);
+            if (f_ok && c0 + j + 1 < t.n_valid) st_b16_hint(dst + (size_t)(j + 1) * a.n_feat, __bfloat16_as_ushort(pk.y), pol_keep);
           }
         } else {
+          char *pr[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
+          for (int j = 0; j < 16; ++j) {
+            pr[j] = ctrl->dst_s[acc][c0 + j];
+            v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
+          }
+          if constexpr (OUT16) {
 #pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            float lo, hi;
-            pair_exchange(v[j], v[j + 1], odd, lo, hi);
-            const int col = c0 + j + (odd ? 1 : 0);
-            char *row = ctrl->dst_s[acc][col];
-            if (f_ok && col < t.n_valid) {
-              if (a.out_bf16) st_b32_hint(row + (size_t)fe * 2, pack_bf16x2(lo, hi), pol_keep);
-              else st_f32x2_hint(row + (size_t)fe * 4, lo, hi, pol_keep);
-            }
+            for (int j = 0; j < 16; ++j)
+              if (f_ok && c0 + j < t.n_valid)
+                st_b16_hint(pr[j] + (size_t)f * 2, __bfloat16_as_ushort(__float2bfloat16_rn(v[j])), pol_keep);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f_ok && c0 + j < t.n_valid) st_f32_hint(reinterpret_cast<float *>(pr[j]) + f, v[j], pol_keep);
           }
           if constexpr (NA == 2) {
+            if constexpr (OUT16) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j];
+              for (int j = 0; j < 16; ++j)
+                if (f1_ok && c0 + j < t.n_valid)
+                  st_b16_hint(pr[j] + (size_t)(f + kTileF) * 2,
+                              __bfloat16_as_ushort(__float2bfloat16_rn((__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j])), pol_keep);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-              float lo, hi;
-              pair_exchange(v[j], v[j + 1], odd, lo, hi);
-              const int col = c0 + j + (odd ? 1 : 0);
-              char *row = ctrl->dst_s[acc][col];
-              if (f1_ok && col < t.n_valid) {
-                if (a.out_bf16) st_b32_hint(row + (size_t)(fe + kTileF) * 2, pack_bf16x2(lo, hi), pol_keep);
-                else st_f32x2_hint(row + (size_t)(fe + kTileF) * 4, lo, hi, pol_keep);
-              }
+              for (int j = 0; j < 16; ++j)
+                if (f1_ok && c0 + j < t.n_valid)
+                  st_f32_hint(reinterpret_cast<float *>(pr[j]) + f + kTileF, (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j], pol_keep);
             }
           }
         }
@@ -494,14 +505,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   }
 }
 
-template <int NA, bool GLU, bool AMAX = false>
+template <int NA, bool GLU, bool AMAX = false, bool OUT16 = false>
 cudaError_t launch_grouped(const GemmArgs &a, int sm_count, cudaStream_t s) {
   const size_t smem = (size_t)kRingBytes + sizeof(Ctrl<NA, GLU>);
   static_assert(kRingBytes + sizeof(Ctrl<NA, GLU>) <= 232448, "exceeds the 227 KiB dynamic shared memory of an SM");
   static_assert(kRingBytes >= 2 * (2 * kATileBytes + kMaxTileTokens * kBlockK * 2), "ring must hold two full stages");
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA, GLU, AMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NA, GLU, AMAX, OUT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return launch_chain(grouped_gemm_kernel<NA, GLU, AMAX>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
+  return launch_chain(grouped_gemm_kernel<NA, GLU, AMAX, OUT16>, dim3(sm_count), dim3(kGemmThreads), smem, s, a);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -538,10 +549,10 @@ cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s)
   GemmArgs b = a;
   if (single || a.n_feat <= kTileF) {
     b.n_feat_tiles = (a.n_feat + kTileF - 1) / kTileF;
-    return launch_grouped<1, false>(b, sm_count, s);
+    return a.out_bf16 ? launch_grouped<1, false, false, true>(b, sm_count, s) : launch_grouped<1, false>(b, sm_count, s);
   }
   b.n_feat_tiles = (a.n_feat + 2 * kTileF - 1) / (2 * kTileF);
-  return launch_grouped<2, false>(b, sm_count, s);
+  return a.out_bf16 ? launch_grouped<2, false, false, true>(b, sm_count, s) : launch_grouped<2, false>(b, sm_count, s);
 }
 
 // Row GEMM with the (max, argmax)-over-rows epilogue: amax_val / amax_at [token blocks][n_feat]
@@ -582,6 +593,31 @@ cudaError_t encode_map_2d(CUtensorMap *m, const void *base, uint64_t K, uint64_t
 
 cudaError_t encode_act_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows) {
   return encode_map_2d(m, base, K, rows, (uint32_t)kTokChunk);
+}
+
+// The same token rows with boxes of 64, 128 and 256 rows (wide[0..2]).
+cudaError_t encode_act_maps_wide(CUtensorMap *wide, const void *base, uint64_t K, uint64_t rows) {
+  for (int i = 0; i < 3; ++i) {
+    cudaError_t e = encode_map_2d(&wide[i], base, K, rows, (uint32_t)(kTokChunk << (i + 1)));
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+// Both weight tiles of a ring stage as one box: {64, 128, 2} (the gate and up slabs of 128 features) when pair_slabs,
+// else {64, 256, 1} (256 adjacent features; rows past the last feature are zero-filled).
+cudaError_t encode_weight_map_wide(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs, bool pair_slabs) {
+  EncodeTiledFn fn;
+  cudaError_t e = get_encode_fn(&fn);
+  if (e != cudaSuccess) return e;
+  const cuuint64_t dims[3] = {K, rows, slabs};
+  const cuuint64_t strides[2] = {K * 2, K * rows * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)(pair_slabs ? kTileF : 2 * kTileF), pair_slabs ? 2u : 1u};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 }  // namespace gptoss

@@ -4,8 +4,9 @@
 // One GPU holds the whole model, or `world` GPUs (one model object each) split the work: the sequences of the
 // batch are dealt out in contiguous slices (attention, dense GEMMs, KV cache and residual stream of a sequence live
 // on its rank only: data-parallel attention, no attention-side all-reduce) and the experts are sharded by rank;
-// per layer the ranks exchange the normalised activations (each stores its slice to all) and the expert outputs
-// (stored to the token's owner from the down-GEMM epilogue), both over peer memory.
+// per layer the ranks exchange the routing of their tokens, the normalised rows (each row only to the ranks whose
+// experts it selected) and the expert outputs (stored to the token's owner from the down-GEMM epilogue), all over
+// peer memory.
 //
 // Per step (all sequences at the same position, prompt tokens force-fed by the caller — the reference's
 // lock-step decode): embedding -> per layer [RMSNorm -> QKV GEMM -> RoPE + KV store -> single-query attention
@@ -419,9 +420,11 @@ int gptoss_model_fill_synthetic(gptoss_model *m, uint64_t seed, float sigma) {
 // an expert-parallel group itself (several model objects driven by one thread, e.g. on one device in a test).
 //   step_begin         tokens of this rank's sequences -> embedding rows (the residual stream)
 //   layer_attention    RMSNorm -> QKV GEMM -> RoPE + KV store -> attention -> o-proj GEMM -> residual + RMSNorm
-//                      (expert-parallel: the normalised rows go to every rank's gathered activations)
-//   layer_moe_push     one GPU: the whole MoE block.  Expert-parallel: routing of the gathered batch, expert GEMMs of
-//                      this rank's experts, rows pushed to the tokens' owners
+//                      (expert-parallel: then the routing of this rank's rows, shared with every rank)
+//   layer_moe_dispatch expert-parallel only: grouping of the whole batch from everybody's routing rows; this rank's
+//                      rows go to the ranks whose experts they selected
+//   layer_moe_push     one GPU: the whole MoE block.  Expert-parallel: expert GEMMs of this rank's experts on the rows
+//                      it received, outputs pushed to the tokens' owners
 //   layer_moe_combine  expert-parallel only: slot-ordered sum of the pushed rows into this rank's residual rows
 //   step_end           final RMSNorm -> classifier GEMM -> argmax -> next tokens of this rank's sequences
 int gptoss_model_slice(const gptoss_model *m, int B, int *first, int *count) {
@@ -471,19 +474,26 @@ int gptoss_model_layer_attention(gptoss_model *m, int layer) {
   }
   if (m->world == 1) {
     MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
-  } else {  // the normalised rows go to every rank, then this rank routes them and shares the routing rows
-    if ((rc = gptoss_moe_gather_slice(m->moe, m->step_B, m->x, m->proj, m->mlp_norm + l * H, s)) ||
-        (rc = gptoss_moe_sliced_route(m->moe, layer, m->step_B, s)))
-      return m->fail(rc, gptoss_last_error(m->moe));
+  } else {  // this rank normalises and routes its own rows and shares the routing rows with every rank
+    if (B > 0) MK(launch_residual_rmsnorm(m->x, m->proj, m->mlp_norm + l * H, B, (int)H, m->t, s));
+    if ((rc = gptoss_moe_dispatch_route(m->moe, layer, m->step_B, m->t, s))) return m->fail(rc, gptoss_last_error(m->moe));
   }
   return GPTOSS_OK;
+}
+
+int gptoss_model_layer_moe_dispatch(gptoss_model *m, int layer) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (layer < 0 || layer >= m->c.n_layers || m->step_B <= 0) return m->fail(GPTOSS_ERR_STATE, "no step in progress or bad layer");
+  if (m->world == 1) return GPTOSS_OK;
+  const int rc = gptoss_moe_dispatch_rows(m->moe, layer, m->step_B, m->t, m->stream);
+  return rc ? m->fail(rc, gptoss_last_error(m->moe)) : GPTOSS_OK;
 }
 
 int gptoss_model_layer_moe_push(gptoss_model *m, int layer) {
   if (!m) return GPTOSS_ERR_BAD_ARG;
   if (layer < 0 || layer >= m->c.n_layers || m->step_B <= 0) return m->fail(GPTOSS_ERR_STATE, "no step in progress or bad layer");
   const int rc = m->world == 1 ? gptoss_moe_forward(m->moe, layer, m->step_B, m->t, m->x, m->stream)
-                               : gptoss_moe_sliced_push(m->moe, layer, m->step_B, m->stream);
+                               : gptoss_moe_dispatch_push(m->moe, layer, m->stream);
   return rc ? m->fail(rc, gptoss_last_error(m->moe)) : GPTOSS_OK;
 }
 
@@ -547,6 +557,7 @@ int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, i
   int rc = gptoss_model_step_begin(m, tokens_host, pos, B);
   for (int l = 0; !rc && l < m->c.n_layers; ++l) {
     if ((rc = gptoss_model_layer_attention(m, l))) break;
+    if ((rc = gptoss_model_layer_moe_dispatch(m, l))) break;
     if ((rc = gptoss_model_layer_moe_push(m, l))) break;
     rc = gptoss_model_layer_moe_combine(m, l);
   }

@@ -208,22 +208,16 @@ __global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ 
 }
 
 // ---- prefix sums: expert offsets, per-block bases, token-block prefix for the GEMM tile scheduler -----
-// Token-block size of an expert GEMM.  The work items of a launch, (expert, token block, feature tile), go round-robin
-// over the persistent CTAs, so a launch takes (rounds of items) x (time of one item).  An item costs about its block's
-// rows, but not less than kItemFloorRows (below that the ring of weight tiles, whose stages have a fixed round trip,
-// bounds the item, not the MMAs), plus a fixed part (pipeline fill, epilogue).  One block size, a multiple of 16 in
-// [64, 256], is chosen for all local experts: expert e is cut into ceil(rows_e / size) blocks of equal size.  The
-// largest size wins ties, so a batch whose experts all fit one block is never cut (its weights are streamed once).
-constexpr int kItemFloorRows = 176;
-constexpr int kItemFixedRows = 32;
-constexpr int kBlockSizeChoices = 13;  // 256, 240, ..., 64
-
+// Token blocks of the expert GEMMs: expert e is cut into ceil(rows_e / 256) blocks of equal size (a multiple of 16
+// rows), 256 being the widest MMA.  Smaller blocks were measured (forced sizes from 96 to 208 rows, T = 8192, 4 and 32
+// local experts) in the hope of filling the last round of the persistent CTAs: every one was slower, because a work
+// item's time is set by the round trip of its ring stages far more than by its rows (256 rows: 43 us, 128 rows: 31 us).
+// tb.force_rows > 0 still forces another size, for such measurements.
 __device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + size - 1) / size; }
 
 __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d, TileBalance tb) {
   __shared__ int seg_sum[1024];
   __shared__ int off_s[kMaxExperts + 1];
-  __shared__ long long cost_s[2 * kBlockSizeChoices];
   const int E = d.E;
   const int nseg = 1024 / E;
   const int tid = threadIdx.x;
@@ -262,40 +256,14 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
       run += rb.blk_hist[(size_t)b * E + e];
     }
   }
-  // token-block prefix of each GEMM: lane g * 13 + c of warp 0 prices block size 256 - 16 c for GEMM g
-  if (tid < 2 * kBlockSizeChoices && rb.tb_prefix != nullptr) {
-    const int g = tid / kBlockSizeChoices, c = tid % kBlockSizeChoices;
-    const int size = kMaxTileTokens - 16 * c;
-    long long items = 0;
-    int max_rows = 0;
+  // token-block prefix of the local experts for the GEMM tile schedulers
+  if (tid == 0 && rb.tb_prefix != nullptr) {
+    const int size = tb.force_rows > 0 ? min(kMaxTileTokens, max(16, tb.force_rows & ~15)) : kMaxTileTokens;
+    int n = 0;
+    rb.tb_prefix[0] = 0;
     for (int x = d.e_begin; x < d.e_end; ++x) {
-      const int rows = off_s[x + 1] - off_s[x];
-      if (rows > 0) {
-        const int nb = blocks_of(rows, size);
-        items += nb;
-        max_rows = max(max_rows, (blocks_of(rows, nb) + 15) & ~15);
-      }
-    }
-    items *= g ? tb.nft2 : tb.nft1;
-    const long long rounds = (items + tb.sm_count - 1) / tb.sm_count;
-    cost_s[tid] = rounds * (max(max_rows, kItemFloorRows) + kItemFixedRows);
-  }
-  __syncthreads();
-  if ((tid == 0 || tid == kBlockSizeChoices) && rb.tb_prefix != nullptr) {
-    const int g = tid / kBlockSizeChoices;
-    int *out = g ? rb.tb_prefix2 : rb.tb_prefix;
-    if (out != nullptr) {
-      int best = 0;
-      for (int c = 1; c < kBlockSizeChoices; ++c)
-        if (cost_s[g * kBlockSizeChoices + c] < cost_s[g * kBlockSizeChoices + best]) best = c;
-      int size = kMaxTileTokens - 16 * best;
-      if (tb.force_rows > 0) size = min(kMaxTileTokens, max(16, tb.force_rows & ~15));
-      int n = 0;
-      out[0] = 0;
-      for (int x = d.e_begin; x < d.e_end; ++x) {
-        n += blocks_of(off_s[x + 1] - off_s[x], size);
-        out[x - d.e_begin + 1] = n;
-      }
+      n += blocks_of(off_s[x + 1] - off_s[x], size);
+      rb.tb_prefix[x - d.e_begin + 1] = n;
     }
   }
 }
@@ -554,14 +522,13 @@ extern "C" int gptoss_moe_build_offsets_noalloc(int T, int n_experts, int top_k,
   RouteBuffers rb{};
   rb.blk_hist = scratch;
   rb.blk_base = scratch + kNoAllocMaxEntries;
-  rb.tb_prefix = nullptr;  // no GEMM follows: the token-block prefixes are not computed
-  rb.tb_prefix2 = nullptr;
+  rb.tb_prefix = nullptr;  // no GEMM follows: the token-block prefix is not computed
   rb.offsets = offsets_dev;
   rb.sorted = sorted_pair_ids_dev;
   // every entry of the scratch that the scan and the scatter read is first written by this call, so
   // nothing has to start at zero
   if (launch_pair_hist(topk_i_dev, T, d, rb.blk_hist, s) != cudaSuccess ||
-      launch_expert_scan(rb, T, d, TileBalance{1, 1, 1, 0}, s) != cudaSuccess ||
+      launch_expert_scan(rb, T, d, TileBalance{0}, s) != cudaSuccess ||
       launch_scatter_gather(nullptr, 0, 0, topk_i_dev, T, d, rb.blk_base, rb.sorted, RowDispatch{}, s) != cudaSuccess)
     return noalloc_fail(GPTOSS_ERR_CUDA, "kernel launch failed");
   return GPTOSS_OK;

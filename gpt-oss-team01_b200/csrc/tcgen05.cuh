@@ -88,12 +88,6 @@ __device__ __forceinline__ void st_f32_hint(float *p, float v, uint64_t policy) 
 __device__ __forceinline__ void st_b16_hint(void *p, uint16_t v, uint64_t policy) {
   asm volatile("st.global.L2::cache_hint.b16 [%0], %1, %2;" ::"l"(p), "h"(v), "l"(policy) : "memory");
 }
-__device__ __forceinline__ void st_b32_hint(void *p, uint32_t v, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.b32 [%0], %1, %2;" ::"l"(p), "r"(v), "l"(policy) : "memory");
-}
-__device__ __forceinline__ void st_f32x2_hint(void *p, float a, float b, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.v2.f32 [%0], {%1, %2}, %3;" ::"l"(p), "f"(a), "f"(b), "l"(policy) : "memory");
-}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

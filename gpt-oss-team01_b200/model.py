@@ -126,6 +126,8 @@ class Model:
             for m in models:
                 m._check(m.lib.gptoss_model_layer_attention(m._m, layer))
             for m in models:
+                m._check(m.lib.gptoss_model_layer_moe_dispatch(m._m, layer))
+            for m in models:
                 m._check(m.lib.gptoss_model_layer_moe_push(m._m, layer))
             for m in models:
                 m._check(m.lib.gptoss_model_layer_moe_combine(m._m, layer))

@@ -302,8 +302,8 @@ int gptoss_model_create(const gptoss_model_config *cfg, int device, int max_batc
  * process each).  max_batch is the batch of the whole group.  The sequences are dealt out in contiguous slices
  * (gptoss_model_slice): attention, dense GEMMs, KV cache and residual stream of a sequence live on its rank only, so
  * the attention side needs no all-reduce (the reference's ring_all_reduce_tb2_quantize_fp8, parallelism.cpp:1195,
- * has no counterpart); the experts are sharded by rank (n_experts % world == 0) and each layer exchanges the
- * normalised activations and the expert outputs over peer memory (token-sliced form of the MoE block above).
+ * has no counterpart); the experts are sharded by rank (n_experts % world == 0) and each layer exchanges routing
+ * rows, token rows and expert outputs over peer memory (dispatch form of the MoE block above).
  * Every rank loads the same checkpoint (or the same synthetic seed) and keeps its share.  Before the first step
  * the ranks' MoE contexts (gptoss_model_moe_ctx) must be attached to one another with gptoss_comm_export /
  * gptoss_comm_attach (processes) or gptoss_comm_attach_local (one process).  A decode must keep the same batch
@@ -340,16 +340,19 @@ int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, i
  * only (the ranks of a group keep their slices). */
 int gptoss_model_step_rows(gptoss_model *m, const int *tokens_host, const int *rows_host, int pos, int n,
                            int *next_tokens_host);
-/* The phases of gptoss_model_step, which runs begin, then per layer attention / moe_push / moe_combine, then end.
- * In a group, B is the batch of the group and tokens_host / next_tokens_host hold this rank's sequences only.
+/* The phases of gptoss_model_step, which runs begin, then per layer attention / moe_dispatch / moe_push / moe_combine,
+ * then end.  In a group, B is the batch of the group and tokens_host / next_tokens_host hold this rank's sequences only.
  * Separate entry points so that one host thread can drive the ranks of a group in turn (each phase for every rank
- * before the next phase: a rank's moe_push waits on the device for every rank's attention phase, its moe_combine
- * for every rank's moe_push).  attention: RMSNorm, QKV GEMM, RoPE + KV store, attention, o-proj GEMM, residual +
- * RMSNorm (group: stored into every rank's gathered activations).  moe_push: the MoE block (group: routing, expert
- * GEMMs, rows pushed to their owners).  moe_combine: group only, the owner's slot-ordered sum into its residual
- * rows.  end: final norm, classifier, argmax, synchronises and reports device-side errors. */
+ * before the next phase: a rank's moe_dispatch waits on the device for every rank's attention phase, its moe_push for
+ * every rank's moe_dispatch, its moe_combine for every rank's moe_push).  attention: RMSNorm, QKV GEMM, RoPE + KV
+ * store, attention, o-proj GEMM, residual + RMSNorm (group: and the routing of this rank's rows, shared with all).
+ * moe_dispatch: group only, grouping of the batch and this rank's rows to the experts' ranks (dispatch form of the MoE
+ * block above).  moe_push: the MoE block (group: expert GEMMs on the received rows, outputs pushed to their owners).
+ * moe_combine: group only, the owner's slot-ordered sum into its residual rows.  end: final norm, classifier with the
+ * argmax fused, synchronises and reports device-side errors. */
 int gptoss_model_step_begin(gptoss_model *m, const int *tokens_host, int pos, int B);
 int gptoss_model_layer_attention(gptoss_model *m, int layer);
+int gptoss_model_layer_moe_dispatch(gptoss_model *m, int layer);
 int gptoss_model_layer_moe_push(gptoss_model *m, int layer);
 int gptoss_model_layer_moe_combine(gptoss_model *m, int layer);
 int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host);

@@ -43,6 +43,19 @@ int ref_forward(void *h, int token, int pos, float *logits_out) {
   return sample_argmax(logits, tr->config.vocab_size);
 }
 
+// forward() through the first n_layers layers only (the loop bound is the configuration's layer count, run.cpp:519;
+// the per-layer weight pointers were laid out for the full model when it was opened, so the prefix sees the same
+// weights).  Afterwards ref_last_moe_state describes layer n_layers - 1.  The KV rows it writes for `pos` are the
+// ones the full forward() writes, so calling it before ref_forward at the same position changes nothing.
+void ref_forward_prefix(void *h, int token, int pos, int n_layers) {
+  Transformer *tr = static_cast<Transformer *>(h);
+  const int full = tr->config.n_layers;
+  if (n_layers < 1 || n_layers > full) return;
+  tr->config.n_layers = n_layers;
+  forward(tr, token, pos);
+  tr->config.n_layers = full;
+}
+
 // State left behind by the LAST layer's MoE block after a forward() call: the block input t
 // (run.cpp:623), the routing result (run.cpp:636-638; topk_v already softmaxed) and the block
 // output e_agg (run.cpp:641-704).  None of these buffers is written again before forward() returns.

@@ -145,6 +145,8 @@ class Reference:
         lib.ref_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         lib.ref_forward.restype = C.c_int
         lib.ref_last_moe_state.argtypes = [C.c_void_p] + [C.c_void_p] * 5
+        if hasattr(lib, "ref_forward_prefix"):
+            lib.ref_forward_prefix.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
         lib.ref_moe_rows.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p,
                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _f32p, C.c_void_p,
                                      C.c_void_p]
@@ -168,6 +170,10 @@ class Reference:
 
     def forward(self, h, token, pos, logits=None):
         return self.lib.ref_forward(h, int(token), int(pos), _opt(logits, np.float32))
+
+    def forward_prefix(self, h, token, pos, n_layers):
+        """forward() through the first n_layers layers only; last_moe_state then describes layer n_layers - 1."""
+        self.lib.ref_forward_prefix(h, int(token), int(pos), int(n_layers))
 
     def last_moe_state(self, h, H, E, k):
         t = np.empty(H, np.float32)

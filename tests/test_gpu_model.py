@@ -1,11 +1,15 @@
 """Whole-model decode (embedding, attention with sinks / sliding window, dense GEMMs, MoE block, argmax)
-against the reference's own forward() on the seeded gpt-oss-7m checkpoint (tests/golden/moe_7m_golden.npz:
-32 random prompt ids, 64 greedy tokens, per-position argmax, top-2 logit gap and 64 probe logits).
+against the reference's own forward() on seeded gpt-oss-7m checkpoints (tests/golden/moe_7m_golden.npz:
+32 random prompt ids, 64 greedy tokens, per-position argmax, top-2 logit gap, router-score gaps and 64 probe logits;
+tests/golden/greedy_7m_golden.npz: the greedy continuation of a second seed).
 
 The GPU path rounds GEMM inputs and the KV cache to bf16 (like the reference's GPU engine), the CPU reference
 is fp32: logits agree to ~1e-3 (they have a spread of 0.1), so the argmax must agree wherever the reference's
-top-2 gap exceeds that noise.  The fixture's seed was picked (tests/golden/make_golden.py) so that none of the first
-32 generated tokens is such a near-tie: the free-running decode must reproduce them all."""
+top-2 gap exceeds that noise.  A second discrete effect is a token whose 4th and 5th router scores nearly tie: the
+bf16 engine may pick the other expert, which moves that position's logits by far more than rounding noise and stays in
+the KV cache.  The seeds of the fixtures were picked with this in mind (tests/golden/make_golden.py): the teacher-forced
+one has no such router tie on any of its 95 positions, the free-running one no near-tie among the top-2 logits of its
+first 32 generated tokens, all of which the decode must reproduce."""
 from pathlib import Path
 
 import numpy as np
@@ -18,6 +22,8 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 GOLDEN = Path(__file__).parent / "golden" / "moe_7m_golden.npz"
+GREEDY = Path(__file__).parent / "golden" / "greedy_7m_golden.npz"
+ROUTE_GAP_SAFE = 4e-4  # smallest 4th/5th router-score gap at which the expert choice cannot flip (flips seen at ~1e-4)
 LOGIT_TOL = 4e-3      # absolute; logits have a standard deviation of 0.10
 MARGIN_SAFE = 8e-3    # reference top-2 gap above which the greedy token must be identical
 
@@ -41,11 +47,13 @@ def test_teacher_forced_decode_matches_reference_forward(golden, checkpoint):
     n_pos = len(golden["next_token"])
     m = model.Model(cfg, max_batch=2, max_seq=128)
     m.load_bin(checkpoint)
+    assert float(golden["route_gap"].min()) > ROUTE_GAP_SAFE  # what the fixture's seed was chosen for
     agree, safe_total = 0, 0
     for pos in range(n_pos):
         nxt = m.step(seq[pos:pos + 1], pos)
         got = m.logits(0)
-        np.testing.assert_allclose(got[golden["probe_idx"]], golden["probe_logits"][pos], rtol=0, atol=LOGIT_TOL)
+        np.testing.assert_allclose(got[golden["probe_idx"]], golden["probe_logits"][pos], rtol=0, atol=LOGIT_TOL,
+                                   err_msg=f"position {pos}")
         if golden["top2_margin"][pos] > MARGIN_SAFE:
             safe_total += 1
             assert nxt[0] == golden["next_token"][pos], (pos, nxt[0], golden["next_token"][pos])
@@ -55,11 +63,14 @@ def test_teacher_forced_decode_matches_reference_forward(golden, checkpoint):
     m.close()
 
 
-def test_free_running_greedy_decode_first_32_tokens(golden, checkpoint):
+def test_free_running_greedy_decode_first_32_tokens(tmp_path):
     from gptoss_b200 import model
+    golden = np.load(GREEDY)
     cfg = binfmt.config_7m()
+    ckpt = tmp_path / "gpt-oss-7m-greedy.bin"
+    binfmt.write_synthetic(str(ckpt), cfg, int(golden["seed"]))
     m = model.Model(cfg, max_batch=4, max_seq=128)
-    m.load_bin(checkpoint)
+    m.load_bin(ckpt)
     prompts = np.stack([golden["prompt"]] * 3).astype(np.int32)
     prompts[2] = synth.uniform_ids(5, 9, prompts.shape[1], cfg.vocab_size)  # an unrelated sequence in the batch
     out = m.generate(prompts, 64)
