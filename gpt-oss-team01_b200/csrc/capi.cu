@@ -25,7 +25,6 @@ struct LayerWeights {
   __nv_bfloat16 *w2 = nullptr;        // [E_local][H][I]
   float *b2 = nullptr;                // [E_local][H]
   CUtensorMap map_w1, map_w2, map_wr;
-  CUtensorMap map_w1_wide, map_w2_wide;  // both weight tiles of a ring stage in one box
   bool ready = false;
 };
 
@@ -75,8 +74,6 @@ struct gptoss_ctx {
   float *staging = nullptr;           // fp32 scratch for weight conversion
   size_t staging_elems = 0;
   CUtensorMap map_x, map_h;
-  CUtensorMap map_x_wide[3], map_h_wide[3];  // the same rows with boxes of 64, 128 and 256 rows
-  bool wide_copies = true;                   // GPTOSS_NARROW_COPIES=1: one box per weight tile and per 32 rows (A/B runs)
   std::vector<LayerWeights> layers;
   std::string err;
 
@@ -133,8 +130,6 @@ int alloc_layer(gptoss_ctx *ctx, LayerWeights &w) {
   CK(dev_alloc(&w.b2, EL * H));
   CK(encode_weight_map(&w.map_w1, w.w1, H, I, EL * 2));
   CK(encode_weight_map(&w.map_w2, w.w2, I, H, EL));
-  CK(encode_weight_map_wide(&w.map_w1_wide, w.w1, H, I, EL * 2, true));
-  CK(encode_weight_map_wide(&w.map_w2_wide, w.w2, I, H, EL, false));
   CK(encode_map_2d(&w.map_wr, w.router_w, H, E, (uint32_t)((E + 15) & ~(size_t)15)));
   return GPTOSS_OK;
 }
@@ -160,11 +155,6 @@ GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
   memset(&a, 0, sizeof a);
   a.map_w = mlp1 ? w.map_w1 : w.map_w2;
   a.map_act = mlp1 ? ctx->map_x : ctx->map_h;
-  if (ctx->wide_copies && (mlp1 || ctx->d.H > kTileF)) {  // the one-tile down GEMM (at most 128 features) has no pair of tiles
-    a.wide = 1;
-    a.map_w_wide = mlp1 ? w.map_w1_wide : w.map_w2_wide;
-    for (int i = 0; i < 3; ++i) a.map_act_wide[i] = mlp1 ? ctx->map_x_wide[i] : ctx->map_h_wide[i];
-  }
   a.offsets = ctx->rb.offsets;
   a.tb_prefix = ctx->rb.tb_prefix;
   a.e_begin = ctx->d.e_begin;
@@ -276,9 +266,6 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   if (e == cudaSuccess) A(cudaMemset(ctx->gate_up, 0, P * I * sizeof(__nv_bfloat16)));
   if (e == cudaSuccess) A(encode_act_map(&ctx->map_x, ctx->x_packed, H, P));
   if (e == cudaSuccess) A(encode_act_map(&ctx->map_h, ctx->gate_up, I, P));
-  if (e == cudaSuccess) A(encode_act_maps_wide(ctx->map_x_wide, ctx->x_packed, H, P));
-  if (e == cudaSuccess) A(encode_act_maps_wide(ctx->map_h_wide, ctx->gate_up, I, P));
-  if (const char *v = getenv("GPTOSS_NARROW_COPIES")) ctx->wide_copies = !(v[0] == '1');
   if (e != cudaSuccess) {
     gptoss_ctx_destroy(ctx);
     return GPTOSS_ERR_CUDA;

@@ -21,10 +21,14 @@
 // of this launch (read from the expert offsets, rounded to 32 rows), and the ring takes as many stages as
 // fit into shared memory (decode: 4 x 52 KiB).
 //
-// Every mbarrier wait is bounded: when a wait gives up the CTA raises an abort flag and records a time-out in
-// the status words.  Every role then leaves its tile loop at once: the producer waits (bounded) for the copies
-// it has armed, the MMA thread for the MMAs it has issued, the epilogue warps agree on leaving through a
-// barrier reduction (so their named-barrier counts stay equal); then the CTA frees its TMEM and returns.
+// Every mbarrier wait is bounded: when a wait gives up the CTA raises an abort flag and records a time-out in the
+// status words.  Every later wait of the CTA returns at once, and every role looks at the flag at the top of each tile
+// and leaves its loop there (the epilogue warps of the row GEMM agree on it through a barrier reduction, so that their
+// named-barrier counts stay equal).  Then the producer waits (bounded) for the copies it has armed, the MMA thread for
+// the MMAs it has issued, and the CTA frees its TMEM and returns.  The flag is deliberately NOT tested per ring stage:
+// making the single-thread producer / MMA loops branch on the result of each wait was measured 8-15 % slower (both
+// GEMMs, T = 1024 and T = 8192), so a role may still issue the rest of ONE tile's copies or MMAs after a time-out; they
+// touch only this CTA's ring and accumulator, and the drain below waits for them.
 #include <cstdlib>
 
 #include "kernels.cuh"
@@ -51,6 +55,7 @@ constexpr int kRingBytes = 216 * 1024;
 template <int NA, bool GLU>
 struct TileCfg {
   static constexpr int kAStageBytes = NA * kATileBytes;
+  static constexpr int kAccBuffers = (NA == 2) ? 1 : 2;   // two tiles fill all 512 TMEM columns at 256 tokens
   static constexpr int kMetaTokens = GLU ? 1 : kMaxTileTokens;  // pair/weight staging only for the down projection
   static constexpr int kTileFeat = (NA == 2 && !GLU) ? 2 * kTileF : kTileF;  // output features per tile
   static constexpr int kSlabs = GLU ? 2 : 1;                // weight slabs per expert in the tensor map
@@ -81,15 +86,15 @@ struct Tile {
 };
 
 // Items of an expert are ordered feature tile by feature tile with the token block fastest (concurrently running
-// CTAs then share a weight tile in L2), or, with ft_fastest, token block by token block with the feature tile fastest
+// CTAs then share a weight tile in L2), or, with FT_FASTEST, token block by token block with the feature tile fastest
 // (they share the token rows instead: right when the "token" side is the large streamed operand).
-template <int TILE_FEAT, class C>
-__device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, int nft, bool ft_fastest, int &cur, Tile &t) {
+template <int TILE_FEAT, bool FT_FASTEST, class C>
+__device__ __forceinline__ bool decode_tile(int idx, const C *c, int n_local, int nft, int &cur, Tile &t) {
   while (cur < n_local && idx >= c->tbp[cur + 1] * nft) ++cur;
   if (cur >= n_local) return false;
   const int r = idx - c->tbp[cur] * nft;
   const int nb = c->tbp[cur + 1] - c->tbp[cur];
-  const int ft = ft_fastest ? r % nft : r / nb, tb = ft_fastest ? r / nft : r - ft * nb;
+  const int ft = FT_FASTEST ? r % nft : r / nb, tb = FT_FASTEST ? r / nft : r - ft * nb;
   // an expert with more than 256 rows is cut into nb blocks of (almost) equal size, a multiple of 16 rows
   const int rows = c->off[cur + 1] - c->off[cur];
   const int blk = (((rows + nb - 1) / nb) + 15) & ~15;
@@ -109,6 +114,12 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
 }
 
+// OUT16 (with !GLU): the output rows are bf16 instead of fp32 (same row and element indexing).
+// AMAX (with !GLU): instead of storing the products, the epilogue keeps for every output feature (a TMEM lane) the
+// largest value over the token columns of the tile and the row id it came from, i.e. one (max, argmax) partial per
+// (token block, feature), and the items are ordered feature tile fastest.  With the operand roles swapped — the
+// batch's activations as the "weights", a vocabulary-sized matrix as the "tokens" — this is the classifier with the
+// greedy argmax fused: the logits never reach memory.
 // OR of `pred` over the eight epilogue warps (named barrier 1): every epilogue thread gets the same answer
 __device__ __forceinline__ bool epilogue_any(bool pred) {
   uint32_t r;
@@ -122,41 +133,8 @@ __device__ __forceinline__ bool epilogue_any(bool pred) {
       : "memory");
   return r != 0;
 }
+__device__ __forceinline__ bool aborting(const int *flag) { return *reinterpret_cast<const volatile int *>(flag) != 0; }
 
-// The operands of one k-block into a ring stage.  With the wide tensor maps (a.wide) the two weight tiles come as ONE
-// box (the gate and up slabs of the same 128 features, or 256 adjacent features) and the token rows as boxes of 256,
-// 128, 64 and 32 rows (largest first), so a stage is 2 to 5 copy instructions instead of up to 10: the copy engine
-// takes its requests one at a time, and at 256-row blocks the request rate, not the bytes, bounded the ring.
-template <int NA, bool GLU>
-__device__ __forceinline__ void load_weights(const GemmArgs &a, uint32_t sa, uint32_t bar, int kb, const Tile &t, uint64_t pol) {
-  constexpr int kSlabs = GLU ? 2 : 1;
-  if (NA == 2 && a.wide) {
-    tma_load_3d_hint(sa, &a.map_w_wide, bar, kb * kBlockK, t.f0, t.e * kSlabs, pol);
-    return;
-  }
-  tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * kSlabs, pol);
-  if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
-    tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF, GLU ? t.e * kSlabs + 1 : t.e * kSlabs,
-                     pol);
-}
-__device__ __forceinline__ void load_rows(const GemmArgs &a, uint32_t sb, uint32_t bar, int kb, int row0, int n_chunks) {
-  int c = 0;
-  if (a.wide) {
-#pragma unroll
-    for (int lg = 3; lg >= 1; --lg)  // boxes of 256, 128, 64 rows
-      while (n_chunks - c >= (1 << lg)) {
-        tma_load_2d(sb + c * kBChunkBytes, &a.map_act_wide[lg - 1], bar, kb * kBlockK, row0 + c * kTokChunk);
-        c += 1 << lg;
-      }
-  }
-  for (; c < n_chunks; ++c) tma_load_2d(sb + c * kBChunkBytes, &a.map_act, bar, kb * kBlockK, row0 + c * kTokChunk);
-}
-
-// AMAX (with !GLU): instead of storing the products, the epilogue keeps for every output feature (a TMEM lane) the
-// largest value over the token columns of the tile and the row id it came from, i.e. one (max, argmax) partial per
-// (token block, feature).  With the operand roles swapped — the batch's activations as the "weights", a vocabulary-
-// sized matrix as the "tokens" — this is the classifier with the greedy argmax fused: the logits never reach memory.
-// OUT16 (with !GLU): the output rows are bf16 instead of fp32 (same row and element indexing).
 template <int NA, bool GLU, bool AMAX = false, bool OUT16 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmArgs a) {
   static_assert(!AMAX || (NA == 2 && !GLU), "the argmax epilogue exists for the two-tile row GEMM only");
@@ -169,7 +147,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_local = a.n_local, nft = a.n_feat_tiles;
-  const bool ftf = a.ft_fastest != 0;
 
   if (threadIdx.x == 0) {
     ctrl->max_rows = 0;
@@ -217,11 +194,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   const int b_rows = max(kTokChunk, (ctrl->max_rows + kTokChunk - 1) / kTokChunk * kTokChunk);
   const int stage_bytes = Cfg::kAStageBytes + b_rows * kBlockK * 2;
   const int n_stages = min(kMaxStages, kRingBytes / stage_bytes);
-  // accumulators: each weight tile of a stage owns cols_per_tile TMEM columns; when no tile of this launch has more
-  // than 128 token rows two sets fit into the 512 columns and the epilogue of a tile overlaps the MMAs of the next
-  const int cols_per_tile = ctrl->max_rows <= 128 ? 128 : kMaxTileTokens;
-  const int acc_stride = NA * cols_per_tile;
-  const int n_acc = min(2, kTmemCols / acc_stride);
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -229,13 +201,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       int stage = 0, cur = 0;
       uint32_t phase = 0, armed = 0, last_par = 0;
       Tile t;
-      // each weight byte is used once per launch; with the roles swapped (ft_fastest) the "weights" are the small
-      // operand that every item reads again
-      const uint64_t pol_w = ftf ? l2_policy_evict_last() : l2_policy_evict_first();
+      // each weight byte is used once per launch; with the roles swapped (AMAX) the "weights" are the small operand
+      // that every item reads again
+      const uint64_t pol_w = AMAX ? l2_policy_evict_last() : l2_policy_evict_first();
       // Head start: the weights do not depend on the kernel before this one, so the weight tiles of the first
       // ring fill are requested before waiting for it; its outputs (the activation rows) are loaded after.
       int pre = 0;
-      if ((int)blockIdx.x < total_tiles && decode_tile<Cfg::kTileFeat>(blockIdx.x, ctrl, n_local, nft, ftf, cur, t)) {
+      if ((int)blockIdx.x < total_tiles && decode_tile<Cfg::kTileFeat, AMAX>(blockIdx.x, ctrl, n_local, nft, cur, t)) {
         const int n_chunks = (max(16, (t.n_valid + 15) & ~15) + kTokChunk - 1) / kTokChunk;
         pre = min(n_stages, a.k_blocks);
         for (int kb = 0; kb < pre; ++kb) {
@@ -243,12 +215,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           const uint32_t sa = ring + kb * stage_bytes;
           armed |= 1u << kb;
           mbar_expect_tx(bar, Cfg::kAStageBytes + n_chunks * kBChunkBytes);
-          load_weights<NA, GLU>(a, sa, bar, kb, t, pol_w);
+          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * Cfg::kSlabs, pol_w);
+          if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
+            tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF,
+                             GLU ? t.e * Cfg::kSlabs + 1 : t.e * Cfg::kSlabs, pol_w);
         }
         pdl_wait();
         pdl_launch_dependents();
         for (int kb = 0; kb < pre; ++kb)
-          load_rows(a, ring + kb * stage_bytes + Cfg::kAStageBytes, smem_u32(&ctrl->full[kb]), kb, t.row0, n_chunks);
+          for (int c = 0; c < n_chunks; ++c)
+            tma_load_2d(ring + kb * stage_bytes + Cfg::kAStageBytes + c * kBChunkBytes, &a.map_act,
+                        smem_u32(&ctrl->full[kb]), kb * kBlockK, t.row0 + c * kTokChunk);
         stage = pre % n_stages;
         phase = (pre == n_stages) ? 1u : 0u;
         cur = 0;
@@ -257,29 +234,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         pdl_launch_dependents();
       }
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
+        if (aborting(&ctrl->abort) || !decode_tile<Cfg::kTileFeat, AMAX>(idx, ctrl, n_local, nft, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const int n_chunks = (n_mma + kTokChunk - 1) / kTokChunk;
         const uint32_t tx = Cfg::kAStageBytes + n_chunks * kBChunkBytes;
-        bool ok = true;
         for (int kb = (idx == (int)blockIdx.x) ? pre : 0; kb < a.k_blocks; ++kb) {
-          if (!(ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x100 | stage))) break;
+          mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x100 | stage);
           const uint32_t bar = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = ring + stage * stage_bytes;
           armed |= 1u << stage;
           last_par = (last_par & ~(1u << stage)) | (phase << stage);
           mbar_expect_tx(bar, tx);
-          load_weights<NA, GLU>(a, sa, bar, kb, t, pol_w);
-          load_rows(a, sa + Cfg::kAStageBytes, bar, kb, t.row0, n_chunks);
+          tma_load_3d_hint(sa, &a.map_w, bar, kb * kBlockK, t.f0, t.e * Cfg::kSlabs, pol_w);
+          if (NA == 2)  // GLU: the up rows of the same features (next slab); else the next 128 features (zero-filled past the end)
+            tma_load_3d_hint(sa + kATileBytes, &a.map_w, bar, kb * kBlockK, GLU ? t.f0 : t.f0 + kTileF,
+                             GLU ? t.e * Cfg::kSlabs + 1 : t.e * Cfg::kSlabs, pol_w);
+          const uint32_t sb = sa + Cfg::kAStageBytes;
+          for (int c = 0; c < n_chunks; ++c)
+            tma_load_2d(sb + c * kBChunkBytes, &a.map_act, bar, kb * kBlockK, t.row0 + c * kTokChunk);
           if (++stage == n_stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (!ok) break;  // aborting: arm nothing more
       }
-      // drain: every armed stage must have landed before the CTA may exit (bounded).  A stage is re-armed only
-      // after its previous phase was consumed, so only the last armed phase of a stage can still be in flight.
+      // drain: every armed stage must have landed before the CTA may exit (bounded)
       for (int s = 0; s < n_stages; ++s)
         if (armed & (1u << s)) {
           const uint32_t par = (last_par >> s) & 1u;
@@ -294,15 +273,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       uint32_t phase = 0, acc_phase = 0;
       Tile t;
       for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-        if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
+        if (aborting(&ctrl->abort) || !decode_tile<Cfg::kTileFeat, AMAX>(idx, ctrl, n_local, nft, cur, t)) break;
         const int n_mma = max(16, (t.n_valid + 15) & ~15);
         const uint32_t idesc = umma_idesc(n_mma);
-        if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1u, &ctrl->abort, a.status, 0x200 | acc)) break;
+        mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1u, &ctrl->abort, a.status, 0x200 | acc);
         tc_fence_after();
-        const uint32_t d0 = tmem_base + (uint32_t)(acc * acc_stride);
-        bool ok = true;
+        const uint32_t d0 = tmem_base + (uint32_t)(acc * kMaxTileTokens);
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          if (!(ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x300 | stage))) break;
+          mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x300 | stage);
           tc_fence_after();
           const uint32_t sa = ring + stage * stage_bytes;
           const uint64_t da0 = smem_desc_sw128(sa);
@@ -312,7 +290,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           for (int k = 0; k < kBlockK / 16; ++k) {
             const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
             umma_bf16(d0, da0 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
-            if (NA == 2) umma_bf16(d0 + cols_per_tile, da1 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            if (NA == 2) umma_bf16(d0 + kMaxTileTokens, da1 + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));
           if (++stage == n_stages) {
@@ -320,15 +298,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             phase ^= 1u;
           }
         }
-        if (!ok) break;
         umma_commit(smem_u32(&ctrl->tmem_full[acc]));
-        if (++acc == n_acc) {
+        if (++acc == Cfg::kAccBuffers) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
-      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
-        // aborting: the MMAs issued so far must have retired before TMEM and the ring are given up (bounded)
+      if (aborting(&ctrl->abort)) {  // the MMAs issued so far must have retired before TMEM and the ring are given up
         umma_commit(smem_u32(&ctrl->mma_done));
         for (uint32_t i = 0; i < kSpinLimit; ++i)
           if (mbar_try_wait(smem_u32(&ctrl->mma_done), 0)) break;
@@ -343,26 +319,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     uint32_t acc_phase = 0;
     Tile t;
     const uint64_t pol_keep = l2_policy_evict_last();  // the outputs are read again by the next kernel
-    constexpr size_t esize = OUT16 ? 2 : 4;  // mlp2 output element: fp32, or bf16 on the bf16 wire
     for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x) {
-      if (!decode_tile<Cfg::kTileFeat>(idx, ctrl, n_local, nft, ftf, cur, t)) break;
-      // Top of every tile: all epilogue threads meet and learn whether any role gave up.  The answer is the same for
-      // all of them, so they leave together; the meeting also means that every thread has left the previous tile
-      // before its staging slots (dst_s / w_s) are overwritten below.
-      if (epilogue_any(*reinterpret_cast<volatile int *>(&ctrl->abort) != 0)) break;
+      if (!decode_tile<Cfg::kTileFeat, AMAX>(idx, ctrl, n_local, nft, cur, t)) break;
+      if constexpr (GLU) {
+        if (aborting(&ctrl->abort)) break;  // no named barrier in this loop: each thread may leave on its own
+      } else {
+        // all epilogue threads meet, learn whether any role gave up and leave together; the meeting also means that
+        // every thread has left the previous tile before its staging slots (dst_s / w_s) are overwritten below
+        if (epilogue_any(aborting(&ctrl->abort))) break;
+      }
       const int f = t.f0 + q * 32 + lane;
       const bool f_ok = f < a.n_feat;
       if constexpr (AMAX) {
         // running first maximum of this thread's columns for its two features (f: first tile, f + 128: second tile)
         float best0 = -3.402823466e+38f, best1 = -3.402823466e+38f;
         int at0 = 0x7fffffff, at1 = 0x7fffffff;
-        const bool got = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
+        mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
         tc_fence_after();
-        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_stride);
-        for (int c0 = half * 16; got && c0 < t.n_valid; c0 += 32) {
+        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kMaxTileTokens);
+        for (int c0 = half * 16; c0 < t.n_valid; c0 += 32) {
           uint32_t r0[16], r1[16];
           tmem_ld16(tbase + c0, r0);
-          tmem_ld16(tbase + cols_per_tile + c0, r1);
+          tmem_ld16(tbase + kMaxTileTokens + c0, r1);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -378,7 +356,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         }
         tc_fence_before();
         mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
-        if (++acc == n_acc) {
+        if (++acc == Cfg::kAccBuffers) {
           acc = 0;
           acc_phase ^= 1u;
         }
@@ -399,14 +377,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           if (f_ok) a.amax_val[o + f] = best0, a.amax_at[o + f] = at0;
           if (f + kTileF < a.n_feat) a.amax_val[o + f + kTileF] = best1, a.amax_at[o + f + kTileF] = at1;
         }
-        continue;  // the meeting at the top of the next tile keeps the merge slots of this one intact until read
+        continue;
       }
       if constexpr (!GLU) {
         for (int n = et; n < t.n_valid; n += kEpilogueThreads) {
           const int pair = a.sorted[t.row0 + n];
           char *base = reinterpret_cast<char *>(a.y_pairs);
           if (a.n_owners > 1) base = reinterpret_cast<char *>(a.y_owner[min(a.n_owners - 1, (pair / a.top_k) / a.slice_tokens)]);
-          ctrl->dst_s[acc][n] = base + (size_t)pair * a.n_feat * esize;
+          ctrl->dst_s[acc][n] = base + (size_t)pair * a.n_feat * (OUT16 ? 2 : 4);
           ctrl->w_s[acc][n] = a.topk_w[pair];
         }
         epilogue_bar_sync();
@@ -416,20 +394,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const float bias1 = (GLU && f_ok)            ? a.bias_b[(size_t)t.e * a.n_feat + f]
                           : (f1_ok && a.bias_a) ? a.bias_a[(size_t)t.e * a.n_feat + f + kTileF]
                                                 : 0.f;
-      const bool got = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
+      mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, &ctrl->abort, a.status, 0x400 | acc);
       tc_fence_after();
-      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_stride);
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kMaxTileTokens);
       // 16 token columns at a time, alternating between the two warps of the quadrant; the 16 values of a
       // chunk are independent chains, computed branch-free so that they overlap
-      for (int c0 = half * 16; got && c0 < t.n_valid; c0 += 32) {
+      for (int c0 = half * 16; c0 < t.n_valid; c0 += 32) {
         uint32_t r0[16], r1[16];
         tmem_ld16(tbase + c0, r0);
-        if (NA == 2) tmem_ld16(tbase + cols_per_tile + c0, r1);
+        if (NA == 2) tmem_ld16(tbase + kMaxTileTokens + c0, r1);
         tmem_ld_wait();
         float v[16];
-        // One lane = one feature, so a warp's store of one token column covers 32 adjacent features of that row (128
-        // bytes of fp32, 64 of bf16).  Pairing lanes through shuffles to store two adjacent elements per lane was
-        // measured slower: the down GEMM's epilogue is exposed (one accumulator set), and the shuffles lengthen it.
         if constexpr (GLU) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -442,41 +417,46 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             if (f_ok && c0 + j + 1 < t.n_valid) st_b16_hint(dst + (size_t)(j + 1) * a.n_feat, __bfloat16_as_ushort(pk.y), pol_keep);
           }
         } else {
-          char *pr[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            pr[j] = ctrl->dst_s[acc][c0 + j];
-            v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
-          }
           if constexpr (OUT16) {
+            char *pr[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              pr[j] = ctrl->dst_s[acc][c0 + j];
+              v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (f_ok && c0 + j < t.n_valid)
                 st_b16_hint(pr[j] + (size_t)f * 2, __bfloat16_as_ushort(__float2bfloat16_rn(v[j])), pol_keep);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (f_ok && c0 + j < t.n_valid) st_f32_hint(reinterpret_cast<float *>(pr[j]) + f, v[j], pol_keep);
-          }
-          if constexpr (NA == 2) {
-            if constexpr (OUT16) {
+            if constexpr (NA == 2) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
                 if (f1_ok && c0 + j < t.n_valid)
                   st_b16_hint(pr[j] + (size_t)(f + kTileF) * 2,
                               __bfloat16_as_ushort(__float2bfloat16_rn((__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j])), pol_keep);
-            } else {
+            }
+          } else {
+            float *pr[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              pr[j] = reinterpret_cast<float *>(ctrl->dst_s[acc][c0 + j]);
+              v[j] = (__uint_as_float(r0[j]) + bias0) * ctrl->w_s[acc][c0 + j];
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f_ok && c0 + j < t.n_valid) st_f32_hint(pr[j] + f, v[j], pol_keep);
+            if constexpr (NA == 2) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
                 if (f1_ok && c0 + j < t.n_valid)
-                  st_f32_hint(reinterpret_cast<float *>(pr[j]) + f + kTileF, (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j], pol_keep);
+                  st_f32_hint(pr[j] + f + kTileF, (__uint_as_float(r1[j]) + bias1) * ctrl->w_s[acc][c0 + j], pol_keep);
             }
           }
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
-      if (++acc == n_acc) {
+      if (++acc == Cfg::kAccBuffers) {
         acc = 0;
         acc_phase ^= 1u;
       }
@@ -593,31 +573,6 @@ cudaError_t encode_map_2d(CUtensorMap *m, const void *base, uint64_t K, uint64_t
 
 cudaError_t encode_act_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows) {
   return encode_map_2d(m, base, K, rows, (uint32_t)kTokChunk);
-}
-
-// The same token rows with boxes of 64, 128 and 256 rows (wide[0..2]).
-cudaError_t encode_act_maps_wide(CUtensorMap *wide, const void *base, uint64_t K, uint64_t rows) {
-  for (int i = 0; i < 3; ++i) {
-    cudaError_t e = encode_map_2d(&wide[i], base, K, rows, (uint32_t)(kTokChunk << (i + 1)));
-    if (e != cudaSuccess) return e;
-  }
-  return cudaSuccess;
-}
-
-// Both weight tiles of a ring stage as one box: {64, 128, 2} (the gate and up slabs of 128 features) when pair_slabs,
-// else {64, 256, 1} (256 adjacent features; rows past the last feature are zero-filled).
-cudaError_t encode_weight_map_wide(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs, bool pair_slabs) {
-  EncodeTiledFn fn;
-  cudaError_t e = get_encode_fn(&fn);
-  if (e != cudaSuccess) return e;
-  const cuuint64_t dims[3] = {K, rows, slabs};
-  const cuuint64_t strides[2] = {K * 2, K * rows * 2};
-  const cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)(pair_slabs ? kTileF : 2 * kTileF), pair_slabs ? 2u : 1u};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 }  // namespace gptoss

@@ -108,9 +108,6 @@ cudaError_t encode_map_2d(CUtensorMap *m, const void *base, uint64_t K, uint64_t
 struct GemmArgs {
   CUtensorMap map_w;    // weights: 3-D (k, feature, expert-slab), bf16, 128-byte swizzle, box {64,128,1}
   CUtensorMap map_act;  // activations: 2-D (k, row), bf16, 128-byte swizzle, box {64,32}
-  int wide;                    // the two maps below are set: fewer, larger copies per ring stage
-  CUtensorMap map_w_wide;      // both weight tiles of a stage as one box: {64,128,2} (gate/up slabs) or {64,256,1}
-  CUtensorMap map_act_wide[3]; // the activations with boxes of 64, 128 and 256 rows
   const int *offsets;    // [E+1] global expert offsets
   const int *tb_prefix;  // [E_local+1]
   int e_begin, n_local;  // local expert range
@@ -130,7 +127,6 @@ struct GemmArgs {
   int signal_step;               // signal_step by the last CTA to finish (0 = no signalling)
   int *signal_counter;           // CTAs finished so far (left at 0)
   int top_k;
-  int ft_fastest;          // order of the items of an expert: 0 = token block fastest, 1 = feature tile fastest
   float *amax_val;         // argmax epilogue (launch_grouped_amax): per (token block, feature) the largest product over
   int *amax_at;            // the block's rows, and the id of the row that gave it (first one on ties)
   const int *sorted;       // mlp2: [P]
@@ -144,8 +140,6 @@ cudaError_t launch_grouped_amax(const GemmArgs &a, int sm_count, cudaStream_t s)
 // weights: base of [slabs][rows][K] bf16;  activations: base of [rows][K] bf16.
 cudaError_t encode_weight_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs);
 cudaError_t encode_act_map(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows);
-cudaError_t encode_act_maps_wide(CUtensorMap *wide, const void *base, uint64_t K, uint64_t rows);
-cudaError_t encode_weight_map_wide(CUtensorMap *m, const void *base, uint64_t K, uint64_t rows, uint64_t slabs, bool pair_slabs);
 
 // model_kernels.cu — the kernels around the MoE block that a decode step needs
 cudaError_t launch_embed(const int *tokens, const __nv_bfloat16 *table, int B, int H, int vocab, float *x, cudaStream_t s);

@@ -531,7 +531,8 @@ int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host) {
     a.n_owners = 1;
     a.top_k = 1;
     a.slice_tokens = m->max_local;
-    a.ft_fastest = 1;  // the sequence tiles of one vocabulary block run side by side and share its rows in L2
+    // (the argmax kernel orders its items with the sequence tile fastest: the tiles of one vocabulary block run side
+    // by side and share its rows in L2)
     a.amax_val = m->amax_val;
     a.amax_at = m->amax_at;
     MK(launch_grouped_amax(a, m->sm_count, s));

@@ -2,8 +2,11 @@
 // (bf16 x bf16 -> fp32).  Tokens are the UMMA M side (128 per CTA, one TMEM lane each), experts the N side
 // (E rounded up to 16, at most 256), K is split over gridDim.y CTAs so that even T = 1024 keeps ~64 SMs
 // streaming; the splits are summed in a fixed order by the top-k kernel, so the scores are bit-identical
-// on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs; a role whose wait
-// gives up stops issuing work, and the kernel leaves the scores of its tile unwritten (the host sees the time-out).
+// on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs.  A CTA computes one tile:
+// when a wait gives up, every later wait of the CTA returns at once, the loops run out (their copies and MMAs touch only
+// this CTA's ring and accumulator; the single-thread loops do not branch on the result of a wait, which was measured
+// to slow the expert GEMMs by 8-15 %), the MMA thread waits for what it has issued, and the host sees the time-out; the
+// scores of that tile are then meaningless.
 #include "kernels.cuh"
 #include "tcgen05.cuh"
 
@@ -62,7 +65,7 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
       uint32_t phase = 0, armed = 0, last_par = 0;
       const uint32_t tx = kRouterATile + a.n_cols * kBlockK * 2;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x1100 | stage)) break;
+        mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1u, &ctrl->abort, a.status, 0x1100 | stage);
         const uint32_t bar = smem_u32(&ctrl->full[stage]);
         const uint32_t sa = tiles_base + stage * a.stage_bytes;
         armed |= 1u << stage;
@@ -88,7 +91,7 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
       uint32_t phase = 0;
       const uint32_t idesc = umma_idesc(a.n_cols);
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x1300 | stage)) break;
+        mbar_wait(smem_u32(&ctrl->full[stage]), phase, &ctrl->abort, a.status, 0x1300 | stage);
         tc_fence_after();
         const uint32_t sa = tiles_base + stage * a.stage_bytes;
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + kRouterATile);
@@ -113,11 +116,11 @@ __global__ void __launch_bounds__(kRouterThreads, 1) router_gemm_kernel(const __
   } else {
     const int q = warp & 3;
     const int b = row0 + q * 32 + lane;
-    const bool got = mbar_wait(smem_u32(&ctrl->tmem_full), 0, &ctrl->abort, a.status, 0x1400);
+    mbar_wait(smem_u32(&ctrl->tmem_full), 0, &ctrl->abort, a.status, 0x1400);
     tc_fence_after();
     float *dst = a.partials + ((size_t)blockIdx.y * a.T + b) * a.E;
     const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16);
-    for (int c0 = 0; got && c0 < a.n_cols; c0 += 16) {  // after an abort the accumulator is not read
+    for (int c0 = 0; c0 < a.n_cols; c0 += 16) {
       uint32_t r[16];
       tmem_ld16(tbase + c0, r);
       tmem_ld_wait();
