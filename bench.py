@@ -735,7 +735,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
-                    help="N > 1: format in which owners deliver the summed rows (rows travel to the owner in fp32)")
+                    help="N > 1: wire format. Dispatch form: the expert rows pushed to the token's owner (summed there in "
+                         "fp32). Replicated form: the sums the owners deliver (rows travel to the owner in fp32)")
     ap.add_argument("--workload", choices=["moe_layer", "decode20b", "decode120b"], default="moe_layer",
                     help="moe_layer: the MoE block (headline, with the other workloads as extra keys); decode20b / "
                          "decode120b: only the whole-model greedy decode")

@@ -49,6 +49,7 @@ struct gptoss_ctx {
   RowDispatch rows_all{};             // ... or to the x_packed of the expert's owner (filled when peers are attached)
   TileBalance balance{};              // how expert_scan_kernel cuts the experts' rows into token blocks
   bool pushed_bf16 = false;           // the rows of the last push travelled as bf16 (token-sliced forms on the bf16 wire)
+  bool group_broken = false;          // a wait on a peer gave up: the ranks' step counters no longer match
   RouteShare share_self{};            // where routing rows go: this rank alone ...
   RouteShare share{};                 // ... or every rank of the group (filled when peers are attached)
   int route_step = 0;                 // number of shared routings so far (flag D carries it)
@@ -313,6 +314,9 @@ int gptoss_ctx_status(gptoss_ctx *ctx) {
   CK(cudaMemcpy(st, ctx->status, sizeof st, cudaMemcpyDeviceToHost));
   if (st[0] != 0) {
     CK(cudaMemset(ctx->status, 0, sizeof st));
+    // a wait on a peer flag (sites 0x21xx..0x26xx) that gave up leaves this rank's step counters ahead of the silent
+    // rank's: later exchanges of this group could never match again
+    if (st[0] == kDevErrTimeout && ctx->attached && st[1] >= 0x2100 && st[1] < 0x2700) ctx->group_broken = true;
     char buf[160];
     snprintf(buf, sizeof buf, "device-side bounded wait gave up: code %d site 0x%x block %d", st[0], st[1], st[2]);
     return ctx->fail(st[0] == kDevErrTimeout ? GPTOSS_ERR_TIMEOUT : GPTOSS_ERR_CUDA, buf);
@@ -464,7 +468,7 @@ static int route_rows(gptoss_ctx *ctx, int layer, int T, const void *rows, int f
 // Counting sort of the whole batch from the routing rows present in this rank's buffers + gather of the token rows
 // of this rank's experts.
 static int route_group(gptoss_ctx *ctx, int T, const void *t_full, cudaStream_t s) {
-  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, s));
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, FlagWait{}, s));
   CK(launch_scatter_gather(static_cast<const __nv_bfloat16 *>(t_full), 0, T, ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base,
                            ctx->rb.sorted, ctx->rows_self, s));
   return GPTOSS_OK;
@@ -553,6 +557,9 @@ int gptoss_moe_combine(gptoss_ctx *ctx, int T, float *x_dev, int residual, void 
 static int check_attached(gptoss_ctx *ctx) {
   if (!ctx) return GPTOSS_ERR_BAD_ARG;
   if (ctx->world < 2 || !ctx->attached) return ctx->fail(GPTOSS_ERR_STATE, "no peers attached");
+  if (ctx->group_broken)
+    return ctx->fail(GPTOSS_ERR_STATE, "an earlier wait on a peer timed out: the group's step counters no longer match, "
+                                       "destroy and re-create the contexts of all ranks");
   return GPTOSS_OK;
 }
 
@@ -698,8 +705,9 @@ int gptoss_moe_dispatch_rows(gptoss_ctx *ctx, int layer, int T, const void *t_sl
   if (n > 0 && !t_slice_dev_bf16) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null slice pointer");
   if (n > 0 && (reinterpret_cast<uintptr_t>(t_slice_dev_bf16) & 15)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "slice must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  CK(launch_wait_flags(ctx->peers, 0, ctx->route_step, ctx->status, s));  // every rank's routing rows have arrived
-  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, s));
+  // the prefix-sum kernel first waits until every rank's routing rows have arrived (flag D)
+  const FlagWait fw{ctx->peers.flags[ctx->rank] + 3 * kMaxRanks, ctx->world, ctx->route_step, ctx->peers.timeout_ns, ctx->status, 0x2600};
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, fw, s));
   RowDispatch rd = ctx->rows_all;
   rd.step = ctx->pending_gather = ++ctx->gather_step;
   // a rank without tokens still places the pair ids and raises its flag
@@ -979,7 +987,7 @@ int gptoss_moe_build_offsets(gptoss_ctx *ctx, int T, const int *topk_i_dev, int 
   rb.sorted = sorted_pair_ids_dev;
   rb.tb_prefix = nullptr;  // the token-block prefix of the context's own batch stays as it is
   CK(launch_pair_hist(topk_i_dev, T, ctx->d, rb.blk_hist, s));
-  CK(launch_expert_scan(rb, T, ctx->d, ctx->balance, s));
+  CK(launch_expert_scan(rb, T, ctx->d, ctx->balance, FlagWait{}, s));
   CK(launch_scatter_gather(nullptr, 0, 0, topk_i_dev, T, ctx->d, rb.blk_base, rb.sorted, RowDispatch{}, s));
   return GPTOSS_OK;
 }

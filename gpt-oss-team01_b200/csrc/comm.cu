@@ -23,31 +23,6 @@ namespace gptoss {
 
 namespace {
 
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Threads 0..world-1 of the block each wait until flags[r] >= step; then the block synchronises.
-__device__ __forceinline__ void wait_all_ranks(const int *flags, int world, int step, unsigned long long limit_ns,
-                                               int *status, int site) {
-  if ((int)threadIdx.x < world) {
-    const unsigned long long t0 = global_ns();
-    while (ld_acquire_sys(flags + threadIdx.x) < step) {
-      if (*reinterpret_cast<volatile int *>(status) != 0) break;  // some wait already gave up
-      if (global_ns() - t0 > limit_ns) {
-        if (atomicCAS(status, 0, kDevErrTimeout) == 0) {
-          status[1] = site;
-          status[2] = (int)threadIdx.x;
-        }
-        break;
-      }
-      __nanosleep(200);
-    }
-  }
-  __syncthreads();
-}
-
 // The last block of the grid to get here raises flag `which` (0 = A, 1 = B, 2 = C) of this rank on every rank.  The
 // block's stores are ordered before its count by the barrier plus ONE thread's system-scope fence (the fence is
 // cumulative over what the barrier made visible to that thread); a fence by every thread would make each of them

@@ -102,4 +102,39 @@ __device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
   asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// ---- waits on flags that peers raise ---------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Threads 0..world-1 of the block each wait until flags[r] >= step; then the block synchronises.  The wait is bounded
+// by wall time; a wait that gives up records a time-out (with `site`) in the status words and returns.
+__device__ __forceinline__ void wait_all_ranks(const int *flags, int world, int step, unsigned long long limit_ns,
+                                               int *status, int site) {
+  if ((int)threadIdx.x < world) {
+    const unsigned long long t0 = global_ns();
+    while (ld_acquire_sys(flags + threadIdx.x) < step) {
+      if (*reinterpret_cast<volatile int *>(status) != 0) break;  // some wait already gave up
+      if (global_ns() - t0 > limit_ns) {
+        if (atomicCAS(status, 0, kDevErrTimeout) == 0) {
+          status[1] = site;
+          status[2] = (int)threadIdx.x;
+        }
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+}
+// A wait on one kind of flag of every rank, to be done at the start of a kernel (step == 0: nothing to wait for).
+struct FlagWait {
+  const int *flags;  // this rank's copy of the flags of that kind, one per rank
+  int world, step;
+  unsigned long long timeout_ns;
+  int *status;
+  int site;
+};
+
 }  // namespace gptoss

@@ -50,7 +50,9 @@ cudaError_t launch_router_topk(const float *partials, int n_splits, const float 
 cudaError_t launch_topk_softmax(const float *scores, int T, int E, int k, float *topk_w, int *topk_i,
                                 cudaStream_t s);
 cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_hist, cudaStream_t s);
-cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, const TileBalance &tb, cudaStream_t s);
+// fw.step > 0: the kernel first waits for that flag of every rank (dispatch form: the routing rows of all ranks)
+cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, const TileBalance &tb, const FlagWait &fw,
+                               cudaStream_t s);
 // t: rows of tokens [t_first, t_first + t_count) (null: pair ids only)
 cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, int t_first, int t_count, const int *topk_i, int T, const Dims &d,
                                   const int *blk_base, int *sorted, const RowDispatch &rd, cudaStream_t s);

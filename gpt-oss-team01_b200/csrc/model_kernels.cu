@@ -394,17 +394,31 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
 }
 
 // Second stage of the fused classifier argmax: per sequence the first maximum over the per-vocabulary-block partials
-// (blocks ascend in vocabulary id, so a strict '>' keeps the first).  A sequence without any comparable logit gets 0.
-__global__ void __launch_bounds__(256) argmax_partials_kernel(const float *__restrict__ val, const int *__restrict__ at,
-                                                              int n_blocks, int B, int *__restrict__ next) {
+// (blocks ascend in vocabulary id, so among equal values the one from the lower block — the lower id — wins).  A
+// block of 32 warps serves 32 sequences: lane = sequence (coalesced reads of val/at [block][sequence]), the warps share
+// out the vocabulary blocks and merge through shared memory.  A sequence without any comparable logit gets 0.
+__global__ void __launch_bounds__(1024) argmax_partials_kernel(const float *__restrict__ val, const int *__restrict__ at,
+                                                               int n_blocks, int B, int *__restrict__ next) {
+  __shared__ float best_s[32][33];
+  __shared__ int idx_s[32][33];
   pdl_wait();
-  const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b < B) {
-    float best = -FLT_MAX;
-    int idx = 0x7fffffff;
-    for (int i = 0; i < n_blocks; ++i) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x * 32 + lane;
+  float best = -FLT_MAX;
+  int idx = 0x7fffffff;
+  if (b < B)
+    for (int i = warp; i < n_blocks; i += 32) {  // ascending blocks per warp: strict '>' keeps the first maximum
       const float v = val[(size_t)i * B + b];
       if (v > best) best = v, idx = at[(size_t)i * B + b];
+    }
+  best_s[warp][lane] = best;
+  idx_s[warp][lane] = idx;
+  __syncthreads();
+  if (warp == 0 && b < B) {
+    for (int w = 1; w < 32; ++w) {
+      const float v = best_s[w][lane];
+      const int j = idx_s[w][lane];
+      if (v > best || (v == best && j < idx)) best = v, idx = j;
     }
     next[b] = idx == 0x7fffffff ? 0 : idx;
   }
@@ -463,7 +477,7 @@ cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStre
   return launch_chain(argmax_kernel, dim3(B), dim3(1024), 0, s, logits, V, next);
 }
 cudaError_t launch_argmax_partials(const float *val, const int *at, int n_blocks, int B, int *next, cudaStream_t s) {
-  return launch_chain(argmax_partials_kernel, dim3((B + 255) / 256), dim3(256), 0, s, val, at, n_blocks, B, next);
+  return launch_chain(argmax_partials_kernel, dim3((B + 31) / 32), dim3(1024), 0, s, val, at, n_blocks, B, next);
 }
 cudaError_t launch_iota_ones(int *iota, float *ones, int n, cudaStream_t s) {
   iota_ones_kernel<<<(n + 255) / 256, 256, 0, s>>>(iota, ones, n);

@@ -215,13 +215,17 @@ __global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ 
 // tb.force_rows > 0 still forces another size, for such measurements.
 __device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + size - 1) / size; }
 
-__global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d, TileBalance tb) {
+// fw: in the dispatch form the block histograms come from every rank; the kernel first waits for their "routed" flags
+// (and only then lets its successor start: a kernel that became resident behind a pending flag wait would sit in its
+// own waits for as long as the slowest peer takes).
+__global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d, TileBalance tb, FlagWait fw) {
   __shared__ int seg_sum[1024];
   __shared__ int off_s[kMaxExperts + 1];
   const int E = d.E;
   const int nseg = 1024 / E;
   const int tid = threadIdx.x;
   pdl_wait();
+  if (fw.step > 0) wait_all_ranks(fw.flags, fw.world, fw.step, fw.timeout_ns, fw.status, fw.site);
   pdl_launch_dependents();
   const int seg = tid / E, e = tid % E;
   const bool active = seg < nseg;
@@ -443,8 +447,9 @@ cudaError_t launch_pair_hist(const int *topk_i, int T, const Dims &d, int *blk_h
   return cudaGetLastError();
 }
 
-cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, const TileBalance &tb, cudaStream_t s) {
-  return launch_chain(expert_scan_kernel, dim3(1), dim3(1024), 0, s, rb, route_blocks(T), d, tb);
+cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, const TileBalance &tb, const FlagWait &fw,
+                               cudaStream_t s) {
+  return launch_chain(expert_scan_kernel, dim3(1), dim3(1024), 0, s, rb, route_blocks(T), d, tb, fw);
 }
 
 cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, int t_first, int t_count, const int *topk_i, int T, const Dims &d,
@@ -528,7 +533,7 @@ extern "C" int gptoss_moe_build_offsets_noalloc(int T, int n_experts, int top_k,
   // every entry of the scratch that the scan and the scatter read is first written by this call, so
   // nothing has to start at zero
   if (launch_pair_hist(topk_i_dev, T, d, rb.blk_hist, s) != cudaSuccess ||
-      launch_expert_scan(rb, T, d, TileBalance{0}, s) != cudaSuccess ||
+      launch_expert_scan(rb, T, d, TileBalance{0}, FlagWait{}, s) != cudaSuccess ||
       launch_scatter_gather(nullptr, 0, 0, topk_i_dev, T, d, rb.blk_base, rb.sorted, RowDispatch{}, s) != cudaSuccess)
     return noalloc_fail(GPTOSS_ERR_CUDA, "kernel launch failed");
   return GPTOSS_OK;

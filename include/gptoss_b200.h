@@ -116,7 +116,10 @@ int gptoss_moe_forward_partial(gptoss_ctx *ctx, int layer, int T, const void *t_
  * from the down-GEMM epilogue straight into the buffer of the GPU that owns the token (peer stores over
  * NVLink), the owner sums its slice in slot order and stores it to every rank, and every rank adds it to
  * its residual stream.  All ranks must call gptoss_moe_forward the same number of times with the same T.
- * Device-side waits on peers are bounded (2 s) and end as GPTOSS_ERR_TIMEOUT in gptoss_ctx_status. */
+ * Device-side waits on peers are bounded (2 s) and end as GPTOSS_ERR_TIMEOUT in gptoss_ctx_status.  After such a
+ * time-out the context still serves calls that involve no peer (gptoss_moe_forward_partial, the stages, the taps), but
+ * the ranks' step counters no longer match: every later call that exchanges with peers returns GPTOSS_ERR_STATE until
+ * the contexts of all ranks have been destroyed and created again. */
 #define GPTOSS_IPC_HANDLE_BYTES 64
 int gptoss_comm_export(gptoss_ctx *ctx, void *handle_out);
 int gptoss_comm_attach(gptoss_ctx *ctx, const void *handles /* world x GPTOSS_IPC_HANDLE_BYTES */);

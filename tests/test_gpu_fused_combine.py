@@ -117,6 +117,9 @@ def test_wait_on_a_silent_peer_times_out_as_status():
     ranks[0].forward_partial(0, t_dev, part)
     ranks[0].status()
     assert torch.isfinite(part).all()
+    with pytest.raises(moe.GptossError) as e:   # but the group is out of step: exchanges are refused from now on
+        ranks[0].forward(0, t_dev, x)
+    assert e.value.code == capi.ERR_STATE
     for b in ranks:
         b.close()
 
@@ -218,14 +221,14 @@ def test_token_sliced_form_matches_single_context_bitwise(world, T):
         b.close()
 
 
-@pytest.mark.parametrize("world,T", [(2, 300), (4, 203), (8, 64), (8, 5)])
-def test_dispatch_form_matches_single_context_bitwise(world, T):
+@pytest.mark.parametrize("world,T,E", [(2, 300, 16), (4, 203, 16), (8, 64, 16), (8, 5, 16), (8, 300, 128)])
+def test_dispatch_form_matches_single_context_bitwise(world, T, E):
     """Dispatch form: every rank routes its own rows, shares the routing, and sends each row only to the ranks whose
     experts it selected (into its place in the receiver's grouped input); expert rows are pushed back to the token's
     owner.  fp32 wire: identical to one context bit for bit, routing and grouping included.  Stage by stage over
     emulated ranks; uneven and empty slices."""
     from gptoss_b200 import moe
-    H, I, E, k = 256, 192, 16, 4
+    H, I, k = 256, 192, 4     # E = 128 on 8 ranks: 16 experts per rank, the 120b sharding
     w = synth.MoELayerWeights(H, I, E, 91, sigma=0.05)
     single = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T)
     single.upload_layer(0, w)
