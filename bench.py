@@ -53,7 +53,7 @@ FLOP_PER_TOKEN = 2 * H * E + 2 * K_TOP * H * (2 * I) + 2 * K_TOP * I * H  # 199,
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM kernel at this workload,
 # from the ncu capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_MLP1_BYTES = 1_105_950_368  # dram read 1,102,148,000 + write 3,802,368 per launch (ncu capture of this workload, summarised under profiles/)
+NCU_TRAFFIC_MLP1_BYTES = 1_106_306_536  # dram read 1,101,761,000 + write 4,545,536 per launch (ncu capture of this workload, summarised under profiles/)
 
 
 def measured_peaks():

@@ -285,8 +285,12 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
   __shared__ int pos_s[kTokensPerRouteBlock * kMaxTopK];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k = d.k;
-  const int first = blockIdx.x * kTokensPerRouteBlock * k;
-  const int n = min(kTokensPerRouteBlock, T - blockIdx.x * kTokensPerRouteBlock) * k;
+  // The blocks that copy rows (the tokens [t_first, t_first + t_count)) take the lowest block indices, so that they
+  // are scheduled first on every rank: in the dispatch form their peer stores are what the other ranks wait for, and
+  // the placement-only blocks of the other tokens fill in behind them.  (t_first is a multiple of the 8 tokens per block.)
+  const int blk = (int)((blockIdx.x + (unsigned)(t_first / kTokensPerRouteBlock)) % gridDim.x);
+  const int first = blk * kTokensPerRouteBlock * k;
+  const int n = min(kTokensPerRouteBlock, T - blk * kTokensPerRouteBlock) * k;
   pdl_wait();
   pdl_launch_dependents();
   for (int q = threadIdx.x; q < kTokensPerRouteBlock * k; q += blockDim.x)
@@ -298,7 +302,7 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
     if (0 <= e && e < d.E) {
       int rank = 0;
       for (int r = 0; r < q; ++r) rank += (ids[r] == e);
-      pos = blk_base[(size_t)blockIdx.x * d.E + e] + rank;
+      pos = blk_base[(size_t)blk * d.E + e] + rank;
       sorted[pos] = first + q;
     }
     pos_s[q] = pos;
@@ -308,7 +312,7 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
   // keeps enough loads in flight; the row is read once and written to each slot that wants it
   const int wpt = blockDim.x >> 8;            // warps per token
   const int tok = warp / wpt, part = warp - tok * wpt;
-  const int b = blockIdx.x * kTokensPerRouteBlock + tok;
+  const int b = blk * kTokensPerRouteBlock + tok;
   if (t != nullptr && b < T && b >= t_first && b < t_first + t_count) {
     const int nchunk = d.H >> 3;
     const uint4 *src = reinterpret_cast<const uint4 *>(t + (size_t)(b - t_first) * d.H);
