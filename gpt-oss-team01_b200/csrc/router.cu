@@ -1,8 +1,8 @@
 // Router GEMM on the tensor cores: partial[s][b][e] = sum over the k-blocks of split s of t[b,:] . Wr[e,:]
 // (bf16 x bf16 -> fp32).  Tokens are the UMMA M side (128 per CTA, one TMEM lane each), experts the N side
-// (E rounded up to 16, at most 256), K is split over gridDim.y CTAs so that even T = 1024 keeps ~64 SMs
-// streaming; the splits are summed in a fixed order by the top-k kernel, so the scores are bit-identical
-// on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs.  A CTA computes one tile:
+// (E rounded up to 16, at most 256), K is split over gridDim.y CTAs (4 or 8, by the size of the whole batch) so that
+// even 1024 tokens keep 32 to 64 SMs streaming; the splits are summed in a fixed order by the top-k kernel, so the scores are
+// bit-identical on every launch and on every rank.  Same warp roles and bounded waits as the expert GEMMs.  A CTA computes one tile:
 // when a wait gives up, every later wait of the CTA returns at once, the loops run out (their copies and MMAs touch only
 // this CTA's ring and accumulator; the single-thread loops do not branch on the result of a wait, which was measured
 // to slow the expert GEMMs by 8-15 %), the MMA thread waits for what it has issued, and the host sees the time-out; the
@@ -159,12 +159,18 @@ cudaError_t launch_router_gemm(RouterArgs a, int max_splits, cudaStream_t s) {
   return launch_chain(router_gemm_kernel, dim3(n_tiles, splits), dim3(kRouterThreads), smem, s, a);
 }
 
+// Split-K factor of the router GEMM, from the size of the WHOLE batch (a rank that routes only its slice of a batch
+// passes the batch size, so that a token's partial sums are added in the same order whoever routes it: otherwise the
+// scores would differ in their last bits and a slice-routing rank could pick another expert than a rank routing
+// everything).  Up to 2048 tokens: 8 splits (1024 tokens: 64 CTAs with 6 k-blocks each).  Beyond: 4 — a CTA's fixed
+// cost (TMEM allocation, barrier set-up) then outweighs shorter k-loops for a full batch (8192 tokens: 91 us with 8
+// splits, 79 us with 1), while a 1024-token slice of such a batch still gets 32 CTAs with 12 k-blocks each instead
+// of 8 CTAs walking all 45.
 int router_splits_for(int T, int k_blocks, int max_splits) {
-  const int n_tiles = (T + 127) / 128;
-  int splits = 96 / n_tiles;
-  if (splits < 1) splits = 1;
+  int splits = T <= 2048 ? 8 : 4;
   if (splits > max_splits) splits = max_splits;
   if (splits > k_blocks) splits = k_blocks;
+  if (splits < 1) splits = 1;
   const int per = (k_blocks + splits - 1) / splits;
   return (k_blocks + per - 1) / per;
 }
