@@ -704,6 +704,99 @@ def decode_leg(args, workload, dist):
             "clocks": clocks.summary() if rank == 0 else None, "distinct_tokens_generated_rank0": n_distinct}
 
 
+def ragged_leg(args):
+    """Whole-model decode of requests of unequal length on one GPU, under two schedules: batch-at-a-time (the
+    reference's, getp-csrc/submit/getp_run_submit.cpp:33-96, plus the removal of finished sequences from the batch)
+    and continuous batching (a free slot is refilled at once; sequences at different positions share a step).
+    gpt-oss-20b architecture, random-init weights; 4 x batch requests of 16 random prompt ids, each generating a seeded
+    number of tokens drawn uniformly from [32, 256] (standing in for where a stop id would fall in real text).
+    Both schedules produce the same tokens; reported: generated tokens / wall time of each."""
+    from gptoss_b200 import binfmt, model
+    B = args.decode_batch or 1024
+    n_prompt = args.decode_prompt or 16
+    n_req = 4 * B
+    rng = np.random.default_rng(SEED)
+    gen_len = rng.integers(32, 257, size=n_req)
+    cfg = binfmt.config_20b(seq_len=1024)
+    if args.decode_layers:
+        cfg.n_layers = args.decode_layers
+    prompts = synth.uniform_ids(SEED, 12, n_req * n_prompt, cfg.vocab_size).reshape(n_req, n_prompt).astype(np.int32)
+    last_pos = n_prompt - 1 + gen_len  # a request has finished once it has taken this many steps
+    m = model.Model(cfg, device=0, max_batch=B, max_seq=n_prompt + 256)
+    out = {}
+    try:
+        m.fill_synthetic(SEED, SIGMA)
+        m.generate(prompts[:B, :2], 2)  # warm-up
+        for schedule in ("batches", "continuous"):
+            tokens_out = np.full((n_req, 256), -1, np.int32)
+            steps = 0
+            seq_steps = 0
+            with ClockSampler(0) as clocks:
+                t0 = time.perf_counter()
+                if schedule == "batches":
+                    for first in range(0, n_req, B):
+                        req = np.arange(first, first + B)
+                        cur = prompts[req, 0].copy()
+                        live = np.arange(B, dtype=np.int32)
+                        pos = 0
+                        while live.size:
+                            r = req[live]
+                            gen = pos + 1 >= n_prompt  # inside the prompts nobody needs the model's token
+                            nxt = m.step(cur, pos, need_next=gen) if live.size == B else m.step_rows(cur[live], live, pos, need_next=gen)
+                            steps += 1
+                            seq_steps += live.size
+                            if gen:
+                                tokens_out[r, pos + 1 - n_prompt] = nxt
+                                cur[live] = nxt
+                            else:
+                                cur[live] = prompts[r, pos + 1]
+                            pos += 1
+                            live = live[last_pos[r] > pos]
+                else:
+                    slot_req = np.full(B, -1, np.int64)
+                    slot_pos = np.zeros(B, np.int32)
+                    cur = np.zeros(B, np.int32)
+                    next_req = 0
+                    while True:
+                        free = np.flatnonzero(slot_req < 0)
+                        take = min(free.size, n_req - next_req)
+                        if take:
+                            f = free[:take]
+                            slot_req[f] = np.arange(next_req, next_req + take)
+                            slot_pos[f] = 0
+                            cur[f] = prompts[slot_req[f], 0]
+                            next_req += take
+                        live = np.flatnonzero(slot_req >= 0).astype(np.int32)
+                        if not live.size:
+                            break
+                        r, p = slot_req[live], slot_pos[live]
+                        nxt = m.step_seqs(cur[live], live, p)
+                        steps += 1
+                        seq_steps += live.size
+                        gen = p + 1 >= n_prompt
+                        tokens_out[r[gen], p[gen] + 1 - n_prompt] = nxt[gen]
+                        cur[live] = np.where(gen, nxt, prompts[r, np.minimum(p + 1, n_prompt - 1)])
+                        slot_pos[live] = p + 1
+                        done = live[last_pos[r] <= p + 1]
+                        slot_req[done] = -1
+                dt = time.perf_counter() - t0
+            out[schedule] = {"tok_s": float(gen_len.sum() / dt), "wall_s": dt, "steps": steps,
+                             "mean_sequences_per_step": seq_steps / steps, "ms_per_step": 1e3 * dt / steps,
+                             "clocks": clocks.summary(), "tokens": tokens_out}
+    finally:
+        m.close()
+    same = bool(np.array_equal(out["batches"]["tokens"], out["continuous"]["tokens"]))
+    for v in out.values():
+        del v["tokens"]
+    return {"metric": "batched decode tok/s, gpt-oss-20b arch (whole model, greedy), requests of unequal length",
+            "value": out["continuous"]["tok_s"], "unit": "tok/s", "n_gpus": 1, "higher_is_better": True,
+            "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"gpt-oss-20b architecture, {cfg.n_layers} layers, {n_req} requests on {B} slots, {n_prompt} random "
+                                   "prompt ids each, generated length uniform in [32, 256] (seeded)", "seed": SEED},
+            "schedules": out, "speedup_continuous_over_batches": out["continuous"]["tok_s"] / out["batches"]["tok_s"],
+            "same_tokens_under_both_schedules": same}
+
+
 def run_decode(args):
     import torch
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -713,7 +806,7 @@ def run_decode(args):
         import torch.distributed as dist
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
-    line = decode_leg(args, args.workload, dist)
+    line = ragged_leg(args) if args.workload == "decode20b_ragged" else decode_leg(args, args.workload, dist)
     if rank == 0:
         print_line(line)
     if world > 1:
@@ -737,9 +830,10 @@ def main():
     ap.add_argument("--wire", choices=["f32", "bf16"], default="bf16",
                     help="N > 1: wire format. Dispatch form: the expert rows pushed to the token's owner (summed there in "
                          "fp32). Replicated form: the sums the owners deliver (rows travel to the owner in fp32)")
-    ap.add_argument("--workload", choices=["moe_layer", "decode20b", "decode120b"], default="moe_layer",
+    ap.add_argument("--workload", choices=["moe_layer", "decode20b", "decode120b", "decode20b_ragged"], default="moe_layer",
                     help="moe_layer: the MoE block (headline, with the other workloads as extra keys); decode20b / "
-                         "decode120b: only the whole-model greedy decode")
+                         "decode120b: only the whole-model greedy decode; decode20b_ragged: requests of unequal length "
+                         "on one GPU, batch-at-a-time against continuous batching")
     ap.add_argument("--decode-batch", type=int, default=0, help="0 = the config's batch (1024 / 2048)")
     ap.add_argument("--decode-prompt", type=int, default=0, help="0 = the config's prompt length (128 / 256)")
     ap.add_argument("--decode-gen", type=int, default=0, help="0 = 256")
@@ -760,7 +854,7 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload in ("decode20b", "decode120b"):
+    elif args.workload in ("decode20b", "decode120b", "decode20b_ragged"):
         run_decode(args)
     else:
         run_ours(args)

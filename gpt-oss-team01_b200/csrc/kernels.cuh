@@ -149,10 +149,21 @@ cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, 
                                     cudaStream_t s);
 cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
                                   int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
-                                  const int *cache_rows, cudaStream_t s);
+                                  const int *cache_rows, const int *pos_rows, cudaStream_t s);
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
                              int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, const int *cache_rows,
-                             cudaStream_t s);
+                             const int *pos_rows, int window, cudaStream_t s);
+// Warps that share one (sequence, kv head) problem of the attention kernel, by the number of cached positions it reads
+// minus one (`span` = pos - t_lo): the split fixes the order of the softmax accumulation, so it follows the context
+// length only.
+inline int attention_warps_per_problem(int span) {
+  const int n_chunks = span / 32 + 1;
+  return n_chunks <= 16 ? 1 : (n_chunks <= 64 ? 2 : 4);
+}
+// pos_rows (both launchers above): null, or the position of each of the B sequences (a batch whose sequences started at
+// different steps); `pos` is then ignored by the RoPE kernel, and the attention launcher takes the sequences of ONE
+// class of attention_warps_per_problem per call, with pos / t_lo those of its longest context and `window` the
+// sliding window of the layer (0 = none), from which the kernel derives each sequence's first position.
 // cache_rows (both launchers above): null, or for each of the B sequences of the step the row of the KV cache that holds
 // it (a batch from which finished sequences were dropped keeps the cache rows of the remaining ones)
 cudaError_t launch_argmax(const float *logits, int B, int V, int *next, cudaStream_t s);

@@ -54,6 +54,14 @@ struct gptoss_model {
   int *tokens_dev = nullptr, *next_dev = nullptr, *iota = nullptr, *dense_off = nullptr, *dense_tbp = nullptr, *status = nullptr;
   int *rows_dev = nullptr;              // cache row of each sequence of a compacted step
   const int *step_rows = nullptr;       // rows_dev during such a step, else null (sequence i lives in cache row i)
+  int *pos_dev = nullptr;               // position of each sequence of a step whose sequences started at different times
+  const int *step_pos_rows = nullptr;   // pos_dev during such a step, else null (every sequence at step_pos)
+  // such a step keeps its sequences ordered by position; [class_end[c-1], class_end[c]) are those with a position below
+  // kPosClassEnd[c], and class_pos[c] the largest position among them
+  int class_end[3] = {0, 0, 0}, class_pos[3] = {0, 0, 0};
+  std::vector<int> perm, sorted_in, sorted_out;  // host scratch of the ordering: [3][max_batch] and [max_batch]
+  std::vector<int> place;               // after such a step: where the caller's sequence i stands in that order
+  bool last_step_ordered = false;       // the last step was one (gptoss_model_read_logits translates its row)
   int cur_B = -1;
   cudaStream_t stream = nullptr;
   bool weights_ready = false;
@@ -268,6 +276,7 @@ int gptoss_model_create_ep(const gptoss_model_config *cfg, int device, int rank,
   A(dalloc(&m->next_dev, B));
   A(dalloc(&m->iota, B));
   A(dalloc(&m->rows_dev, B));
+  A(dalloc(&m->pos_dev, B));
   A(dalloc(&m->ones, B));
   A(dalloc(&m->dense_off, 2));
   A(dalloc(&m->dense_tbp, 6));
@@ -311,7 +320,7 @@ int gptoss_model_destroy(gptoss_model *m) {
   if (m->moe) gptoss_ctx_destroy(m->moe);
   void *ptrs[] = {m->emb, m->unemb, m->attn_norm, m->mlp_norm, m->final_norm, m->w_qkv, m->b_qkv, m->w_o, m->b_o, m->sinks,
                   m->cos_t, m->sin_t, m->k_cache, m->v_cache, m->x, m->t, m->qkv, m->q, m->att, m->proj, m->logits,
-                  m->tokens_dev, m->next_dev, m->iota, m->rows_dev, m->amax_val, m->amax_at, m->amax_sched, m->ones, m->dense_off, m->dense_tbp, m->status, m->staging};
+                  m->tokens_dev, m->next_dev, m->iota, m->rows_dev, m->pos_dev, m->amax_val, m->amax_at, m->amax_sched, m->ones, m->dense_off, m->dense_tbp, m->status, m->staging};
   for (void *p : ptrs) cudaFree(p);
   if (m->stream) cudaStreamDestroy(m->stream);
   delete m;
@@ -444,6 +453,8 @@ int gptoss_model_step_begin(gptoss_model *m, const int *tokens_host, int pos, in
   if (n > 0 && !tokens_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token pointer");
   m->step_B = B, m->step_pos = pos, m->step_first = first, m->step_n = n;
   m->step_rows = nullptr;
+  m->step_pos_rows = nullptr;
+  m->last_step_ordered = false;
   if (n == 0) return GPTOSS_OK;
   int rc = set_batch(m, n);
   if (rc) return rc;
@@ -466,10 +477,35 @@ int gptoss_model_layer_attention(gptoss_model *m, int layer) {
     MK(launch_residual_rmsnorm(m->x, nullptr, m->attn_norm + l * H, B, (int)H, m->t, s));
     if ((rc = dense(m, kDenseQkv, m->map_qkv[l], m->map_t, (int)H, (int)qkvd, m->b_qkv + l * qkvd, m->qkv))) return rc;
     __nv_bfloat16 *kc = m->k_cache + l * (size_t)m->max_local * S * kvd, *vc = m->v_cache + l * (size_t)m->max_local * S * kvd;
-    MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, m->step_rows, s));
+    MK(launch_qkv_rope_store(m->qkv, m->cos_t, m->sin_t, pos, B, nq, nkv, hd, (int)S, m->q, kc, vc, m->step_rows,
+                             m->step_pos_rows, s));
     const bool windowed = c.sliding_window > 0 && (l % 2 == 0);  // run.cpp:582
-    const int t_lo = windowed ? (pos - c.sliding_window + 1 > 0 ? pos - c.sliding_window + 1 : 0) : 0;
-    MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, m->step_rows, s));
+    const int window = windowed ? c.sliding_window : 0;
+    if (!m->step_pos_rows) {
+      const int t_lo = windowed && pos - window + 1 > 0 ? pos - window + 1 : 0;
+      MK(launch_attention(m->q, kc, vc, m->sinks + l * nq, pos, t_lo, B, nq, nkv, hd, (int)S, m->att, m->step_rows, nullptr, 0, s));
+    } else {
+      // sequences at their own positions, ordered by position: one launch per run of sequences whose contexts (the
+      // window applied) ask for the same number of warps per problem, so every sequence is summed in the order a
+      // lock-step batch at its position would use
+      int b0 = 0;
+      while (b0 < B) {
+        int cls = 0;
+        while (m->class_end[cls] <= b0) ++cls;
+        const auto span_of = [&](int p) { return windowed && p > window - 1 ? window - 1 : p; };
+        const int warps = attention_warps_per_problem(span_of(m->class_pos[cls]));
+        int b1 = m->class_end[cls], span = span_of(m->class_pos[cls]);
+        for (int nx = cls + 1; nx < 3; ++nx) {  // following classes that the window folds into the same split
+          if (m->class_end[nx] == b1) continue;
+          if (attention_warps_per_problem(span_of(m->class_pos[nx])) != warps) break;
+          b1 = m->class_end[nx];
+          span = span_of(m->class_pos[nx]);
+        }
+        MK(launch_attention(m->q + (size_t)b0 * qd, kc, vc, m->sinks + l * nq, span, 0, b1 - b0, nq, nkv, hd, (int)S,
+                            m->att + (size_t)b0 * qd, m->step_rows + b0, m->step_pos_rows + b0, window, s));
+        b0 = b1;
+      }
+    }
     if ((rc = dense(m, kDenseOut, m->map_o[l], m->map_att, (int)qd, (int)H, m->b_o + l * H, m->proj))) return rc;
   }
   if (m->world == 1) {
@@ -597,12 +633,68 @@ int gptoss_model_step_rows(gptoss_model *m, const int *tokens_host, const int *r
   return rc;
 }
 
+// The same step for sequences that did not start together (continuous batching: a sequence that finished hands its
+// cache row to a waiting request, which starts at position 0 while its batch mates carry on): sequence i holds cache row
+// rows_host[i] and is at position pos_host[i].  Only RoPE and attention look at positions; they take them per sequence.
+// Internally the sequences are ordered by position, so that attention runs each class of context lengths with the
+// warp split a lock-step batch of that length gets; a sequence's result does not depend on who shares the batch.
+int gptoss_model_step_seqs(gptoss_model *m, const int *tokens_host, const int *rows_host, const int *pos_host, int n,
+                           int *next_tokens_host) {
+  if (!m) return GPTOSS_ERR_BAD_ARG;
+  if (m->world != 1) return m->fail(GPTOSS_ERR_UNSUPPORTED, "per-sequence positions are for a single-GPU model (a group steps in lock-step)");
+  if (!tokens_host || !rows_host || !pos_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null token, row or position pointer");
+  if (n <= 0 || n > m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "batch out of range");
+  // class c: positions whose full-context attention uses 1, 2, 4 warps per problem
+  const auto class_of = [](int p) { const int w = attention_warps_per_problem(p); return w == 1 ? 0 : (w == 2 ? 1 : 2); };
+  int count[3] = {0, 0, 0}, max_pos = 0;
+  for (int i = 0; i < n; ++i) {
+    if (rows_host[i] < 0 || rows_host[i] >= m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "cache row out of range");
+    if (pos_host[i] < 0 || pos_host[i] >= m->S) return m->fail(GPTOSS_ERR_BAD_ARG, "position out of range");
+    ++count[class_of(pos_host[i])];
+    if (pos_host[i] > max_pos) max_pos = pos_host[i];
+  }
+  const size_t B = (size_t)m->max_batch;
+  m->perm.resize(B), m->sorted_in.resize(3 * B), m->sorted_out.resize(B);
+  int at[3] = {0, count[0], count[0] + count[1]};
+  m->class_end[0] = count[0], m->class_end[1] = count[0] + count[1], m->class_end[2] = n;
+  m->class_pos[0] = m->class_pos[1] = m->class_pos[2] = 0;
+  int *tok_s = m->sorted_in.data(), *row_s = tok_s + B, *pos_s = row_s + B;
+  for (int i = 0; i < n; ++i) {
+    const int c = class_of(pos_host[i]), j = at[c]++;
+    m->perm[j] = i;
+    tok_s[j] = tokens_host[i], row_s[j] = rows_host[i], pos_s[j] = pos_host[i];
+    if (pos_host[i] > m->class_pos[c]) m->class_pos[c] = pos_host[i];
+  }
+  int rc = gptoss_model_step_begin(m, tok_s, max_pos, n);
+  if (rc) return rc;
+  MK(cudaMemcpyAsync(m->rows_dev, row_s, n * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+  MK(cudaMemcpyAsync(m->pos_dev, pos_s, n * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+  m->step_rows = m->rows_dev;
+  m->step_pos_rows = m->pos_dev;
+  for (int l = 0; !rc && l < m->c.n_layers; ++l) {
+    if ((rc = gptoss_model_layer_attention(m, l))) break;
+    rc = gptoss_model_layer_moe_push(m, l);
+  }
+  if (!rc) rc = gptoss_model_step_end(m, next_tokens_host ? m->sorted_out.data() : nullptr);
+  m->step_B = 0;
+  m->step_rows = nullptr;
+  m->step_pos_rows = nullptr;
+  if (rc) return rc;
+  if (next_tokens_host)
+    for (int j = 0; j < n; ++j) next_tokens_host[m->perm[j]] = m->sorted_out[j];
+  m->place.assign(B, -1);
+  for (int j = 0; j < n; ++j) m->place[m->perm[j]] = j;
+  m->last_step_ordered = true;
+  return GPTOSS_OK;
+}
+
 // Logits of one sequence of the last step that produced tokens (debug/parity tap).  The step itself never stores
 // logits (the classifier's epilogue keeps only the argmax), so they are computed here for the one row asked for:
 // the classifier GEMM on that row of the final-norm output, which the step left in place.
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out) {
   if (!m || !host_out) return GPTOSS_ERR_BAD_ARG;
   if (row < 0 || row >= m->max_local) return m->fail(GPTOSS_ERR_BAD_ARG, "row out of range");
+  if (m->last_step_ordered && (row = m->place[row]) < 0) return m->fail(GPTOSS_ERR_BAD_ARG, "row was not part of the last step");
   MK(cudaSetDevice(m->device));
   const int H = m->c.hidden_dim, V = m->c.vocab_size;
   CUtensorMap map_row;

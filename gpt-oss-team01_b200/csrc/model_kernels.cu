@@ -60,10 +60,12 @@ __global__ void __launch_bounds__(256) qkv_rope_store_kernel(const float *__rest
                                                              int hd, int S, float *__restrict__ q_out,
                                                              __nv_bfloat16 *__restrict__ k_cache,
                                                              __nv_bfloat16 *__restrict__ v_cache,
-                                                             const int *__restrict__ cache_rows) {
+                                                             const int *__restrict__ cache_rows,
+                                                             const int *__restrict__ pos_rows) {
   pdl_wait();
   const int b = blockIdx.x;
   const int cb = cache_rows ? cache_rows[b] : b;  // cache row of sequence b (a compacted batch keeps its rows)
+  if (pos_rows) pos = pos_rows[b];                // sequences that joined the batch later are at their own positions
   const int half = hd >> 1, hp = half >> 1;  // hp: pairs of adjacent rotation indices per head (hd is 32 or 64)
   const int qdim = nq * hd, kvdim = nkv * hd;
   const float *row = qkv + (size_t)b * (qdim + 2 * kvdim);
@@ -136,7 +138,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
                                                         const float *__restrict__ sinks, int pos, int t_lo, int nq,
                                                         int nkv, int kvm, int S, int n_problems,
                                                         __nv_bfloat16 *__restrict__ out,
-                                                        const int *__restrict__ cache_rows) {
+                                                        const int *__restrict__ cache_rows,
+                                                        const int *__restrict__ pos_rows, int window) {
   constexpr int PS = 4 / G;    // warps (position groups) per problem
   constexpr int D4 = HD / 4;   // K dims per thread
   constexpr int KS = HD / 16;  // k-steps of the score MMA
@@ -151,6 +154,10 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
   const int b = active ? prob / nkv : 0, kvh = active ? prob % nkv : 0;
   pdl_wait();  // q and this position's K/V rows come from the kernel before
   const int cb = cache_rows ? cache_rows[b] : b;  // cache row of sequence b
+  if (pos_rows) {  // every sequence at its own position (and the window that ends there)
+    pos = pos_rows[b];
+    t_lo = window > 0 && pos - window + 1 > 0 ? pos - window + 1 : 0;
+  }
   uint32_t qh[KS][2], ql[KS][2];
 #pragma unroll
   for (int s = 0; s < KS; ++s) {
@@ -443,26 +450,27 @@ cudaError_t launch_residual_rmsnorm(float *x, const float *add, const float *w, 
 }
 cudaError_t launch_qkv_rope_store(const float *qkv, const float *cos_t, const float *sin_t, int pos, int B, int nq, int nkv,
                                   int hd, int S, float *q_out, __nv_bfloat16 *k_cache, __nv_bfloat16 *v_cache,
-                                  const int *cache_rows, cudaStream_t s) {
+                                  const int *cache_rows, const int *pos_rows, cudaStream_t s) {
   return launch_chain(qkv_rope_store_kernel, dim3(B), dim3(256), 0, s, qkv, cos_t, sin_t, pos, nq, nkv, hd, S, q_out, k_cache,
-                      v_cache, cache_rows);
+                      v_cache, cache_rows, pos_rows);
 }
 cudaError_t launch_attention(const float *q, const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache, const float *sinks,
                              int pos, int t_lo, int B, int nq, int nkv, int hd, int S, __nv_bfloat16 *out, const int *cache_rows,
-                             cudaStream_t s) {
+                             const int *pos_rows, int window, cudaStream_t s) {
   const int kv_mul = nq / nkv;
   if (kv_mul < 1 || kv_mul > 8 || kv_mul * nkv != nq) return cudaErrorInvalidValue;  // query rows of one MMA tile
-  const int n_chunks = (pos - t_lo) / 32 + 1, n_prob = B * nkv;
+  const int n_prob = B * nkv;
   // Warps per problem by the context length alone (1 up to 512 positions: a warp streams its problem's rows front
   // to back with the loads one chunk ahead, which beats sharing them out; 2 up to 2048; else 4): the split fixes the
   // order of the softmax accumulation, so it must not depend on the batch, or a sequence would get different
-  // low-order bits in a large batch, a small one, or a slice of one on another GPU.
-  const int g = n_chunks <= 16 ? 4 : (n_chunks <= 64 ? 2 : 1);
+  // low-order bits in a large batch, a small one, or a slice of one on another GPU.  With per-sequence positions the
+  // caller passes sequences of one length class per launch, and `pos` / `t_lo` are those of the longest context.
+  const int g = 4 / attention_warps_per_problem(pos - t_lo);
   const int grid = (n_prob + g - 1) / g;
 #define GPTOSS_ATT_CASE(HD, G)                                                                                             \
   if (hd == HD && g == G) {                                                                                                \
     return launch_chain(attention_kernel<HD, G>, dim3(grid), dim3(128), 0, s, q, k_cache, v_cache, sinks, pos, t_lo, nq, nkv,   \
-                        kv_mul, S, n_prob, out, cache_rows);                                                               \
+                        kv_mul, S, n_prob, out, cache_rows, pos_rows, window);                                             \
   }
   GPTOSS_ATT_CASE(64, 4)
   GPTOSS_ATT_CASE(64, 2)

@@ -23,6 +23,10 @@
 // survivors keep their KV-cache rows (gptoss_model_step_rows takes the row of each live sequence), nothing is copied,
 // and since a sequence's tokens do not depend on its batch mates the output is unchanged; GPTOSS_NO_COMPACT=1 switches
 // it off.  GPTOSS_STOP_IDS="id,id,..." names further token ids that end a sequence like 199999 / 200002 do.
+// By default a replica goes one step further and batches continuously: it holds GPTOSS_BATCH slots, and a slot whose
+// sequence has finished is handed to the next waiting request at once, which starts at position 0 while the other
+// slots carry on (gptoss_model_step_seqs takes a position per sequence); the replicas draw requests from one queue.
+// Each request's tokens are what the batch-at-a-time schedule produces.  GPTOSS_NO_CONTINUOUS=1 restores that schedule.
 #include "getp_eval.cpp"
 
 #include <pthread.h>
@@ -46,6 +50,7 @@ int g_batch = 1024;
 int g_max_seq = 0;
 bool g_group = false;  // GPTOSS_EP: the models are the ranks of one group
 bool g_compact = true;  // drop finished sequences from a replica's batch between steps
+bool g_continuous = true;  // refill a finished sequence's slot with the next request instead of draining the batch
 std::vector<int> g_stop_ids = {199999, 200002};  // run.cpp:939, getp_run_submit.cpp:249
 
 bool is_stop(int tok) { return std::find(g_stop_ids.begin(), g_stop_ids.end(), tok) != g_stop_ids.end(); }
@@ -78,6 +83,19 @@ struct GroupSync {
   }
 };
 
+std::vector<int> encode_prompt(Tokenizer *tokenizer, const Config &cfg, Requests *reqs, int idx) {
+  const char *text = get_str_req_ptr(reqs, idx);
+  std::vector<int> buf(strlen(text) + 3);
+  int count = 0;
+  encode(tokenizer, text, -1, -1, buf.data(), &count, cfg.initial_context_length);
+  if (count < 1) {
+    fprintf(stderr, "something is wrong, expected at least 1 prompt token\n");
+    exit(EXIT_FAILURE);
+  }
+  buf.resize(count);
+  return buf;
+}
+
 // One batch of requests [first, first + n) in lock-step.  Returns the token count the reference reports
 // (generated_len + 1 per request).  A single model decodes the whole batch; a rank of a group (sync != nullptr) its
 // slice of it, and keeps stepping, for the other ranks' sake, until no sequence of the batch is running anywhere.
@@ -92,17 +110,7 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
     n = s_n;
   }
   std::vector<std::vector<int>> prompt(n);
-  for (int i = 0; i < n; ++i) {
-    const char *text = get_str_req_ptr(reqs, first + i);
-    std::vector<int> buf(strlen(text) + 3);
-    int count = 0;
-    encode(tokenizer, text, -1, -1, buf.data(), &count, cfg.initial_context_length);
-    if (count < 1) {
-      fprintf(stderr, "something is wrong, expected at least 1 prompt token\n");
-      exit(EXIT_FAILURE);
-    }
-    prompt[i].assign(buf.begin(), buf.begin() + count);
-  }
+  for (int i = 0; i < n; ++i) prompt[i] = encode_prompt(tokenizer, cfg, reqs, first + i);
   std::vector<int> cur(n), next(n), pos_of(n, 0);
   std::vector<char> active(n, 1);
   int n_active = n;
@@ -154,6 +162,73 @@ long long run_batch(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg
   return count;
 }
 
+// Continuous batching on one replica: `g_batch` slots (slot s = KV-cache row s), requests drawn from the shared queue
+// `next_req` whenever a slot is free.  Per sequence the rules are those of run_batch: prompt tokens force-fed one per
+// step, generated tokens from index 0 of the request's output row, stop ids, at most max_seq_len - 1 steps, the row
+// terminated by -1 after generated_len + 1 ids.
+long long run_continuous(gptoss_model *model, Tokenizer *tokenizer, const Config &cfg, Requests *reqs, std::atomic<int> &next_req) {
+  struct Slot {
+    int req = -1;  // request index, -1 = free
+    std::vector<int> prompt;
+    int pos = 0, cur = 0;
+  };
+  const int max_seq_len = reqs->max_seq_len;
+  std::vector<Slot> slots(g_batch);
+  std::vector<int> tokens, rows, pos, next;
+  long long count = 0;
+  bool queue_empty = max_seq_len < 2;  // no step fits: nothing is taken from the queue (run_batch would write -1 only)
+  if (queue_empty) {
+    for (int r = next_req++; r < reqs->num_reqs; r = next_req++) {
+      get_tok_gen_ptr(reqs, r)[1] = -1;
+      ++count;
+    }
+    return count;
+  }
+  for (;;) {
+    tokens.clear(), rows.clear(), pos.clear();
+    bool need_next = false;
+    for (int s = 0; s < g_batch; ++s) {
+      Slot &sl = slots[s];
+      if (sl.req < 0 && !queue_empty) {
+        const int r = next_req++;
+        if (r >= reqs->num_reqs) {
+          queue_empty = true;
+        } else {
+          sl.req = r;
+          sl.prompt = encode_prompt(tokenizer, cfg, reqs, r);
+          sl.pos = 0;
+          sl.cur = sl.prompt[0];
+        }
+      }
+      if (sl.req < 0) continue;
+      tokens.push_back(sl.cur), rows.push_back(s), pos.push_back(sl.pos);
+      need_next = need_next || sl.pos >= (int)sl.prompt.size() - 1;
+    }
+    if (tokens.empty()) break;
+    next.resize(tokens.size());
+    if (gptoss_model_step_seqs(model, tokens.data(), rows.data(), pos.data(), (int)tokens.size(), need_next ? next.data() : nullptr))
+      die("decode step failed", model);
+    for (size_t j = 0; j < rows.size(); ++j) {
+      Slot &sl = slots[rows[j]];
+      const int n_prompt = (int)sl.prompt.size();
+      int tok;
+      if (sl.pos < n_prompt - 1)
+        tok = sl.prompt[sl.pos + 1];  // still inside the prompt: force-feed
+      else
+        get_tok_gen_ptr(reqs, sl.req)[sl.pos - (n_prompt - 1)] = tok = next[j];
+      sl.cur = tok;
+      ++sl.pos;
+      if (is_stop(tok) || sl.pos >= max_seq_len - 1) {
+        const int generated_len = std::max(0, sl.pos - n_prompt);
+        get_tok_gen_ptr(reqs, sl.req)[generated_len + 1] = -1;
+        count += generated_len + 1;
+        sl.req = -1;  // refilled at the top of the next step
+      }
+    }
+  }
+  return count;
+}
+
 }  // namespace
 
 void warm_up(Transformer *transformer, Tokenizer *tokenizer) {
@@ -163,6 +238,7 @@ void warm_up(Transformer *transformer, Tokenizer *tokenizer) {
   if (const char *g = getenv("GPTOSS_GPUS")) n_gpus = std::max(1, atoi(g));
   if (const char *e = getenv("GPTOSS_EP")) g_group = atoi(e) != 0 && n_gpus > 1;
   if (const char *e = getenv("GPTOSS_NO_COMPACT")) g_compact = atoi(e) == 0;
+  if (const char *e = getenv("GPTOSS_NO_CONTINUOUS")) g_continuous = atoi(e) == 0;
   if (const char *e = getenv("GPTOSS_STOP_IDS"))
     for (const char *p = e; *p;) {
       char *end = nullptr;
@@ -213,6 +289,13 @@ long long inference(Transformer *transformer, Tokenizer *tokenizer, Sampler *sam
           total += run_batch(g_models[r], tokenizer, cfg, requests, first, n, &sync, r);
         }
       });
+    for (auto &w : workers) w.join();
+    return total;
+  }
+  if (g_continuous) {  // every replica refills its slots from one queue of requests
+    std::atomic<int> next_req{0};
+    for (gptoss_model *model : g_models)
+      workers.emplace_back([&, model] { total += run_continuous(model, tokenizer, cfg, requests, next_req); });
     for (auto &w : workers) w.join();
     return total;
   }

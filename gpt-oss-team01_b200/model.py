@@ -110,6 +110,19 @@ class Model:
                                                     int(pos), tokens.size, nxt.ctypes.data_as(C.c_void_p) if need_next else None))
         return nxt
 
+    def step_seqs(self, tokens, rows, positions, need_next=True):
+        """A step of sequences that did not start together (continuous batching): sequence i takes ``tokens[i]`` at
+        position ``positions[i]`` and lives in KV-cache row ``rows[i]``."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        rows = np.ascontiguousarray(rows, dtype=np.int32)
+        positions = np.ascontiguousarray(positions, dtype=np.int32)
+        assert tokens.shape == rows.shape == positions.shape
+        nxt = np.empty_like(tokens) if need_next else None
+        self._check(self.lib.gptoss_model_step_seqs(self._m, tokens.ctypes.data_as(C.c_void_p), rows.ctypes.data_as(C.c_void_p),
+                                                    positions.ctypes.data_as(C.c_void_p), tokens.size,
+                                                    nxt.ctypes.data_as(C.c_void_p) if need_next else None))
+        return nxt
+
     @staticmethod
     def step_group(models, tokens, pos, need_next=True):
         """One step of a whole group driven from this thread: ``tokens`` int32 [B] for the whole batch; every phase

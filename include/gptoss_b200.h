@@ -343,6 +343,15 @@ int gptoss_model_step(gptoss_model *m, const int *tokens_host, int pos, int B, i
  * only (the ranks of a group keep their slices). */
 int gptoss_model_step_rows(gptoss_model *m, const int *tokens_host, const int *rows_host, int pos, int n,
                            int *next_tokens_host);
+/* The same step for sequences that did not start together — continuous batching, which the reference's scheduler
+ * lacks too (getp-csrc/submit/getp_run_submit.cpp:33-96 starts the next batch only when the current one has
+ * drained): a finished sequence hands its KV-cache row to a waiting request, which starts at position 0 while its batch
+ * mates carry on.  Sequence i holds cache row rows_host[i] (in [0, max_batch), distinct) and is at position
+ * pos_host[i] (in [0, max_seq)); only RoPE (run.cpp:545-563) and attention (run.cpp:565-607) depend on the position,
+ * and they take it per sequence.  A sequence's tokens are bit for bit those of a lock-step batch at its position,
+ * whoever shares the batch.  Single-GPU models only. */
+int gptoss_model_step_seqs(gptoss_model *m, const int *tokens_host, const int *rows_host, const int *pos_host, int n,
+                           int *next_tokens_host);
 /* The phases of gptoss_model_step, which runs begin, then per layer attention / moe_dispatch / moe_push / moe_combine,
  * then end.  In a group, B is the batch of the group and tokens_host / next_tokens_host hold this rank's sequences only.
  * Separate entry points so that one host thread can drive the ranks of a group in turn (each phase for every rank
@@ -361,7 +370,8 @@ int gptoss_model_layer_moe_combine(gptoss_model *m, int layer);
 int gptoss_model_step_end(gptoss_model *m, int *next_tokens_host);
 /* Logits (fp32 [vocab]) of one sequence of the last step that produced tokens; debug/parity tap (PRINT_LOGITS,
  * getp_run.cpp:236).  A step keeps no logits (the classifier's epilogue reduces them to the greedy token, as
- * layer_hip_batch.cpp:1465-1712 does for the reference): the row is computed when asked for. */
+ * layer_hip_batch.cpp:1465-1712 does for the reference): the row is computed when asked for.  `row` is the index of
+ * the sequence in the arrays of that step. */
 int gptoss_model_read_logits(gptoss_model *m, int row, float *host_out);
 
 /* Library build info: "gptoss_b200 <version> sm_100a". */

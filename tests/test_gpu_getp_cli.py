@@ -96,15 +96,52 @@ def test_getp_mode_drops_finished_sequences_without_changing_the_output(tmp_path
             if t > 255:
                 candidates.setdefault(t, set()).add(j)
     stop = next(t for t in sorted(candidates) if sum(t in row[:12] for row in plain) < len(plain))
-    a = run("compact.txt", GPTOSS_STOP_IDS=str(stop))
-    b = run("nocompact.txt", GPTOSS_STOP_IDS=str(stop), GPTOSS_NO_COMPACT="1")
+    a = run("compact.txt", GPTOSS_STOP_IDS=str(stop), GPTOSS_NO_CONTINUOUS="1")
+    b = run("nocompact.txt", GPTOSS_STOP_IDS=str(stop), GPTOSS_NO_CONTINUOUS="1", GPTOSS_NO_COMPACT="1")
     assert a == b
+    assert run("continuous.txt", GPTOSS_STOP_IDS=str(stop)) == a
     lengths = {len(r) for r in a}
     assert len(lengths) > 1                                  # some stopped early, some ran on
     for row, full in zip(a, plain):
         assert row == full[:len(row)]                        # a prefix of the unstopped run ...
         if len(row) < len(full):
             assert row[-1] == stop                           # ... that ends at the stop id
+
+
+@pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")
+def test_getp_mode_refills_free_slots_without_changing_the_output(tmp_path):
+    """Continuous batching: 11 requests on 3 slots, prompts of different lengths, some requests stopping early on an
+    extra stop id.  A slot that falls free is taken by the next request at once, so sequences at different positions
+    share every step; each request's row must equal the one the batch-at-a-time schedule writes."""
+    cfg = binfmt.config_7m()
+    ckpt, tok, inp = (tmp_path / n for n in ("m.bin", "tokenizer.bin", "in.txt"))
+    binfmt.write_synthetic(str(ckpt), cfg, 4242)
+    binfmt.write_synthetic_tokenizer(str(tok), cfg.vocab_size)
+    prompts = ["hello world", "a", "The quick brown fox jumps over the lazy dog", "B200", "mixture of experts", "peer memory",
+               "x y z", "q", "tensor memory accumulators", "zz", "one more request"]
+    inp.write_text(f"{len(prompts)}\n" + "\n".join(prompts) + "\n")
+    steps = 48
+
+    def run(name, **env):
+        out = tmp_path / name
+        r = subprocess.run([str(EXE), str(ckpt), "-z", str(tok), "-m", "getp", "-i", str(inp), "-o", str(out), "-n", str(steps)],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
+                           env={"GPTOSS_BATCH": "3", "GPTOSS_MAX_SEQ": str(steps), "PATH": "/usr/bin:/bin", **env})
+        assert r.returncode == 0, r.stdout[-2000:]
+        return [[int(x) for x in line.split()] for line in out.read_text().splitlines()], r.stdout
+
+    plain, _ = run("plain.txt", GPTOSS_NO_CONTINUOUS="1")
+    counts = {}
+    for row in plain:
+        for t in set(row[1:20]):
+            if t > 255:
+                counts[t] = counts.get(t, 0) + 1
+    stop = next(t for t in sorted(counts) if 1 <= counts[t] < len(plain))
+    want, _ = run("batches.txt", GPTOSS_STOP_IDS=str(stop), GPTOSS_NO_CONTINUOUS="1")
+    got, log_c = run("continuous.txt", GPTOSS_STOP_IDS=str(stop))
+    assert got == want
+    assert len({len(r) for r in got}) > 1  # some stopped early
+    assert "achieved throughput TPS" in log_c
 
 
 @pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")

@@ -160,6 +160,58 @@ def test_compacted_batch_continues_the_survivors_bit_for_bit(checkpoint):
     comp.close()
 
 
+def test_sequences_at_their_own_positions_match_the_lock_step_batch():
+    """Continuous batching (gptoss_model_step_seqs): sequences join the batch at different steps, each at its own
+    position and in its own KV-cache row, rows are reused by later sequences, and the positions of one step span all
+    three context-length classes of the attention kernel (below 512, below 2048, beyond).  Every token, and the logits
+    at two probe steps, must equal bit for bit what the same sequence gets in a batch that runs in lock-step."""
+    from gptoss_b200 import model
+    P, S, B = 2120, 2176, 6
+    cfg = binfmt.config_7m(seq_len=S)
+    ids = synth.uniform_ids(91, 3, P * B, cfg.vocab_size).reshape(P, B).astype(np.int32)
+    # (first step, sequence = column of ids, positions it runs for, cache row)
+    jobs = [(0, 0, P, 5), (0, 1, 50, 0), (50, 2, P, 0), (40, 3, P, 2), (600, 4, 1500, 1), (1700, 5, 700, 3),
+            (2100, 1, 300, 4), (2110, 4, 60, 1)]
+    probes = (650, 2115)  # steps at which the logits of every live sequence are compared
+    wanted_logits = {}
+    for s in probes:
+        for first, seq, n, _ in jobs:
+            if first <= s < first + n:
+                wanted_logits[(s - first, seq)] = None
+    full = model.Model(cfg, max_batch=B, max_seq=S)
+    full.fill_synthetic(2025)
+    want = np.empty((P, B), np.int32)
+    for pos in range(P):
+        want[pos] = full.step(ids[pos], pos)
+        for (p, seq) in wanted_logits:
+            if p == pos:
+                wanted_logits[(p, seq)] = full.logits(seq).copy()
+    full.close()
+
+    cont = model.Model(cfg, max_batch=B, max_seq=S)
+    cont.fill_synthetic(2025)
+    last = max(first + n for first, _, n, _ in jobs)
+    classes_seen = set()
+    for s in range(last):
+        live = [(s - first, seq, row) for first, seq, n, row in jobs if first <= s < first + n]
+        if not live:
+            continue
+        pos = np.array([p for p, _, _ in live], np.int32)
+        seqs = np.array([q for _, q, _ in live])
+        rows = np.array([r for _, _, r in live], np.int32)
+        assert len(set(rows.tolist())) == len(rows)
+        got = cont.step_seqs(ids[pos, seqs], rows, pos)
+        assert np.array_equal(got, want[pos, seqs]), (s, pos.tolist())
+        classes_seen.add(tuple(sorted({0 if p < 512 else (1 if p < 2048 else 2) for p in pos.tolist()})))
+        if s in probes:
+            for j, (p, q, _) in enumerate(live):
+                assert np.array_equal(cont.logits(j), wanted_logits[(p, q)]), (s, p, q)
+    assert (0, 1, 2) in classes_seen  # one step held sequences of all three classes
+    with pytest.raises(Exception):
+        cont.step_seqs(ids[0, :2], np.array([0, 1], np.int32), np.array([0, S], np.int32))  # position beyond the cache
+    cont.close()
+
+
 def test_step_rejects_bad_arguments(checkpoint):
     from gptoss_b200 import capi, model, moe
     cfg = binfmt.config_7m()
