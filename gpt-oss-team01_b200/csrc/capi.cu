@@ -157,7 +157,7 @@ GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
   a.map_w = mlp1 ? w.map_w1 : w.map_w2;
   a.map_act = mlp1 ? ctx->map_x : ctx->map_h;
   a.offsets = ctx->rb.offsets;
-  a.tb_prefix = ctx->rb.tb_prefix;
+  a.tb_prefix = mlp1 ? ctx->rb.tb_prefix : ctx->rb.tb_prefix2;
   a.e_begin = ctx->d.e_begin;
   a.n_local = ctx->n_local;
   a.n_feat = mlp1 ? ctx->d.I : ctx->d.H;
@@ -217,6 +217,10 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->layers.resize(dims->n_layers);
   ctx->peers.timeout_ns = 2000000000ull;
   if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
+  // token blocks of the expert GEMMs: sized per call and per GEMM to fill the rounds of the persistent CTAs
+  ctx->balance.ctas = ctx->sm_count;
+  ctx->balance.nft1 = (dims->intermediate + kTileF - 1) / kTileF;
+  ctx->balance.nft2 = dims->hidden <= kTileF ? 1 : (dims->hidden + 2 * kTileF - 1) / (2 * kTileF);
   if (const char *e = getenv("GPTOSS_TOKEN_BLOCK")) ctx->balance.force_rows = atoi(e);  // measurement aid: fixed token-block size
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
@@ -230,6 +234,7 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->rb.offsets, E + 1));
   A(dev_alloc(&ctx->rb.sorted, P));
   A(dev_alloc(&ctx->rb.tb_prefix, E + 1));
+  A(dev_alloc(&ctx->rb.tb_prefix2, E + 1));
   A(dev_alloc(&ctx->gate_up, P * I));
   ctx->sym_delta_off = 1024;
   ctx->sym_y_off = ctx->sym_delta_off + ((T * H * sizeof(float) + 1023) & ~(size_t)1023);
@@ -285,6 +290,7 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->rb.offsets);
   cudaFree(ctx->rb.sorted);
   cudaFree(ctx->rb.tb_prefix);
+  cudaFree(ctx->rb.tb_prefix2);
   cudaFree(ctx->gate_up);
   for (int r = 0; r < kMaxRanks; ++r)
     if (ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);

@@ -35,12 +35,15 @@ struct RouteBuffers {
   int *offsets;         // [E+1]
   int *sorted;          // [T*k]
   int *tb_prefix;       // [E_local+1]   cumulative count of token blocks (at most kMaxTileTokens rows each) of the local
-                        //               experts; null = not wanted (grouping only)
+                        //               experts, as the gate/up GEMM cuts them; null = not wanted (grouping only)
+  int *tb_prefix2;      // [E_local+1]   the same for the down GEMM (its own block size)
 };
 
 // How the prefix-sum kernel cuts the experts' rows into token blocks (see expert_scan_kernel).
 struct TileBalance {
-  int force_rows; // > 0: blocks of at most this many rows instead of kMaxTileTokens (measurement aid)
+  int force_rows;  // > 0: blocks of at most this many rows instead of a size chosen per GEMM (measurement aid)
+  int ctas;        // persistent CTAs of a GEMM launch; 0: blocks of at most kMaxTileTokens rows, no balancing
+  int nft1, nft2;  // work items per token block (feature tiles) of the gate/up and of the down GEMM
 };
 
 // Where the gathered token rows go.  n == 1: into this rank's own x_packed, rows of its experts only.  n > 1 (dispatch

@@ -4,6 +4,7 @@
 // Everything here is bandwidth/latency-bound integer and fp32 work: one warp per token, 16-byte
 // loads, warp shuffles, no global atomics, deterministic results (all ranks of an expert-parallel
 // group must derive bit-identical routing from the replicated activations).
+#include <climits>
 #include <cstdio>
 #include <mutex>
 
@@ -208,11 +209,22 @@ __global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ 
 }
 
 // ---- prefix sums: expert offsets, per-block bases, token-block prefix for the GEMM tile scheduler -----
-// Token blocks of the expert GEMMs: expert e is cut into ceil(rows_e / 256) blocks of equal size (a multiple of 16
-// rows), 256 being the widest MMA.  Smaller blocks were measured (forced sizes from 96 to 208 rows, T = 8192, 4 and 32
-// local experts) in the hope of filling the last round of the persistent CTAs: every one was slower, because a work
-// item's time is set by the round trip of its ring stages far more than by its rows (256 rows: 43 us, 128 rows: 31 us).
-// tb.force_rows > 0 still forces another size, for such measurements.
+// Token blocks of the expert GEMMs: expert e is cut into ceil(rows_e / size) blocks of equal size (a multiple of 16
+// rows), size <= 256, the widest MMA.  The persistent CTAs of a GEMM take the (block, feature tile) items round-robin,
+// so a launch lasts about `rounds` = ceil(items / CTAs) items.  An item's time follows the bytes it brings into shared
+// memory — its weight tiles (as many bytes as 256 token rows) plus its token rows: measured 27 / 32 / 37 us at 128 /
+// 176 / 256 rows on both GEMMs — so an item of b rows costs about (256 + b).  With few local experts the size decides
+// how full the last round is: 4 experts x 1024 rows are 192-240 items of the down GEMM at size 256 (two rounds, the
+// second half empty) and 288 at size 192 (two full rounds of 176-row items): 65 us instead of 72.  The kernel evaluates
+// rounds x (256 + largest block) for the sizes 256, 240, .., 128 on the row counts at hand, separately for the two
+// GEMMs (they differ in items per block), and keeps the cheapest (the larger size on a tie).  Beyond 8 rounds at size
+// 256 it keeps 256: there the CTAs drift apart, rounds mean little, and the total bytes decide, which fewer, larger
+// items minimise.  Measured against blocks of 256 rows with uniform routing, one GPU's share of 2048 / 4096 / 8192
+// tokens on 2 / 4 / 8 GPUs: the two GEMMs together -13 .. -18 % / -6 .. -12 % / -3 .. -7 %.
+// tb.force_rows > 0 forces one size for both GEMMs (measurements).
+constexpr int kBlockSizeCandidates = 9;  // 256 - 16 c
+constexpr int kItemFixedRows = 256;
+constexpr int kBalanceMaxRounds = 8;
 __device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + size - 1) / size; }
 
 // fw: in the dispatch form the block histograms come from every rank; the kernel first waits for their "routed" flags
@@ -261,13 +273,49 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
     }
   }
   // token-block prefix of the local experts for the GEMM tile schedulers
-  if (tid == 0 && rb.tb_prefix != nullptr) {
-    const int size = tb.force_rows > 0 ? min(kMaxTileTokens, max(16, tb.force_rows & ~15)) : kMaxTileTokens;
-    int n = 0;
-    rb.tb_prefix[0] = 0;
-    for (int x = d.e_begin; x < d.e_end; ++x) {
-      n += blocks_of(off_s[x + 1] - off_s[x], size);
-      rb.tb_prefix[x - d.e_begin + 1] = n;
+  if (rb.tb_prefix == nullptr) return;
+  __shared__ int cost_s[2][kBlockSizeCandidates];
+  __shared__ int rounds_s[2];  // rounds at the largest size
+  const int warp = tid >> 5, lane = tid & 31;
+  const bool choose = tb.force_rows <= 0 && tb.ctas > 0;
+  if (choose && warp < 2 * kBlockSizeCandidates) {  // one warp per (GEMM, candidate size)
+    const int g = warp / kBlockSizeCandidates, c = warp - g * kBlockSizeCandidates;
+    const int size = kMaxTileTokens - 16 * c;
+    int blocks = 0, largest = 0;
+    for (int x = d.e_begin + lane; x < d.e_end; x += 32) {
+      const int rows = off_s[x + 1] - off_s[x], nb = blocks_of(rows, size);
+      blocks += nb;
+      if (nb > 0) largest = max(largest, (blocks_of(rows, nb) + 15) & ~15);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      blocks += __shfl_xor_sync(0xffffffffu, blocks, o);
+      largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+    }
+    if (lane == 0) {
+      const long long items = (long long)blocks * (g == 0 ? tb.nft1 : tb.nft2);
+      const long long rounds = (items + tb.ctas - 1) / tb.ctas;
+      cost_s[g][c] = (int)min(rounds * (kItemFixedRows + largest), (long long)INT_MAX);
+      if (c == 0) rounds_s[g] = (int)min(rounds, (long long)INT_MAX);
+    }
+  }
+  __syncthreads();
+  if (lane == 0 && warp < 2) {  // warp 0: gate/up GEMM, warp 1: down GEMM
+    int size = kMaxTileTokens;
+    if (tb.force_rows > 0) {
+      size = min(kMaxTileTokens, max(16, tb.force_rows & ~15));
+    } else if (choose && rounds_s[warp] <= kBalanceMaxRounds) {
+      int best = cost_s[warp][0];
+      for (int c = 1; c < kBlockSizeCandidates; ++c)
+        if (cost_s[warp][c] < best) best = cost_s[warp][c], size = kMaxTileTokens - 16 * c;
+    }
+    int *prefix = warp == 0 ? rb.tb_prefix : rb.tb_prefix2;
+    if (prefix != nullptr) {
+      int n = 0;
+      prefix[0] = 0;
+      for (int x = d.e_begin; x < d.e_end; ++x) {
+        n += blocks_of(off_s[x + 1] - off_s[x], size);
+        prefix[x - d.e_begin + 1] = n;
+      }
     }
   }
 }
