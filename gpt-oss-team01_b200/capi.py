@@ -14,9 +14,9 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 # GPTOSS_B200_LIB points the binding at another build of the same C ABI (e.g. a tuning variant)
 LIB_PATH = Path(os.environ.get("GPTOSS_B200_LIB", CSRC / "libgptoss_b200.so"))
-SOURCES = ["routing.cu", "router.cu", "grouped_gemm.cu", "comm.cu", "convert.cu", "capi.cu", "model_kernels.cu",
+SOURCES = ["routing.cu", "router.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu", "comm.cu", "convert.cu", "capi.cu", "model_kernels.cu",
            "model.cu"]
-HEADERS = ["common.cuh", "kernels.cuh", "tcgen05.cuh", "../../include/gptoss_b200.h"]
+HEADERS = ["common.cuh", "kernels.cuh", "tcgen05.cuh", "gemm_tile.cuh", "../../include/gptoss_b200.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--threads", "4"]
 

@@ -48,6 +48,8 @@ struct gptoss_ctx {
   RowDispatch rows_self{};            // token rows go to this rank's x_packed (its own experts only) ...
   RowDispatch rows_all{};             // ... or to the x_packed of the expert's owner (filled when peers are attached)
   TileBalance balance{};              // how expert_scan_kernel cuts the experts' rows into token blocks
+  bool pair_policy = false;           // expert GEMMs on pairs of CTAs (GPTOSS_PAIR=1)
+  bool pair_mode = false;             // the routed batch's GEMMs run on pairs (decided when the batch is grouped)
   bool pushed_bf16 = false;           // the rows of the last push travelled as bf16 (token-sliced forms on the bf16 wire)
   bool group_broken = false;          // a wait on a peer gave up: the ranks' step counters no longer match
   RouteShare share_self{};            // where routing rows go: this rank alone ...
@@ -151,6 +153,29 @@ int check_T(gptoss_ctx *ctx, int T) {
   return GPTOSS_OK;
 }
 
+// Fixes, for the batch about to be grouped, whether its expert GEMMs run on pairs of CTAs, and returns the parameters
+// with which expert_scan_kernel sizes the token blocks for that choice.  The pair kernels (tcgen05 cta_group::2) give
+// the same bits and, measured from 128 to 1024 rows per expert, the same time or a few per cent more than one CTA per
+// item (the GEMMs are bound by the tensor pipe under the board's power cap, not by what a CTA stages), so they run
+// only on request: GPTOSS_PAIR=1.
+TileBalance balance_for(gptoss_ctx *ctx) {
+  ctx->pair_mode = ctx->pair_policy && ctx->d.H > kTileF;  // the one-tile down GEMM has no pair form
+  TileBalance b = ctx->balance;
+  const int H = ctx->d.H, I = ctx->d.I;
+  if (ctx->pair_mode) {
+    b.ctas = ctx->sm_count / 2;
+    b.nft1 = (I + 2 * kTileF - 1) / (2 * kTileF);
+    b.nft2 = (H + 4 * kTileF - 1) / (4 * kTileF);
+    b.fixed_rows = 2 * kMaxTileTokens;  // a CTA stages two weight tiles (as many bytes as 256 token rows) and HALF the block's rows
+  } else {
+    b.ctas = ctx->sm_count;
+    b.nft1 = (I + kTileF - 1) / kTileF;
+    b.nft2 = H <= kTileF ? 1 : (H + 2 * kTileF - 1) / (2 * kTileF);
+    b.fixed_rows = kMaxTileTokens;
+  }
+  return b;
+}
+
 GemmArgs gemm_args(gptoss_ctx *ctx, const LayerWeights &w, bool mlp1) {
   GemmArgs a;
   memset(&a, 0, sizeof a);
@@ -217,11 +242,8 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->layers.resize(dims->n_layers);
   ctx->peers.timeout_ns = 2000000000ull;
   if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
-  // token blocks of the expert GEMMs: sized per call and per GEMM to fill the rounds of the persistent CTAs
-  ctx->balance.ctas = ctx->sm_count;
-  ctx->balance.nft1 = (dims->intermediate + kTileF - 1) / kTileF;
-  ctx->balance.nft2 = dims->hidden <= kTileF ? 1 : (dims->hidden + 2 * kTileF - 1) / (2 * kTileF);
   if (const char *e = getenv("GPTOSS_TOKEN_BLOCK")) ctx->balance.force_rows = atoi(e);  // measurement aid: fixed token-block size
+  if (const char *e = getenv("GPTOSS_PAIR")) ctx->pair_policy = atoi(e) != 0;           // expert GEMMs on pairs of CTAs
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
   const size_t P = T * k, nblk = (T + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock;
@@ -474,7 +496,7 @@ static int route_rows(gptoss_ctx *ctx, int layer, int T, const void *rows, int f
 // Counting sort of the whole batch from the routing rows present in this rank's buffers + gather of the token rows
 // of this rank's experts.
 static int route_group(gptoss_ctx *ctx, int T, const void *t_full, cudaStream_t s) {
-  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, FlagWait{}, s));
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, balance_for(ctx), FlagWait{}, s));
   CK(launch_scatter_gather(static_cast<const __nv_bfloat16 *>(t_full), 0, T, ctx->rb.topk_i, T, ctx->d, ctx->rb.blk_base,
                            ctx->rb.sorted, ctx->rows_self, s));
   return GPTOSS_OK;
@@ -533,7 +555,8 @@ int gptoss_moe_mlp1_swiglu(gptoss_ctx *ctx, int layer, void *stream) {
   if (rc) return rc;
   CK(cudaSetDevice(ctx->device));
   if (ctx->cur_T == 0) return GPTOSS_OK;
-  CK(launch_grouped_mlp1(gemm_args(ctx, ctx->layers[layer], true), ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  CK((ctx->pair_mode ? launch_grouped_mlp1_pair : launch_grouped_mlp1)(gemm_args(ctx, ctx->layers[layer], true), ctx->sm_count,
+                                                                       static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }
 
@@ -542,7 +565,8 @@ int gptoss_moe_mlp2(gptoss_ctx *ctx, int layer, void *stream) {
   if (rc) return rc;
   CK(cudaSetDevice(ctx->device));
   if (ctx->cur_T == 0) return GPTOSS_OK;
-  CK(launch_grouped_mlp2(gemm_args(ctx, ctx->layers[layer], false), ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  CK((ctx->pair_mode ? launch_grouped_mlp2_pair : launch_grouped_mlp2)(gemm_args(ctx, ctx->layers[layer], false), ctx->sm_count,
+                                                                       static_cast<cudaStream_t>(stream)));
   return GPTOSS_OK;
 }
 
@@ -590,7 +614,7 @@ static int push_rows(gptoss_ctx *ctx, int layer, bool bf16, void *stream) {
   }
   a.signal_step = step;
   a.signal_counter = ctx->comm_counter;
-  CK(launch_grouped_mlp2(a, ctx->sm_count, s));
+  CK((ctx->pair_mode ? launch_grouped_mlp2_pair : launch_grouped_mlp2)(a, ctx->sm_count, s));
   return GPTOSS_OK;
 }
 
@@ -713,7 +737,7 @@ int gptoss_moe_dispatch_rows(gptoss_ctx *ctx, int layer, int T, const void *t_sl
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // the prefix-sum kernel first waits until every rank's routing rows have arrived (flag D)
   const FlagWait fw{ctx->peers.flags[ctx->rank] + 3 * kMaxRanks, ctx->world, ctx->route_step, ctx->peers.timeout_ns, ctx->status, 0x2600};
-  CK(launch_expert_scan(ctx->rb, T, ctx->d, ctx->balance, fw, s));
+  CK(launch_expert_scan(ctx->rb, T, ctx->d, balance_for(ctx), fw, s));
   RowDispatch rd = ctx->rows_all;
   rd.step = ctx->pending_gather = ++ctx->gather_step;
   // a rank without tokens still places the pair ids and raises its flag

@@ -42,8 +42,10 @@ struct RouteBuffers {
 // How the prefix-sum kernel cuts the experts' rows into token blocks (see expert_scan_kernel).
 struct TileBalance {
   int force_rows;  // > 0: blocks of at most this many rows instead of a size chosen per GEMM (measurement aid)
-  int ctas;        // persistent CTAs of a GEMM launch; 0: blocks of at most kMaxTileTokens rows, no balancing
-  int nft1, nft2;  // work items per token block (feature tiles) of the gate/up and of the down GEMM
+  int ctas;        // CTAs (or pairs of CTAs) that share out the items of a GEMM launch; 0: blocks of at most
+                   // kMaxTileTokens rows, no balancing
+  int nft1, nft2;  // work items per token block (feature tiles, or pairs of them) of the gate/up and of the down GEMM
+  int fixed_rows;  // an item of b rows costs (fixed_rows + b): the weight tiles it stages, in units of staged token rows
 };
 
 // Where the gathered token rows go.  n == 1: into this rank's own x_packed, rows of its experts only.  n > 1 (dispatch

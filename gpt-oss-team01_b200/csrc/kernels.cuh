@@ -137,6 +137,9 @@ struct GemmArgs {
 };
 cudaError_t launch_grouped_mlp1(const GemmArgs &a, int sm_count, cudaStream_t s);
 cudaError_t launch_grouped_mlp2(const GemmArgs &a, int sm_count, cudaStream_t s);
+// grouped_gemm_pair.cu — the same two GEMMs with a pair of CTAs (tcgen05 cta_group::2) per work item
+cudaError_t launch_grouped_mlp1_pair(const GemmArgs &a, int sm_count, cudaStream_t s);
+cudaError_t launch_grouped_mlp2_pair(const GemmArgs &a, int sm_count, cudaStream_t s);
 cudaError_t launch_grouped_amax(const GemmArgs &a, int sm_count, cudaStream_t s);
 // Encodes the two tensor maps (driver entry point resolved at run time; no link-time libcuda).
 // weights: base of [slabs][rows][K] bf16;  activations: base of [rows][K] bf16.

@@ -223,7 +223,6 @@ __global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ 
 // tokens on 2 / 4 / 8 GPUs: the two GEMMs together -13 .. -18 % / -6 .. -12 % / -3 .. -7 %.
 // tb.force_rows > 0 forces one size for both GEMMs (measurements).
 constexpr int kBlockSizeCandidates = 9;  // 256 - 16 c
-constexpr int kItemFixedRows = 256;
 constexpr int kBalanceMaxRounds = 8;
 __device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + size - 1) / size; }
 
@@ -294,7 +293,7 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
     if (lane == 0) {
       const long long items = (long long)blocks * (g == 0 ? tb.nft1 : tb.nft2);
       const long long rounds = (items + tb.ctas - 1) / tb.ctas;
-      cost_s[g][c] = (int)min(rounds * (kItemFixedRows + largest), (long long)INT_MAX);
+      cost_s[g][c] = (int)min(rounds * (tb.fixed_rows + largest), (long long)INT_MAX);
       if (c == 0) rounds_s[g] = (int)min(rounds, (long long)INT_MAX);
     }
   }

@@ -100,6 +100,36 @@ def test_token_block_size_does_not_change_the_result(oracle, rows, monkeypatch):
     forced.close()
 
 
+@pytest.mark.parametrize("shape", [(256, 128, 4, 4, 700), (384, 320, 8, 2, 1500), (2880, 2880, 4, 4, 1024), (320, 192, 16, 4, 37)])
+def test_pair_of_ctas_per_item_gives_the_same_bits(oracle, shape, monkeypatch):
+    """The expert GEMMs on pairs of CTAs (tcgen05 cta_group::2: each CTA of a cluster of two stages its own weight
+    tiles and half of the token rows) against one CTA per item: every dot product runs over K in the same order, so
+    the intermediate rows and the block's output must be identical, ragged feature tiles and token blocks included."""
+    H, I, E, k, T = shape
+    small = H < 1024  # the large shape fills its weights on the device and is compared between the two kernels only
+    w = synth.MoELayerWeights(H, I, E, 77 + H, sigma=0.05) if small else None
+    t = synth.activations(77 + H, T, H)
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("GPTOSS_PAIR", mode)  # read when a context is created
+        blk = make_block(H, I, E, k, T)
+        if small:
+            blk.upload_layer(0, w)
+        else:
+            blk.fill_layer_synthetic(0, 77 + H, 0.02)
+        if mode == "1" and small:
+            run_and_compare(oracle, blk, w, t, T, k)
+        x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+        for _ in range(3):  # the rings and accumulators are reused across items and launches
+            x.zero_()
+            blk.forward(0, to_dev_bf16(t), x)
+        blk.status()
+        outs[mode] = (x.clone(), blk.tap("gate_up", T).copy())
+        blk.close()
+    assert np.array_equal(outs["0"][1], outs["1"][1])
+    assert torch.equal(outs["0"][0], outs["1"][0])
+
+
 def test_residual_is_added_in_place(oracle):
     H, I, E, k, T = 128, 128, 8, 2, 40
     w = synth.MoELayerWeights(H, I, E, 5, sigma=0.05)
