@@ -173,6 +173,10 @@ TileBalance balance_for(gptoss_ctx *ctx) {
     b.nft2 = H <= kTileF ? 1 : (H + 2 * kTileF - 1) / (2 * kTileF);
     b.fixed_rows = kMaxTileTokens;
   }
+  // The down GEMM of a group of GPUs keeps blocks of 256 rows (no items: every size costs the same, the largest wins):
+  // its epilogue stores the rows to their owners over NVLink, and more, smaller items were measured slower there on
+  // two real GPUs (96 us against 92.5) although faster without the push (86 against 97).
+  if (ctx->world > 1) b.nft2 = 0;
   return b;
 }
 

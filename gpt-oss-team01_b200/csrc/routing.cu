@@ -211,17 +211,13 @@ __global__ void __launch_bounds__(256) pair_hist_kernel(const int *__restrict__ 
 // ---- prefix sums: expert offsets, per-block bases, token-block prefix for the GEMM tile scheduler -----
 // Token blocks of the expert GEMMs: expert e is cut into ceil(rows_e / size) blocks of equal size (a multiple of 16
 // rows), size <= 256, the widest MMA.  The persistent CTAs of a GEMM take the (block, feature tile) items round-robin,
-// so a launch lasts about `rounds` = ceil(items / CTAs) items.  An item's time follows the bytes it brings into shared
-// memory — its weight tiles (as many bytes as 256 token rows) plus its token rows: measured 27 / 32 / 37 us at 128 /
-// 176 / 256 rows on both GEMMs — so an item of b rows costs about (256 + b).  With few local experts the size decides
-// how full the last round is: 4 experts x 1024 rows are 192-240 items of the down GEMM at size 256 (two rounds, the
-// second half empty) and 288 at size 192 (two full rounds of 176-row items): 65 us instead of 72.  The kernel evaluates
-// rounds x (256 + largest block) for the sizes 256, 240, .., 128 on the row counts at hand, separately for the two
-// GEMMs (they differ in items per block), and keeps the cheapest (the larger size on a tie).  Beyond 8 rounds at size
-// 256 it keeps 256: there the CTAs drift apart, rounds mean little, and the total bytes decide, which fewer, larger
-// items minimise.  Measured against blocks of 256 rows with uniform routing, one GPU's share of 2048 / 4096 / 8192
-// tokens on 2 / 4 / 8 GPUs: the two GEMMs together -13 .. -18 % / -6 .. -12 % / -3 .. -7 %.
-// tb.force_rows > 0 forces one size for both GEMMs (measurements).
+// so a launch lasts about `rounds` = ceil(items / CTAs) items, and an item of b rows takes about as long as
+// (tb.fixed_rows + b) rows' worth of work (measured 27 / 32 / 37 us at 128 / 176 / 256 rows on both GEMMs: fixed part
+// 256).  With few local experts the size decides how full the last round is.  The kernel evaluates
+// rounds x (fixed + largest block) for the sizes 256, 240, .., 128 on the row counts at hand, separately for the two
+// GEMMs (they differ in items per block; a GEMM given no items keeps 256), and keeps the cheapest (the larger size on
+// a tie).  Beyond 8 rounds at size 256 it keeps 256: there the CTAs drift apart, rounds mean little, and fewer, larger
+// items win.  tb.force_rows > 0 forces one size for both GEMMs (measurements).
 constexpr int kBlockSizeCandidates = 9;  // 256 - 16 c
 constexpr int kBalanceMaxRounds = 8;
 __device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + size - 1) / size; }

@@ -169,3 +169,27 @@ def test_getp_mode_group_of_gpus_writes_the_same_tokens(tmp_path):
         assert r.returncode == 0, r.stdout[-2000:]
         outs.append(out.read_text())
     assert outs[0] == outs[1] and len(outs[0].splitlines()) == len(prompts)
+
+
+@pytest.mark.skipif(not EXE.exists(), reason="run_b200 not built (needs the reference sources: make -C gpt-oss-team01_b200/host)")
+def test_getp_mode_replicas_draw_requests_from_one_queue(tmp_path):
+    """GPTOSS_GPUS=2 without GPTOSS_EP: two data-parallel replicas (the reference's 20B mode), each refilling its
+    slots from the same queue of requests; which replica serves a request must not show in its output row."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    cfg = binfmt.config_7m()
+    ckpt, tok, inp = (tmp_path / n for n in ("m.bin", "tokenizer.bin", "in.txt"))
+    binfmt.write_synthetic(str(ckpt), cfg, 4242)
+    binfmt.write_synthetic_tokenizer(str(tok), cfg.vocab_size)
+    prompts = [f"request number {i} " + "x" * (i % 5) for i in range(13)]
+    inp.write_text(f"{len(prompts)}\n" + "\n".join(prompts) + "\n")
+    steps = 36
+    outs = []
+    for env in ({"GPTOSS_GPUS": "1"}, {"GPTOSS_GPUS": "2"}, {"GPTOSS_GPUS": "2", "GPTOSS_NO_CONTINUOUS": "1"}):
+        out = tmp_path / f"out{len(outs)}.txt"
+        r = subprocess.run([str(EXE), str(ckpt), "-z", str(tok), "-m", "getp", "-i", str(inp), "-o", str(out), "-n", str(steps)],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
+                           env={"GPTOSS_BATCH": "3", "GPTOSS_MAX_SEQ": str(steps), "PATH": "/usr/bin:/bin", **env})
+        assert r.returncode == 0, r.stdout[-2000:]
+        outs.append(out.read_text())
+    assert outs[0] == outs[1] == outs[2] and len(outs[0].splitlines()) == len(prompts)
