@@ -60,6 +60,7 @@ struct gptoss_model {
   // kPosClassEnd[c], and class_pos[c] the largest position among them
   int class_end[3] = {0, 0, 0}, class_pos[3] = {0, 0, 0};
   std::vector<int> perm, sorted_in, sorted_out;  // host scratch of the ordering: [3][max_batch] and [max_batch]
+  std::vector<char> row_taken;          // host scratch: cache rows named by the step's sequences (they must be distinct)
   std::vector<int> place;               // after such a step: where the caller's sequence i stands in that order
   bool last_step_ordered = false;       // the last step was one (gptoss_model_read_logits translates its row)
   int cur_B = -1;
@@ -613,8 +614,11 @@ int gptoss_model_step_rows(gptoss_model *m, const int *tokens_host, const int *r
   if (m->world != 1) return m->fail(GPTOSS_ERR_UNSUPPORTED, "compacted steps are for a single-GPU model (a group keeps its slices)");
   if (!rows_host) return m->fail(GPTOSS_ERR_BAD_ARG, "null row map");
   if (n <= 0 || n > m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "batch out of range");
-  for (int i = 0; i < n; ++i)
+  m->row_taken.assign(m->max_batch, 0);
+  for (int i = 0; i < n; ++i) {
     if (rows_host[i] < 0 || rows_host[i] >= m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "cache row out of range");
+    if (m->row_taken[rows_host[i]]++) return m->fail(GPTOSS_ERR_BAD_ARG, "two sequences name the same cache row");
+  }
   int rc = gptoss_model_step_begin(m, tokens_host, pos, n);
   if (rc) return rc;
   MK(cudaMemcpyAsync(m->rows_dev, rows_host, n * sizeof(int), cudaMemcpyHostToDevice, m->stream));
@@ -647,8 +651,10 @@ int gptoss_model_step_seqs(gptoss_model *m, const int *tokens_host, const int *r
   // class c: positions whose full-context attention uses 1, 2, 4 warps per problem
   const auto class_of = [](int p) { const int w = attention_warps_per_problem(p); return w == 1 ? 0 : (w == 2 ? 1 : 2); };
   int count[3] = {0, 0, 0}, max_pos = 0;
+  m->row_taken.assign(m->max_batch, 0);
   for (int i = 0; i < n; ++i) {
     if (rows_host[i] < 0 || rows_host[i] >= m->max_batch) return m->fail(GPTOSS_ERR_BAD_ARG, "cache row out of range");
+    if (m->row_taken[rows_host[i]]++) return m->fail(GPTOSS_ERR_BAD_ARG, "two sequences name the same cache row");
     if (pos_host[i] < 0 || pos_host[i] >= m->S) return m->fail(GPTOSS_ERR_BAD_ARG, "position out of range");
     ++count[class_of(pos_host[i])];
     if (pos_host[i] > max_pos) max_pos = pos_host[i];

@@ -209,6 +209,8 @@ def test_sequences_at_their_own_positions_match_the_lock_step_batch():
     assert (0, 1, 2) in classes_seen  # one step held sequences of all three classes
     with pytest.raises(Exception):
         cont.step_seqs(ids[0, :2], np.array([0, 1], np.int32), np.array([0, S], np.int32))  # position beyond the cache
+    with pytest.raises(Exception):
+        cont.step_seqs(ids[0, :2], np.array([3, 3], np.int32), np.array([0, 5], np.int32))  # one cache row named twice
     cont.close()
 
 
