@@ -507,43 +507,65 @@ def run_ours(args):
         cs = clocks.summary()
         line["clocks"] = cs
 
-    # end to end through the host-buffer entry point (single GPU: the C ABI call a host program makes)
+    # End to end through the host-buffer entry points (the C ABI calls a host program makes): every step uploads its
+    # inputs from pinned host memory and downloads its result.  A host that feeds batch after batch submits the next
+    # call before it waits for the previous one (two calls in flight, two sets of host buffers), so that the result of
+    # one step crosses PCIe while the next one's inputs cross it the other way and its kernels run; `value` is that
+    # stream of calls, `sync_call_ms` one call at a time (submit + wait back to back).
     if args.no_e2e:
         pass
-    elif world == 1:
-        t_host = torch.empty((T, H), dtype=torch.int16).pin_memory()
-        t_host.copy_(t_dev.view(torch.int16).cpu())
-        x_host = torch.zeros((T, H), dtype=torch.float32).pin_memory()
-        for i in range(3):
-            blk.forward_host(i % N_WEIGHT_SETS, t_host, x_host)
-        torch.cuda.synchronize()
-        n_e2e = max(K, int(0.3 / max(ms / K * 2.5e-3, 1e-6)))  # about 0.3 s of calls
-        t0 = time.perf_counter()
-        for i in range(n_e2e):
-            blk.forward_host(i % N_WEIGHT_SETS, t_host, x_host)
-        e2e_s = (time.perf_counter() - t0) / n_e2e
-        line["e2e"] = {"value": T / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": T * H * 2 + T * H * 4,
-                       "d2h_bytes_per_step": T * H * 4, "ms_per_step": 1e3 * e2e_s, "calls_timed": n_e2e}
     else:
-        # The host holds the batch once; every rank moves ITS slice of the tokens over PCIe (t and x in, x out) and the
-        # ranks exchange token rows and expert rows over NVLink (dispatch form of the block): per step the
-        # batch crosses the host link once in total, not once per GPU.
-        t_host = torch.empty((n_own, H), dtype=torch.int16).pin_memory()
-        t_host.copy_(t_dev.view(torch.int16)[first:first + n_own].cpu())
-        x_host = torch.zeros((n_own, H), dtype=torch.float32).pin_memory()
-        for i in range(3):
-            blk.forward_host_sliced(i % N_WEIGHT_SETS, T, t_host, x_host)
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(K):
-            blk.forward_host_sliced(i % N_WEIGHT_SETS, T, t_host, x_host)
-        barrier()
-        e2e_s = torch.tensor([time.perf_counter() - t0], device="cuda")
-        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-        line["e2e"] = {"value": T * K / float(e2e_s.item()), "unit": "tok/s",
-                       "h2d_bytes_per_step": T * H * 2 + T * H * 4, "d2h_bytes_per_step": T * H * 4,
-                       "ms_per_step": 1e3 * float(e2e_s.item()) / K,
-                       "note": "bytes over all GPUs; each GPU copies its own token slice (1/N of them)"}
+        sliced = world > 1
+        rows, lo = (n_own, first) if sliced else (T, 0)
+        t_host, x_host = [], []
+        for _ in range(2):
+            th = torch.empty((rows, H), dtype=torch.int16).pin_memory()
+            th.copy_(t_dev.view(torch.int16)[lo:lo + rows].cpu())
+            t_host.append(th)
+            x_host.append(torch.zeros((rows, H), dtype=torch.float32).pin_memory())
+
+        def submit(i):
+            if sliced:
+                # The host holds the batch once; every rank moves ITS slice of the tokens over PCIe (t and x in, x out)
+                # and the ranks exchange token rows and expert rows over NVLink (dispatch form of the block)
+                blk.forward_host_sliced_submit(i % N_WEIGHT_SETS, T, t_host[i & 1], x_host[i & 1])
+            else:
+                blk.forward_host_submit(i % N_WEIGHT_SETS, t_host[i & 1], x_host[i & 1])
+
+        def stream_of_calls(n):
+            submit(0)
+            for i in range(1, n):
+                submit(i)
+                blk.forward_host_wait()  # call i - 1: its result is in x_host[(i - 1) & 1]
+            blk.forward_host_wait()
+
+        def one_at_a_time(n):
+            for i in range(n):
+                submit(i)
+                blk.forward_host_wait()
+
+        n_e2e = max(K, 50, int(0.3 / max(ms / K * 2.5e-3, 1e-6))) if not sliced else max(K, 50)  # about 0.3 s of calls
+        timings = {}
+        for name, fn, n in (("stream", stream_of_calls, n_e2e), ("sync", one_at_a_time, max(K, 20))):
+            fn(4)
+            torch.cuda.synchronize()
+            barrier()
+            t0 = time.perf_counter()
+            fn(n)
+            dt = time.perf_counter() - t0
+            if sliced:
+                tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                dt = float(tt.item())
+            timings[name] = dt / n
+        line["e2e"] = {"value": T / timings["stream"], "unit": "tok/s", "h2d_bytes_per_step": T * H * 2 + T * H * 4,
+                       "d2h_bytes_per_step": T * H * 4, "ms_per_step": 1e3 * timings["stream"], "calls_timed": n_e2e,
+                       "calls_in_flight": 2, "sync_call_ms": 1e3 * timings["sync"],
+                       "sync_call_tok_per_s": T / timings["sync"],
+                       "api": ("gptoss_moe_forward_host_sliced_submit" if sliced else "gptoss_moe_forward_host_submit")
+                              + " / gptoss_moe_forward_host_wait"}
+        if sliced:
+            line["e2e"]["note"] = "bytes over all GPUs; each GPU copies its own token slice (1/N of them)"
 
     # the skewed-routing workload: T = 8192 tokens in total, Zipf s = 1.2 over the expert ids, experts sharded E/N
     if not args.no_extras:

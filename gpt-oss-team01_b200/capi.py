@@ -45,6 +45,7 @@ EXPORTS = [
     "gptoss_moe_route_local", "gptoss_moe_route_finish", "gptoss_moe_sliced_route",
     "gptoss_moe_dispatch_route", "gptoss_moe_dispatch_rows", "gptoss_moe_dispatch_push", "gptoss_moe_forward_dispatch",
     "gptoss_launch_count", "gptoss_argmax_rows", "gptoss_model_step_rows", "gptoss_model_step_seqs",
+    "gptoss_moe_forward_host_submit", "gptoss_moe_forward_host_sliced_submit", "gptoss_moe_forward_host_wait",
     "gptoss_model_layer_moe_dispatch",
 ]
 
@@ -164,6 +165,9 @@ def load() -> C.CDLL:
         "gptoss_argmax_rows": ([vp, i32, i32, vp, vp], i32),
         "gptoss_model_step_rows": ([vp, vp, vp, i32, i32, vp], i32),
         "gptoss_model_step_seqs": ([vp, vp, vp, vp, i32, vp], i32),
+        "gptoss_moe_forward_host_submit": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_moe_forward_host_sliced_submit": ([ctxp, i32, i32, vp, vp], i32),
+        "gptoss_moe_forward_host_wait": ([ctxp], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

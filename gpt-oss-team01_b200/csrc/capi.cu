@@ -65,15 +65,22 @@ struct gptoss_ctx {
   int gather_step = 0;  // token-sliced form: number of slice gathers so far (flag C carries it)
   int pending_gather = 0;  // gather step the next route_finish has to wait for (0 = none)
   int *status = nullptr;              // [kStatusWords]
-  __nv_bfloat16 *t_stage = nullptr;   // [max_tokens,H]  device copies for the host-buffer entry point
-  float *x_stage = nullptr;           // [max_tokens,H]
+  // Host-buffer entry points: two sets of device copies, so that a second call can be submitted (its uploads and
+  // kernels running) while the first one's result is still on its way back to the host
+  struct HostSlot {
+    __nv_bfloat16 *t = nullptr;       // [max_tokens,H]
+    float *x = nullptr;               // [max_tokens,H]
+    int *status_host = nullptr;       // pinned copy of the status words, read back behind the result
+    cudaEvent_t ev_t = nullptr, ev_x = nullptr, ev_done = nullptr, ev_out = nullptr;
+    bool busy = false;
+  } hslot[2];
+  int h_head = 0, h_tail = 0;         // slot of the next submit / of the oldest call not yet waited for
+  cudaStream_t s_out = nullptr;       // device -> host copies of the results
   float *router_partials = nullptr;   // [kRouterMaxSplits][max_tokens][E] split-K partial scores
   CUtensorMap map_t;                  // tensor map of the caller's activations (re-encoded when they move)
   const void *map_t_base = nullptr;
   int map_t_rows = -1;
-  cudaStream_t s_main = nullptr, s_copy = nullptr;  // streams of the host-buffer entry point (created on first use)
-  cudaEvent_t ev_x = nullptr, ev_t = nullptr;
-  int *status_host = nullptr;         // pinned copy of the status words
+  cudaStream_t s_main = nullptr, s_copy = nullptr;  // kernels / host -> device copies of the host-buffer entry points (created on first use)
   float *staging = nullptr;           // fp32 scratch for weight conversion
   size_t staging_elems = 0;
   CUtensorMap map_x, map_h;
@@ -289,8 +296,10 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->comm_counter, 4));  // [0] exchange kernels, [1] shared routing, [2] row dispatch
   if (e == cudaSuccess) A(cudaMemset(ctx->comm_counter, 0, 4 * sizeof(int)));
   A(dev_alloc(&ctx->status, kStatusWords));
-  A(dev_alloc(&ctx->t_stage, T * H));
-  A(dev_alloc(&ctx->x_stage, T * H));
+  for (auto &hs : ctx->hslot) {
+    A(dev_alloc(&hs.t, T * H));
+    A(dev_alloc(&hs.x, T * H));
+  }
   A(dev_alloc(&ctx->router_partials, (size_t)kRouterMaxSplits * T * E));
   if (e == cudaSuccess) A(cudaMemset(ctx->status, 0, kStatusWords * sizeof(int)));
   // rows never written by the gather are still read by TMA (their columns are discarded): keep them finite
@@ -323,15 +332,18 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->sym);
   cudaFree(ctx->comm_counter);
   cudaFree(ctx->status);
-  cudaFree(ctx->t_stage);
-  cudaFree(ctx->x_stage);
+  for (auto &hs : ctx->hslot) {
+    cudaFree(hs.t);
+    cudaFree(hs.x);
+    for (cudaEvent_t ev : {hs.ev_t, hs.ev_x, hs.ev_done, hs.ev_out})
+      if (ev) cudaEventDestroy(ev);
+    if (hs.status_host) cudaFreeHost(hs.status_host);
+  }
+  if (ctx->s_out) cudaStreamDestroy(ctx->s_out);
   cudaFree(ctx->router_partials);
   cudaFree(ctx->staging);
   if (ctx->s_main) cudaStreamDestroy(ctx->s_main);
   if (ctx->s_copy) cudaStreamDestroy(ctx->s_copy);
-  if (ctx->ev_x) cudaEventDestroy(ctx->ev_x);
-  if (ctx->ev_t) cudaEventDestroy(ctx->ev_t);
-  if (ctx->status_host) cudaFreeHost(ctx->status_host);
   delete ctx;
   return GPTOSS_OK;
 }
@@ -826,80 +838,124 @@ int gptoss_moe_forward_partial(gptoss_ctx *ctx, int layer, int T, const void *t_
   return forward_common(ctx, layer, T, t_dev_bf16, partial_dev, 0, stream);
 }
 
-int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host) {
+// ---- host buffers ---------------------------------------------------------------------------------------------
+// A call is submitted (uploads on the copy stream, kernels on the main stream, the result's way back on a third
+// stream, all chained by events) and waited for separately; two calls may be in flight, so that the second one's upload
+// and kernels run while the first one's result crosses PCIe in the other direction.  The plain entry points are a
+// submit followed by a wait.
+static int host_streams(gptoss_ctx *ctx) {
+  if (ctx->s_main) return GPTOSS_OK;
+  CK(cudaStreamCreateWithFlags(&ctx->s_main, cudaStreamNonBlocking));
+  CK(cudaStreamCreateWithFlags(&ctx->s_copy, cudaStreamNonBlocking));
+  CK(cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking));
+  for (auto &hs : ctx->hslot) {
+    for (cudaEvent_t *ev : {&hs.ev_t, &hs.ev_x, &hs.ev_done, &hs.ev_out}) CK(cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
+    CK(cudaHostAlloc(reinterpret_cast<void **>(&hs.status_host), kStatusWords * sizeof(int), cudaHostAllocDefault));
+  }
+  return GPTOSS_OK;
+}
+
+// rows: token rows this rank moves over PCIe (all T of them, or its slice of a group's batch)
+static int host_submit(gptoss_ctx *ctx, int layer, int T, int rows, const uint16_t *t_host, float *x_host, bool sliced) {
+  int rc = host_streams(ctx);
+  if (rc) return rc;
+  gptoss_ctx::HostSlot &hs = ctx->hslot[ctx->h_head];
+  if (hs.busy) return ctx->fail(GPTOSS_ERR_STATE, "two host-buffer calls are already in flight: wait for the older one first");
+  const size_t n = (size_t)rows * ctx->d.H;
+  // activations first (the routing needs them at once); the residual is needed only by the last kernel, so its
+  // upload follows on the same copy stream and runs beside the routing and the GEMMs
+  if (n) CK(cudaMemcpyAsync(hs.t, t_host, n * sizeof(uint16_t), cudaMemcpyHostToDevice, ctx->s_copy));
+  CK(cudaEventRecord(hs.ev_t, ctx->s_copy));
+  if (n) CK(cudaMemcpyAsync(hs.x, x_host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
+  CK(cudaEventRecord(hs.ev_x, ctx->s_copy));
+  CK(cudaStreamWaitEvent(ctx->s_main, hs.ev_t, 0));
+  if (T > 0 && !sliced) {
+    if ((rc = gptoss_moe_route(ctx, layer, T, hs.t, ctx->s_main))) return rc;
+    if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, ctx->s_main))) return rc;
+    if ((rc = gptoss_moe_mlp2(ctx, layer, ctx->s_main))) return rc;
+    CK(cudaStreamWaitEvent(ctx->s_main, hs.ev_x, 0));
+    if ((rc = gptoss_moe_combine(ctx, T, hs.x, 1, ctx->s_main))) return rc;
+  } else if (T > 0) {
+    if ((rc = gptoss_moe_dispatch_route(ctx, layer, T, hs.t, ctx->s_main))) return rc;
+    if ((rc = gptoss_moe_dispatch_rows(ctx, layer, T, hs.t, ctx->s_main))) return rc;
+    if ((rc = gptoss_moe_dispatch_push(ctx, layer, ctx->s_main))) return rc;
+    CK(cudaStreamWaitEvent(ctx->s_main, hs.ev_x, 0));
+    if ((rc = gptoss_moe_sliced_combine(ctx, hs.x, ctx->s_main))) return rc;
+  }
+  CK(cudaEventRecord(hs.ev_done, ctx->s_main));
+  CK(cudaStreamWaitEvent(ctx->s_out, hs.ev_done, 0));
+  if (n) CK(cudaMemcpyAsync(x_host, hs.x, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_out));
+  CK(cudaMemcpyAsync(hs.status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_out));
+  CK(cudaEventRecord(hs.ev_out, ctx->s_out));
+  hs.busy = true;
+  ctx->h_head ^= 1;
+  return GPTOSS_OK;
+}
+
+int gptoss_moe_forward_host_submit(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host) {
   int rc = check_layer(ctx, layer, true);
   if (rc) return rc;
   if ((rc = check_T(ctx, T))) return rc;
-  if (!t_host || !x_host) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
-  if (T == 0) return GPTOSS_OK;
+  if (ctx->world > 1) return ctx->fail(GPTOSS_ERR_STATE, "world > 1: use gptoss_moe_forward_host_sliced_submit");
+  if (T > 0 && (!t_host || !x_host)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
   CK(cudaSetDevice(ctx->device));
-  if (!ctx->s_main) {
-    CK(cudaStreamCreateWithFlags(&ctx->s_main, cudaStreamNonBlocking));
-    CK(cudaStreamCreateWithFlags(&ctx->s_copy, cudaStreamNonBlocking));
-    CK(cudaEventCreateWithFlags(&ctx->ev_x, cudaEventDisableTiming));
-    CK(cudaEventCreateWithFlags(&ctx->ev_t, cudaEventDisableTiming));
-    CK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), kStatusWords * sizeof(int), cudaHostAllocDefault));
-  }
-  const size_t n = (size_t)T * ctx->d.H;
-  // activations first (the routing needs them at once); the residual is needed only by the last kernel, so
-  // its upload follows on a second stream and runs beside the routing and the GEMMs
-  CK(cudaMemcpyAsync(ctx->t_stage, t_host, n * sizeof(uint16_t), cudaMemcpyHostToDevice, ctx->s_main));
-  CK(cudaEventRecord(ctx->ev_t, ctx->s_main));
-  CK(cudaStreamWaitEvent(ctx->s_copy, ctx->ev_t, 0));
-  CK(cudaMemcpyAsync(ctx->x_stage, x_host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
-  CK(cudaEventRecord(ctx->ev_x, ctx->s_copy));
-  if (ctx->world == 1) {
-    if ((rc = gptoss_moe_route(ctx, layer, T, ctx->t_stage, ctx->s_main))) return rc;
-    if ((rc = gptoss_moe_mlp1_swiglu(ctx, layer, ctx->s_main))) return rc;
-    if ((rc = gptoss_moe_mlp2(ctx, layer, ctx->s_main))) return rc;
-    CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
-    if ((rc = gptoss_moe_combine(ctx, T, ctx->x_stage, 1, ctx->s_main))) return rc;
-  } else {
-    CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
-    if ((rc = gptoss_moe_forward(ctx, layer, T, ctx->t_stage, ctx->x_stage, ctx->s_main))) return rc;
-  }
-  CK(cudaMemcpyAsync(x_host, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_main));
-  CK(cudaMemcpyAsync(ctx->status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_main));
-  CK(cudaStreamSynchronize(ctx->s_main));
-  if (ctx->status_host[0] != 0) return gptoss_ctx_status(ctx);  // formats the message and clears the word
-  return GPTOSS_OK;
+  return host_submit(ctx, layer, T, T, t_host, x_host, false);
 }
 
 // Token-sliced form through host buffers: this rank's rows of t and x only (the host -> device traffic of a step is
 // then the batch once over all GPUs instead of once per GPU); the rows of the other ranks arrive over NVLink.
-int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice) {
+int gptoss_moe_forward_host_sliced_submit(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice) {
   int rc = check_attached(ctx);
   if (rc) return rc;
   if ((rc = check_layer(ctx, layer, true))) return rc;
   if ((rc = check_T(ctx, T))) return rc;
-  if (T == 0) return GPTOSS_OK;
   int first = 0, n_rows = 0;
   gptoss_moe_slice_bounds(ctx, T, &first, &n_rows);
   if (n_rows > 0 && (!t_host_slice || !x_host_slice)) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
   CK(cudaSetDevice(ctx->device));
-  if (!ctx->s_main) {
-    CK(cudaStreamCreateWithFlags(&ctx->s_main, cudaStreamNonBlocking));
-    CK(cudaStreamCreateWithFlags(&ctx->s_copy, cudaStreamNonBlocking));
-    CK(cudaEventCreateWithFlags(&ctx->ev_x, cudaEventDisableTiming));
-    CK(cudaEventCreateWithFlags(&ctx->ev_t, cudaEventDisableTiming));
-    CK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), kStatusWords * sizeof(int), cudaHostAllocDefault));
-  }
-  const size_t n = (size_t)n_rows * ctx->d.H;
-  if (n) CK(cudaMemcpyAsync(ctx->t_stage, t_host_slice, n * sizeof(uint16_t), cudaMemcpyHostToDevice, ctx->s_main));
-  CK(cudaEventRecord(ctx->ev_t, ctx->s_main));
-  CK(cudaStreamWaitEvent(ctx->s_copy, ctx->ev_t, 0));  // the residual rows follow the activations on the copy engine
-  if (n) CK(cudaMemcpyAsync(ctx->x_stage, x_host_slice, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy));
-  CK(cudaEventRecord(ctx->ev_x, ctx->s_copy));
-  if ((rc = gptoss_moe_dispatch_route(ctx, layer, T, ctx->t_stage, ctx->s_main))) return rc;
-  if ((rc = gptoss_moe_dispatch_rows(ctx, layer, T, ctx->t_stage, ctx->s_main))) return rc;
-  if ((rc = gptoss_moe_dispatch_push(ctx, layer, ctx->s_main))) return rc;
-  CK(cudaStreamWaitEvent(ctx->s_main, ctx->ev_x, 0));
-  if ((rc = gptoss_moe_sliced_combine(ctx, ctx->x_stage, ctx->s_main))) return rc;
-  if (n) CK(cudaMemcpyAsync(x_host_slice, ctx->x_stage, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_main));
-  CK(cudaMemcpyAsync(ctx->status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_main));
-  CK(cudaStreamSynchronize(ctx->s_main));
-  if (ctx->status_host[0] != 0) return gptoss_ctx_status(ctx);
+  return host_submit(ctx, layer, T, n_rows, t_host_slice, x_host_slice, true);
+}
+
+int gptoss_moe_forward_host_wait(gptoss_ctx *ctx) {
+  if (!ctx) return GPTOSS_ERR_BAD_ARG;
+  gptoss_ctx::HostSlot &hs = ctx->hslot[ctx->h_tail];
+  if (!hs.busy) return ctx->fail(GPTOSS_ERR_STATE, "no host-buffer call in flight");
+  CK(cudaSetDevice(ctx->device));
+  CK(cudaEventSynchronize(hs.ev_out));
+  hs.busy = false;
+  ctx->h_tail ^= 1;
+  if (hs.status_host[0] != 0) return gptoss_ctx_status(ctx);  // formats the message and clears the word
   return GPTOSS_OK;
+}
+
+int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host) {
+  if (ctx && ctx->world > 1) {  // a group: every rank passes the whole batch and gets the whole result
+    int rc = check_layer(ctx, layer, true);
+    if (rc) return rc;
+    if ((rc = check_T(ctx, T))) return rc;
+    if (!t_host || !x_host) return ctx->fail(GPTOSS_ERR_BAD_ARG, "null host pointer");
+    if (T == 0) return GPTOSS_OK;
+    if (ctx->hslot[0].busy || ctx->hslot[1].busy) return ctx->fail(GPTOSS_ERR_STATE, "host-buffer calls in flight");
+    CK(cudaSetDevice(ctx->device));
+    if ((rc = host_streams(ctx))) return rc;
+    gptoss_ctx::HostSlot &hs = ctx->hslot[0];
+    const size_t n = (size_t)T * ctx->d.H;
+    CK(cudaMemcpyAsync(hs.t, t_host, n * sizeof(uint16_t), cudaMemcpyHostToDevice, ctx->s_main));
+    CK(cudaMemcpyAsync(hs.x, x_host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->s_main));
+    if ((rc = gptoss_moe_forward(ctx, layer, T, hs.t, hs.x, ctx->s_main))) return rc;
+    CK(cudaMemcpyAsync(x_host, hs.x, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->s_main));
+    CK(cudaMemcpyAsync(hs.status_host, ctx->status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, ctx->s_main));
+    CK(cudaStreamSynchronize(ctx->s_main));
+    if (hs.status_host[0] != 0) return gptoss_ctx_status(ctx);
+    return GPTOSS_OK;
+  }
+  int rc = gptoss_moe_forward_host_submit(ctx, layer, T, t_host, x_host);
+  return rc ? rc : gptoss_moe_forward_host_wait(ctx);
+}
+
+int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice) {
+  int rc = gptoss_moe_forward_host_sliced_submit(ctx, layer, T, t_host_slice, x_host_slice);
+  return rc ? rc : gptoss_moe_forward_host_wait(ctx);
 }
 
 // ---- peer memory ----------------------------------------------------------------------------------------------

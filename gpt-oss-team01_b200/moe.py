@@ -176,6 +176,15 @@ class MoEBlock:
         T = t_bits.shape[0]
         self._check(self.lib.gptoss_moe_forward_host(self._ctx, layer, T, _ptr(t_bits), _ptr(x)))
 
+    def forward_host_submit(self, layer, t_bits, x):
+        """First half of forward_host: queues the uploads, the kernels and the download; at most two calls in flight.
+        The buffers must stay alive (pinned, for the overlap) until the matching forward_host_wait()."""
+        self._check(self.lib.gptoss_moe_forward_host_submit(self._ctx, layer, t_bits.shape[0], _ptr(t_bits), _ptr(x)))
+
+    def forward_host_wait(self):
+        """Blocks until the oldest submitted host-buffer call has finished; its x then holds the result."""
+        self._check(self.lib.gptoss_moe_forward_host_wait(self._ctx))
+
     # -- token-sliced form: every rank holds only its rows of the residual stream ---------------------------------
     def slice(self, n_tokens):
         """(first token, token count) of this rank's slice of a batch of n_tokens."""
@@ -236,6 +245,10 @@ class MoEBlock:
         """Host buffers holding THIS RANK'S rows of a batch of n_tokens: t_bits_slice uint16 [n,H], x_slice fp32 [n,H]
         in/out.  Synchronous; every rank calls it."""
         self._check(self.lib.gptoss_moe_forward_host_sliced(self._ctx, layer, n_tokens, _ptr(t_bits_slice), _ptr(x_slice)))
+
+    def forward_host_sliced_submit(self, layer, n_tokens, t_bits_slice, x_slice):
+        """First half of forward_host_sliced (forward_host_wait is the other); every rank submits the same calls."""
+        self._check(self.lib.gptoss_moe_forward_host_sliced_submit(self._ctx, layer, n_tokens, _ptr(t_bits_slice), _ptr(x_slice)))
 
     # -- stages (reference launcher names in the docstrings) --------------------------------------------------
     def route(self, layer, t, stream=None):

@@ -101,6 +101,16 @@ int gptoss_moe_forward(gptoss_ctx *ctx, int layer, int T, const void *t_dev_bf16
 /* Same with HOST buffers (t: bf16 bits [T,H]; x: fp32 [T,H] in/out): copies in, runs, copies out,
  * synchronises, and returns the device status.  Pinned host memory makes the copies asynchronous. */
 int gptoss_moe_forward_host(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host);
+/* The same call in two halves, for a host that feeds batch after batch: submit returns once the uploads, the kernels and
+ * the download of the result are queued; wait blocks until the OLDEST submitted call has finished (its x_host then
+ * holds the result) and returns its device status.  Two calls may be in flight: while the result of one crosses PCIe
+ * towards the host, the next one's activations cross it the other way and its kernels run, so a stream of batches
+ * is bound by the slowest of the three (upload, kernels, download) instead of their sum.  A third submit without a
+ * wait is refused (GPTOSS_ERR_STATE); the host buffers must stay valid (and pinned, for the overlap) until the wait.
+ * Between a submit and its wait the context serves host-buffer calls only.  (The reference keeps its activations on
+ * the device, getp-csrc/src/model.cpp:153-489; these entry points exist for hosts that do not.) */
+int gptoss_moe_forward_host_submit(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host, float *x_host);
+int gptoss_moe_forward_host_wait(gptoss_ctx *ctx);
 /* Expert-parallel partial: partial[T,H] (fp32, device, overwritten) = sum over THIS rank's experts
  * of gate_weight * expert(t) — the tensor the reference all-reduces (rs_now->e_agg,
  * getp-csrc/src/model.cpp:411-423).  The caller reduces it across ranks and adds it to x. */
@@ -213,6 +223,8 @@ int gptoss_moe_forward_dispatch(gptoss_ctx *ctx, int layer, int T, const void *t
  * x + MoE(t) for them.  Per step each GPU moves only its slice over PCIe (the batch crosses the host link once in
  * total, not once per GPU); the other ranks' activations arrive over NVLink.  Synchronous; every rank must call it. */
 int gptoss_moe_forward_host_sliced(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice);
+/* Its submit half (gptoss_moe_forward_host_wait is the other): every rank submits the same calls in the same order. */
+int gptoss_moe_forward_host_sliced_submit(gptoss_ctx *ctx, int layer, int T, const uint16_t *t_host_slice, float *x_host_slice);
 
 /* ---- stages of the operator (same order as inside gptoss_moe_forward) ------------------------------
  * They work on the context's scratch so that a test can stop after any stage and read the taps. */

@@ -247,6 +247,48 @@ def test_forward_is_deterministic_and_host_entry_point_agrees():
     blk.close()
 
 
+def test_host_calls_in_flight_give_the_results_of_one_call_at_a_time():
+    """gptoss_moe_forward_host_submit / _wait: two host-buffer calls may be in flight (the second one's upload and
+    kernels run while the first one's result travels back).  A stream of calls on different inputs, different batch
+    sizes and two layers must return, call by call, what the synchronous entry point returns; a third submit and a
+    wait without a submit are refused with a status code."""
+    from gptoss_b200 import capi, moe
+    H, I, E, k, T = 256, 192, 16, 4, 600
+    blk = moe.MoEBlock(hidden=H, intermediate=I, n_experts=E, top_k=k, max_tokens=T, n_layers=2)
+    blk.fill_layer_synthetic(0, seed=3, sigma=0.05)
+    blk.fill_layer_synthetic(1, seed=4, sigma=0.05)
+    calls = []
+    for i, n in enumerate([600, 37, 512, 600, 1, 300, 600]):
+        t = synth.activations(100 + i, n, H)
+        x0 = synth.normal(100 + i, synth.tensor_id(synth.TID_RESIDUAL), (n, H), 1.0)
+        calls.append((i % 2, torch.from_numpy(synth.f32_to_bf16_bits(t).view(np.int16).reshape(n, H)).pin_memory(), x0))
+    want = []
+    for layer, t_bits, x0 in calls:
+        x = torch.from_numpy(x0.copy()).pin_memory()
+        blk.forward_host(layer, t_bits, x)
+        want.append(x.numpy().copy())
+    for rep in range(2):  # the second pass starts from the other pair of device buffers
+        xs = [torch.from_numpy(x0.copy()).pin_memory() for _, _, x0 in calls]
+        blk.forward_host_submit(calls[0][0], calls[0][1], xs[0])
+        for i in range(1, len(calls)):
+            blk.forward_host_submit(calls[i][0], calls[i][1], xs[i])
+            if i == 3:
+                with pytest.raises(moe.GptossError) as e:  # two in flight already
+                    blk.forward_host_submit(calls[i][0], calls[i][1], xs[i])
+                assert e.value.code == capi.ERR_STATE
+            blk.forward_host_wait()
+            assert np.array_equal(xs[i - 1].numpy(), want[i - 1]), (rep, i - 1)
+        blk.forward_host_wait()
+        assert np.array_equal(xs[-1].numpy(), want[-1])
+        with pytest.raises(moe.GptossError) as e:
+            blk.forward_host_wait()  # nothing in flight
+        assert e.value.code == capi.ERR_STATE
+        if rep == 0:
+            blk.forward_host(0, calls[1][1], torch.from_numpy(calls[1][2].copy()).pin_memory())  # shifts the slots by one
+    blk.status()
+    blk.close()
+
+
 def test_errors_are_status_codes_not_aborts():
     from gptoss_b200 import capi, moe
     blk = make_block(64, 64, 8, 2, 16)
