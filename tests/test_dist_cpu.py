@@ -158,3 +158,90 @@ def test_partition_covers_all_experts_once():
             r = [expert_range(i, world, E) for i in range(world)]
             assert r[0][0] == 0 and r[-1][1] == E
             assert all(r[i][1] == r[i + 1][0] for i in range(world - 1))
+
+
+def _dispatch_worker(rank, world, port, out_path):
+    """The dispatch form of the GPU path on CPU ranks: every rank holds only ITS slice of the tokens.  It routes its
+    own rows, the routing rows are shared (all ranks then hold the same expert assignment and run the same counting
+    sort), each token row travels only to the ranks whose experts it selected, every rank runs its experts on the rows
+    it received, the gate-weighted expert rows go back to the token's owner, and the owner sums its tokens' k slots in
+    slot order.  gloo all-gathers stand in for the peer stores; a rank reads from a gathered buffer only what the GPU
+    path would have stored into its memory."""
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    sys.path[:0] = [str(root), str(root / "tests")]
+    import __graft_entry__ as entry
+    entry.load_package()
+    import oracle_lib
+    from gptoss_b200 import moe, synth
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    H, I, E, k, T = 64, 48, 8, 2, 50 if world < 8 else 21  # world 8, T 21: the last ranks own no token
+    ora = oracle_lib.oracle()
+    w = synth.MoELayerWeights(H, I, E, 29, sigma=0.05)
+    t_all = synth.activations(29, T, H)  # the whole batch exists only to cut this rank's slice from it and for the check
+    bounds = [moe.slice_bounds(r, world, T) for r in range(world)]
+    per = max(n for _, n in bounds)
+    first, n = bounds[rank]
+    t_own = t_all[first:first + n]
+    # 1. route the own rows, share the routing rows
+    tw_own = np.zeros((per, k), np.float32)
+    ti_own = np.full((per, k), -1, np.int32)
+    if n:
+        tw_own[:n], ti_own[:n], _, _ = ora.topk_softmax(ora.router_scores(t_own, w.router_w, w.router_b), k)
+    tws = [torch.zeros(per, k) for _ in range(world)]
+    tis = [torch.zeros(per, k, dtype=torch.int32) for _ in range(world)]
+    dist.all_gather(tws, torch.from_numpy(tw_own))
+    dist.all_gather(tis, torch.from_numpy(ti_own))
+    tw = np.concatenate([tws[r][:bounds[r][1]].numpy() for r in range(world)])
+    ti = np.concatenate([tis[r][:bounds[r][1]].numpy() for r in range(world)])
+    # 2. dispatch: a token row goes to rank r only if one of its slots selects an expert of r
+    e0, e1 = expert_range(rank, world, E)
+    rows = [torch.zeros(per, H) for _ in range(world)]
+    pad = torch.zeros(per, H)
+    pad[:n] = torch.from_numpy(t_own)
+    dist.all_gather(rows, pad)
+    t_recv = np.zeros((T, H), np.float32)
+    wanted = ((ti >= e0) & (ti < e1)).any(axis=1)  # tokens with a slot on this rank
+    for r, (f, m) in enumerate(bounds):
+        sel = wanted[f:f + m]
+        t_recv[f:f + m][sel] = rows[r][:m].numpy()[sel]  # nothing else of the gathered rows is read
+    # 3. this rank's experts on the rows it received (rows of other tokens stay zero and must not matter)
+    _, _, yp = ora.moe_block(t_recv, tw, ti, w, mode=oracle_lib.MODE_GPU_BF16, e_begin=e0, e_end=e1, taps=True)
+    mine = ((ti >= e0) & (ti < e1)).reshape(-1)
+    yp = np.where(mine[:, None], yp, 0.0).astype(np.float32)
+    # 4. push the expert rows to the tokens' owners, 5. owner sum in slot order
+    send = torch.zeros(world, per * k, H)
+    for r, (f, m) in enumerate(bounds):
+        send[r, :m * k] = torch.from_numpy(yp[f * k:(f + m) * k])
+    gathered = [torch.zeros(world, per * k, H) for _ in range(world)]
+    dist.all_gather(gathered, send)
+    own_rows = torch.zeros(per * k, H)
+    for src in range(world):  # exactly one rank wrote a non-zero row per pair: adding zeros keeps the bits
+        s0, s1 = expert_range(src, world, E)
+        m_src = torch.from_numpy(((ti[first:first + n] >= s0) & (ti[first:first + n] < s1)).reshape(-1))
+        own_rows[:n * k][m_src] = gathered[src][rank][:n * k][m_src]
+    got_own = ora.combine_slots(own_rows[:n * k].numpy(), tw[first:first + n]) if n else np.zeros((0, H), np.float32)
+    # check against the single-rank block on the whole batch
+    tw_f, ti_f, _, _ = ora.topk_softmax(ora.router_scores(t_all, w.router_w, w.router_b), k)
+    _, _, yp_full = ora.moe_block(t_all, tw_f, ti_f, w, mode=oracle_lib.MODE_GPU_BF16, taps=True)
+    want = ora.combine_slots(yp_full, tw_f)
+    ok = torch.tensor([float(np.array_equal(ti, ti_f) and np.array_equal(tw, tw_f) and
+                             np.array_equal(got_own, want[first:first + n]))])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        np.save(out_path, np.array([float(ok.item()), float(np.abs(want).max() > 0)]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_dispatch_form_on_token_slices_equals_the_single_rank_block_bitwise(world, tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "res.npy"
+    mp.spawn(_dispatch_worker, args=(world, port, str(out)), nprocs=world, join=True)
+    same, nonzero = np.load(out)
+    assert same == 1.0 and nonzero == 1.0
