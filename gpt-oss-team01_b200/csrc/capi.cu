@@ -44,7 +44,7 @@ struct gptoss_ctx {
   //   [flags: 4*kMaxRanks ints, padded to 1 KiB][delta: T*H fp32][y_pairs: P*H fp32][topk_w: P fp32][topk_i: P i32]
   //   [blk_hist: n_route_blocks*E i32][x_packed: P*H bf16]
   uint8_t *sym = nullptr;
-  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0, sym_tw_off = 0, sym_ti_off = 0, sym_hist_off = 0, sym_xp_off = 0;
+  size_t sym_bytes = 0, sym_delta_off = 0, sym_y_off = 0, sym_tw_off = 0, sym_ti_off = 0, sym_hist_off = 0, sym_xp_off = 0, sym_sorted_off = 0;
   RowDispatch rows_self{};            // token rows go to this rank's x_packed (its own experts only) ...
   RowDispatch rows_all{};             // ... or to the x_packed of the expert's owner (filled when peers are attached)
   TileBalance balance{};              // how expert_scan_kernel cuts the experts' rows into token blocks
@@ -265,7 +265,6 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   A(dev_alloc(&ctx->rb.scores, T * E));
   A(dev_alloc(&ctx->rb.blk_base, nblk * E));
   A(dev_alloc(&ctx->rb.offsets, E + 1));
-  A(dev_alloc(&ctx->rb.sorted, P));
   A(dev_alloc(&ctx->rb.tb_prefix, E + 1));
   A(dev_alloc(&ctx->rb.tb_prefix2, E + 1));
   A(dev_alloc(&ctx->gate_up, P * I));
@@ -276,7 +275,8 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->sym_ti_off = up(ctx->sym_tw_off + P * sizeof(float));
   ctx->sym_hist_off = up(ctx->sym_ti_off + P * sizeof(int));
   ctx->sym_xp_off = up(ctx->sym_hist_off + nblk * E * sizeof(int));
-  ctx->sym_bytes = up(ctx->sym_xp_off + P * H * sizeof(__nv_bfloat16));
+  ctx->sym_sorted_off = up(ctx->sym_xp_off + P * H * sizeof(__nv_bfloat16));
+  ctx->sym_bytes = up(ctx->sym_sorted_off + P * sizeof(int));
   A(cudaMalloc(reinterpret_cast<void **>(&ctx->sym), ctx->sym_bytes));
   if (e == cudaSuccess) A(cudaMemset(ctx->sym, 0, 1024));
   if (e == cudaSuccess) {
@@ -285,6 +285,7 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
     ctx->rb.topk_i = reinterpret_cast<int *>(ctx->sym + ctx->sym_ti_off);
     ctx->rb.blk_hist = reinterpret_cast<int *>(ctx->sym + ctx->sym_hist_off);
     ctx->x_packed = reinterpret_cast<__nv_bfloat16 *>(ctx->sym + ctx->sym_xp_off);
+    ctx->rb.sorted = reinterpret_cast<int *>(ctx->sym + ctx->sym_sorted_off);
     ctx->rows_self.n = 1;
     ctx->rows_self.experts_per_rank = ctx->n_local;
     ctx->rows_self.xp[0] = ctx->x_packed;
@@ -323,7 +324,6 @@ int gptoss_ctx_destroy(gptoss_ctx *ctx) {
   cudaFree(ctx->rb.scores);
   cudaFree(ctx->rb.blk_base);
   cudaFree(ctx->rb.offsets);
-  cudaFree(ctx->rb.sorted);
   cudaFree(ctx->rb.tb_prefix);
   cudaFree(ctx->rb.tb_prefix2);
   cudaFree(ctx->gate_up);
@@ -756,7 +756,8 @@ int gptoss_moe_dispatch_rows(gptoss_ctx *ctx, int layer, int T, const void *t_sl
   CK(launch_expert_scan(ctx->rb, T, ctx->d, balance_for(ctx), fw, s));
   RowDispatch rd = ctx->rows_all;
   rd.step = ctx->pending_gather = ++ctx->gather_step;
-  // a rank without tokens still places the pair ids and raises its flag
+  // every rank places the pairs of ITS tokens: row and pair id go to the rank of the pair's expert (a rank without
+  // tokens only raises its flag)
   CK(launch_scatter_gather(n > 0 ? static_cast<const __nv_bfloat16 *>(t_slice_dev_bf16) : nullptr, first, n, ctx->rb.topk_i, T, ctx->d,
                            ctx->rb.blk_base, ctx->rb.sorted, rd, s));
   return GPTOSS_OK;
@@ -973,6 +974,7 @@ static void set_share(gptoss_ctx *ctx, int r, uint8_t *base) {
   rd.experts_per_rank = ctx->n_local;
   rd.counter = ctx->comm_counter + 2;
   rd.xp[r] = reinterpret_cast<__nv_bfloat16 *>(base + ctx->sym_xp_off);
+  rd.sorted[r] = reinterpret_cast<int *>(base + ctx->sym_sorted_off);
   rd.flags[r] = reinterpret_cast<int *>(base) + 2 * kMaxRanks + ctx->rank;  // flag C of this rank on rank r
 }
 

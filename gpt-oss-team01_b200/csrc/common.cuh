@@ -57,6 +57,7 @@ struct RowDispatch {
   int step;
   int *counter;
   __nv_bfloat16 *xp[16];
+  int *sorted[16];  // n > 1: the pair id of a dispatched row goes with it, into the sorted order of the expert's owner
   int *flags[16];
 };
 

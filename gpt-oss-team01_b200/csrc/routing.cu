@@ -316,10 +316,11 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
 }
 
 // ---- stable scatter of pair ids (+ optional gather / dispatch of the token rows) ----------------------
-// Every block places the pair ids of its 8 tokens (all tokens of the batch: `sorted` is complete on every rank).
-// Rows: `t` holds the bf16 rows of tokens [t_first, t_first + t_count) (null = ids only); the row of each pair of
-// those tokens is copied to its position in x_packed — of this rank, for slots of its own experts (rd.n == 1), or of
-// the rank that owns the slot's expert (rd.n > 1: the dispatch half of the expert-parallel exchange, peer stores).
+// Every block places the pair ids of its 8 tokens.  rd.n == 1: all tokens of the batch, so `sorted` is complete on this
+// rank.  Rows: `t` holds the bf16 rows of tokens [t_first, t_first + t_count) (null = ids only); the row of each pair
+// of those tokens is copied to its position in x_packed — of this rank, for slots of its own experts (rd.n == 1), or,
+// together with its pair id, of the rank that owns the slot's expert (rd.n > 1: the dispatch half of the
+// expert-parallel exchange, peer stores; a rank then holds the sorted order of its own experts' rows only).
 __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat16 *__restrict__ t, int t_first, int t_count,
                                                              const int *__restrict__ topk_i, int T, Dims d,
                                                              const int *__restrict__ blk_base,
@@ -328,12 +329,13 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
   __shared__ int pos_s[kTokensPerRouteBlock * kMaxTopK];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k = d.k;
-  // The blocks that copy rows (the tokens [t_first, t_first + t_count)) take the lowest block indices, so that they
-  // are scheduled first on every rank: in the dispatch form their peer stores are what the other ranks wait for, and
-  // the placement-only blocks of the other tokens fill in behind them.  (t_first is a multiple of the 8 tokens per block.)
-  const int blk = (int)((blockIdx.x + (unsigned)(t_first / kTokensPerRouteBlock)) % gridDim.x);
+  // rd.n == 1: one block per 8 tokens of the whole batch (this rank keeps the complete sorted order).  rd.n > 1
+  // (dispatch): one block per 8 tokens of this rank's slice only — the pairs of the other tokens are placed by their
+  // owners, which store row and pair id straight into this rank's buffers.  (t_first is a multiple of 8.)
+  const bool own_only = rd.n > 1;
+  const int blk = own_only ? t_first / kTokensPerRouteBlock + (int)blockIdx.x : (int)blockIdx.x;
   const int first = blk * kTokensPerRouteBlock * k;
-  const int n = min(kTokensPerRouteBlock, T - blk * kTokensPerRouteBlock) * k;
+  const int n = max(0, min(kTokensPerRouteBlock, (own_only ? t_first + t_count : T) - blk * kTokensPerRouteBlock)) * k;
   pdl_wait();
   pdl_launch_dependents();
   for (int q = threadIdx.x; q < kTokensPerRouteBlock * k; q += blockDim.x)
@@ -346,7 +348,7 @@ __global__ void __launch_bounds__(1024) scatter_gather_kernel(const __nv_bfloat1
       int rank = 0;
       for (int r = 0; r < q; ++r) rank += (ids[r] == e);
       pos = blk_base[(size_t)blk * d.E + e] + rank;
-      sorted[pos] = first + q;
+      (own_only ? rd.sorted[min(rd.n - 1, e / rd.experts_per_rank)] : sorted)[pos] = first + q;
     }
     pos_s[q] = pos;
   }
@@ -501,8 +503,9 @@ cudaError_t launch_expert_scan(const RouteBuffers &rb, int T, const Dims &d, con
 
 cudaError_t launch_scatter_gather(const __nv_bfloat16 *t, int t_first, int t_count, const int *topk_i, int T, const Dims &d,
                                   const int *blk_base, int *sorted, const RowDispatch &rd, cudaStream_t s) {
-  return launch_chain(scatter_gather_kernel, dim3(route_blocks(T)), dim3(t ? 1024 : 256), 0, s, t, t_first, t_count, topk_i, T,
-                      d, blk_base, sorted, rd);
+  const int blocks = rd.n > 1 ? (t_count + kTokensPerRouteBlock - 1) / kTokensPerRouteBlock : route_blocks(T);
+  return launch_chain(scatter_gather_kernel, dim3(blocks > 0 ? blocks : 1), dim3(t ? 1024 : 256), 0, s, t, t_first, t_count,
+                      topk_i, T, d, blk_base, sorted, rd);
 }
 
 cudaError_t launch_combine(const float *y_pairs, const int *topk_i, int T, const Dims &d, float *x,

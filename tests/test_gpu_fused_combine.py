@@ -256,14 +256,15 @@ def test_dispatch_form_matches_single_context_bitwise(world, T, E):
             b.sliced_combine(x)
         for b in ranks:
             b.status()
-            for name in ("topk_i", "topk_w", "offsets", "sorted"):
+            for name in ("topk_i", "topk_w", "offsets"):
                 assert np.array_equal(b.tap(name, T), single.tap(name, T)), name
-        # every rank received exactly the rows of its experts, in the grouped order
-        off, xp = single.tap("offsets", T), single.tap("x_packed", T)
+        # every rank received exactly the rows of its experts, and their pair ids, in the grouped order
+        off, xp, srt = single.tap("offsets", T), single.tap("x_packed", T), single.tap("sorted", T)
         n_local = E // world
         for r, b in enumerate(ranks):
             lo, hi = off[r * n_local], off[(r + 1) * n_local]
             assert np.array_equal(b.tap("x_packed", T)[lo:hi], xp[lo:hi])
+            assert np.array_equal(b.tap("sorted", T)[lo:hi], srt[lo:hi])
         assert torch.equal(torch.cat(xs), want)
     for b in ranks + [single]:
         b.close()
