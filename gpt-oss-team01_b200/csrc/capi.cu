@@ -49,6 +49,7 @@ struct gptoss_ctx {
   RowDispatch rows_all{};             // ... or to the x_packed of the expert's owner (filled when peers are attached)
   TileBalance balance{};              // how expert_scan_kernel cuts the experts' rows into token blocks
   bool pair_policy = false;           // expert GEMMs on pairs of CTAs (GPTOSS_PAIR=1)
+  int balance_pushing_gemm = -1;      // size the token blocks of a group's down GEMM too: -1 by the number of local experts, 0 / 1 forced
   bool pair_mode = false;             // the routed batch's GEMMs run on pairs (decided when the batch is grouped)
   bool pushed_bf16 = false;           // the rows of the last push travelled as bf16 (token-sliced forms on the bf16 wire)
   bool group_broken = false;          // a wait on a peer gave up: the ranks' step counters no longer match
@@ -180,10 +181,15 @@ TileBalance balance_for(gptoss_ctx *ctx) {
     b.nft2 = H <= kTileF ? 1 : (H + 2 * kTileF - 1) / (2 * kTileF);
     b.fixed_rows = kMaxTileTokens;
   }
-  // The down GEMM of a group of GPUs keeps blocks of 256 rows (no items: every size costs the same, the largest wins):
-  // its epilogue stores the rows to their owners over NVLink, and more, smaller items were measured slower there on
-  // two real GPUs (96 us against 92.5) although faster without the push (86 against 97).
-  if (ctx->world > 1) b.nft2 = 0;
+  // The down GEMM of a group of GPUs stores its rows to their owners over NVLink from its epilogue, which makes more,
+  // smaller items dearer than the model knows.  Measured on real GPUs: with 16 local experts (2 GPUs) the balanced
+  // blocks lose (96 us against 92.5, although they win without the push: 86 against 97), with 4 local experts (8
+  // GPUs), where the fill of the rounds matters most, they win (gate/up + down with push 198 us against 207), with 8
+  // (4 GPUs) it makes no difference (213-214 against 216).  So the down GEMM is balanced up to 4 local experts and keeps
+  // blocks of 256 rows beyond (no items: every size costs the same, the largest wins).  GPTOSS_BALANCE_PUSH=0/1 forces
+  // either for measurements.
+  const bool balance_down = ctx->balance_pushing_gemm >= 0 ? ctx->balance_pushing_gemm != 0 : ctx->n_local <= 4;
+  if (ctx->world > 1 && !balance_down) b.nft2 = 0;
   return b;
 }
 
@@ -254,6 +260,7 @@ int gptoss_ctx_create(const gptoss_moe_dims *dims, int device, int rank, int wor
   ctx->peers.timeout_ns = 2000000000ull;
   if (const char *e = getenv("GPTOSS_SHARED_ROUTING")) ctx->share_routing = world > 1 && e[0] == '1';
   if (const char *e = getenv("GPTOSS_TOKEN_BLOCK")) ctx->balance.force_rows = atoi(e);  // measurement aid: fixed token-block size
+  if (const char *e = getenv("GPTOSS_BALANCE_PUSH")) ctx->balance_pushing_gemm = atoi(e) != 0 ? 1 : 0;
   if (const char *e = getenv("GPTOSS_PAIR")) ctx->pair_policy = atoi(e) != 0;           // expert GEMMs on pairs of CTAs
 
   const size_t T = max_tokens, H = dims->hidden, I = dims->intermediate, E = dims->n_experts, k = dims->top_k;
