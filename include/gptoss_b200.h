@@ -281,7 +281,7 @@ const char *gptoss_noalloc_last_error(void);
 #define GPTOSS_TAP_TOPK_W 1    /* fp32 [T,k]   gate weights                                        */
 #define GPTOSS_TAP_TOPK_I 2    /* int32 [T,k]  expert ids                                          */
 #define GPTOSS_TAP_OFFSETS 3   /* int32 [E+1]  expert_offsets                                      */
-#define GPTOSS_TAP_SORTED 4    /* int32 [T*k]  sorted_pair_ids                                     */
+#define GPTOSS_TAP_SORTED 4    /* int32 [T*k]  sorted_pair_ids (dispatch form: rows of this rank's experts only) */
 #define GPTOSS_TAP_X_PACKED 5  /* bf16 [T*k,H] gathered inputs (rows of this rank's experts only)  */
 #define GPTOSS_TAP_GATE_UP 6   /* bf16 [T*k,I] SwiGLU output, rows in sorted order                 */
 #define GPTOSS_TAP_Y_PAIRS 7   /* fp32 [T*k,H] gate_weight * expert output, rows by PAIR id        */
