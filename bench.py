@@ -447,7 +447,8 @@ def run_ours(args):
         nvlink = {"bytes_out_per_gpu_per_step_max": int(t_out.item()), "dispatch_rows_out": rows_out, "pushed_rows_out": push_out,
                   "pushed_row_dtype": "bf16" if wire == 1 else "f32",
                   "time_at_900_GBs_ms": float(t_out.item()) / 900e9 * 1e3,
-                  "achieved_GBs_over_step": float(t_out.item()) / (ms / K * 1e-3) / 1e9 if step is step_dispatch else None}
+                  "achieved_GBs_over_step": float(t_out.item()) / (ms / K * 1e-3) / 1e9 if step is step_dispatch else None,
+                  "bytes_counted_for": "the dispatch form (token rows out + expert rows out), whichever form `value` times"}
     pairs_local = rows_here
     mlp1_bytes = n_local * (2 * I * H * 2 + 2 * I * 4) + pairs_local * H * 2 + pairs_local * I * 2
     mlp1_flops = 2 * pairs_local * H * 2 * I
@@ -500,6 +501,8 @@ def run_ours(args):
                            "stubbed_exchange_without_rendezvous_ms_per_step": stub_free_ms,
                            "nccl_allreduce_baseline_ms_per_step": nccl_ms,
                            ("replicated_form_ms_per_step" if step is step_dispatch else "dispatch_form_ms_per_step"): other_form_ms,
+                           "other_timings": "one region of K steps each (a burst: where `value`, the median of regions over "
+                                            "0.5 s, runs under the power cap they read lower than a sustained run would)",
                            "dispatch_stage_ms": dispatch_stage_ms, "nvlink": nvlink}
         line["combine"].update(parity)
 
@@ -866,7 +869,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the extra legs of the line (skewed T=8192 workload, whole-model decode)")
     ap.add_argument("--form", choices=["dispatch", "replicated"], default="dispatch",
-                    help="N > 1: which form of the expert-parallel block `value` times (the other is reported beside it)")
+                    help="N > 1: which form of the expert-parallel block `value` times (the other is reported beside it, "
+                         "timed over one short region)")
     ap.add_argument("--tokens-per-gpu", type=int, default=0,
                     help="tokens per step and GPU (0 = 1024, the headline workload; 8192 on one GPU: the block is tensor-bound)")
     ap.add_argument("--zipf", type=float, default=0.0,
