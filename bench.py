@@ -309,23 +309,15 @@ def run_ours(args):
     value = T * K / (ms * 1e-3)
 
     def timed_once(fn, sync_each=None):
+        """ms per step of another arm, timed like `value`: the median of K-step regions over 0.3 s, so that it runs
+        under the same clocks (a single short region would run at burst clocks where `value` is power-capped)."""
+        def one(i):
+            fn(i)
+            if sync_each:
+                sync_each()
         for i in range(3):
-            fn(i)
-            if sync_each:
-                sync_each()
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for i in range(K):
-            fn(i)
-            if sync_each:
-                sync_each()
-        s1.record()
-        barrier()
-        ts = torch.tensor([s0.elapsed_time(s1)], device="cuda")
-        if world > 1:
-            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
-        return float(ts.item()) / K
+            one(i)
+        return statistics.median(timed_regions(one, K, barrier, world, dist, torch, min_seconds=0.3)) / K
 
     nccl_ms = stub_ms = stub_free_ms = other_form_ms = None
     parity = None
@@ -501,8 +493,7 @@ def run_ours(args):
                            "stubbed_exchange_without_rendezvous_ms_per_step": stub_free_ms,
                            "nccl_allreduce_baseline_ms_per_step": nccl_ms,
                            ("replicated_form_ms_per_step" if step is step_dispatch else "dispatch_form_ms_per_step"): other_form_ms,
-                           "other_timings": "one region of K steps each (a burst: where `value`, the median of regions over "
-                                            "0.5 s, runs under the power cap they read lower than a sustained run would)",
+                           "other_timings": "each the median of K-step regions over 0.3 s (sustained, like `value`)",
                            "dispatch_stage_ms": dispatch_stage_ms, "nvlink": nvlink}
         line["combine"].update(parity)
 
