@@ -226,7 +226,9 @@ __device__ __forceinline__ int blocks_of(int rows, int size) { return (rows + si
 // (and only then lets its successor start: a kernel that became resident behind a pending flag wait would sit in its
 // own waits for as long as the slowest peer takes).
 __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int n_blocks, Dims d, TileBalance tb, FlagWait fw) {
-  __shared__ int seg_sum[1024];
+  __shared__ __align__(16) int seg_sum4[4096];  // per (team or segment, expert) sums, then their exclusive prefixes
+  int *const seg_sum = seg_sum4;
+  __shared__ int chunk_sum[1024];
   __shared__ int off_s[kMaxExperts + 1];
   const int E = d.E;
   const int nseg = 1024 / E;
@@ -234,37 +236,109 @@ __global__ void __launch_bounds__(1024) expert_scan_kernel(RouteBuffers rb, int 
   pdl_wait();
   if (fw.step > 0) wait_all_ranks(fw.flags, fw.world, fw.step, fw.timeout_ns, fw.status, fw.site);
   pdl_launch_dependents();
-  const int seg = tid / E, e = tid % E;
-  const bool active = seg < nseg;
-  const int per = (n_blocks + nseg - 1) / nseg;
-  const int b0 = min(n_blocks, seg * per), b1 = min(n_blocks, b0 + per);
-  if (active) {
-    int sum = 0;
-    for (int b = b0; b < b1; ++b) sum += rb.blk_hist[(size_t)b * E + e];
-    seg_sum[seg * E + e] = sum;
-  }
-  __syncthreads();
-  if (tid < E) {
-    int run = 0;
-    for (int s = 0; s < nseg; ++s) {
-      const int v = seg_sum[s * E + tid];
-      seg_sum[s * E + tid] = run;
-      run += v;
+  if ((E & 3) == 0) {
+    // E a multiple of 4 (every real configuration): E/4 threads read one block's histogram row as 16-byte pieces, the
+    // 1024 threads form 1024 / (E/4) such teams, and each team owns a contiguous run of blocks, so a pass over all
+    // blocks is n_blocks / teams iterations of independent 16-byte loads (8 for 8192 tokens and 32 experts).
+    int *const team_sum = seg_sum4;
+    const int G = E >> 2, teams = 1024 / G;
+    const int team = tid / G, g = tid - team * G;
+    const bool active = team < teams;
+    const int per = (n_blocks + teams - 1) / teams;
+    const int b0 = min(n_blocks, team * per), b1 = min(n_blocks, b0 + per);
+    if (active) {
+      int4 sum = make_int4(0, 0, 0, 0);
+#pragma unroll 4
+      for (int b = b0; b < b1; ++b) {
+        const int4 h = reinterpret_cast<const int4 *>(rb.blk_hist + (size_t)b * E)[g];
+        sum.x += h.x, sum.y += h.y, sum.z += h.z, sum.w += h.w;
+      }
+      reinterpret_cast<int4 *>(team_sum + team * E)[g] = sum;
     }
-    off_s[tid + 1] = run;  // count of expert tid
-  }
-  __syncthreads();
-  if (tid == 0) {
-    off_s[0] = 0;
-    for (int x = 0; x < E; ++x) off_s[x + 1] += off_s[x];
-  }
-  __syncthreads();
-  if (tid <= E) rb.offsets[tid] = off_s[tid];
-  if (active) {
-    int run = off_s[e] + seg_sum[seg * E + e];
-    for (int b = b0; b < b1; ++b) {
-      rb.blk_base[(size_t)b * E + e] = run;
-      run += rb.blk_hist[(size_t)b * E + e];
+    __syncthreads();
+    // exclusive prefix over the teams, per expert, in two levels with consecutive lanes on consecutive experts (no
+    // bank conflicts): runs of teams ("chunks") are summed by one thread per (chunk, expert), E threads walk the
+    // 1024 / E chunk sums, and the chunk threads turn their teams' sums into prefixes
+    {
+      const int chunks = 1024 / E, tpc = (teams + chunks - 1) / chunks;
+      const int chunk = tid / E, e = tid - chunk * E;
+      const int c0 = min(teams, chunk * tpc), c1 = min(teams, c0 + tpc);
+      const bool has = chunk < chunks;
+      if (has) {
+        int csum = 0;
+        for (int t = c0; t < c1; ++t) csum += team_sum[t * E + e];
+        chunk_sum[chunk * E + e] = csum;
+      }
+      __syncthreads();
+      if (tid < E) {
+        int run = 0;
+        for (int c = 0; c < chunks; ++c) {
+          const int v = chunk_sum[c * E + tid];
+          chunk_sum[c * E + tid] = run;
+          run += v;
+        }
+        off_s[tid + 1] = run;  // count of expert tid
+      }
+      __syncthreads();
+      if (has) {
+        int run = chunk_sum[chunk * E + e];
+        for (int t = c0; t < c1; ++t) {
+          const int v = team_sum[t * E + e];
+          team_sum[t * E + e] = run;
+          run += v;
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      off_s[0] = 0;
+      for (int x = 0; x < E; ++x) off_s[x + 1] += off_s[x];
+    }
+    __syncthreads();
+    if (tid <= E) rb.offsets[tid] = off_s[tid];
+    if (active) {
+      const int4 p = reinterpret_cast<const int4 *>(team_sum + team * E)[g];
+      int4 run = make_int4(off_s[4 * g] + p.x, off_s[4 * g + 1] + p.y, off_s[4 * g + 2] + p.z, off_s[4 * g + 3] + p.w);
+#pragma unroll 4
+      for (int b = b0; b < b1; ++b) {
+        const int4 h = reinterpret_cast<const int4 *>(rb.blk_hist + (size_t)b * E)[g];
+        reinterpret_cast<int4 *>(rb.blk_base + (size_t)b * E)[g] = run;
+        run.x += h.x, run.y += h.y, run.z += h.z, run.w += h.w;
+      }
+    }
+  } else {
+    const int seg = tid / E, e = tid % E;
+    const bool active = seg < nseg;
+    const int per = (n_blocks + nseg - 1) / nseg;
+    const int b0 = min(n_blocks, seg * per), b1 = min(n_blocks, b0 + per);
+    if (active) {
+      int sum = 0;
+      for (int b = b0; b < b1; ++b) sum += rb.blk_hist[(size_t)b * E + e];
+      seg_sum[seg * E + e] = sum;
+    }
+    __syncthreads();
+    if (tid < E) {
+      int run = 0;
+      for (int s = 0; s < nseg; ++s) {
+        const int v = seg_sum[s * E + tid];
+        seg_sum[s * E + tid] = run;
+        run += v;
+      }
+      off_s[tid + 1] = run;  // count of expert tid
+    }
+    __syncthreads();
+    if (tid == 0) {
+      off_s[0] = 0;
+      for (int x = 0; x < E; ++x) off_s[x + 1] += off_s[x];
+    }
+    __syncthreads();
+    if (tid <= E) rb.offsets[tid] = off_s[tid];
+    if (active) {
+      int run = off_s[e] + seg_sum[seg * E + e];
+      for (int b = b0; b < b1; ++b) {
+        rb.blk_base[(size_t)b * E + e] = run;
+        run += rb.blk_hist[(size_t)b * E + e];
+      }
     }
   }
   // token-block prefix of the local experts for the GEMM tile schedulers
